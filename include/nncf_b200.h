@@ -1,0 +1,130 @@
+/*
+ * nncf_b200 -- C ABI of the B200 (sm_100a) weight-compression kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*; NULL = the legacy default stream).  The caller owns all
+ * memory: inputs are read-only unless stated, outputs are caller-allocated device buffers.
+ * No entry point allocates or frees device memory, synchronises the device or keeps
+ * per-call state.  Return value: 0 on success, a negative NNCFB_E_* code otherwise;
+ * nncfb_last_error() returns a human-readable description of the last failure on the
+ * calling thread.
+ *
+ * Each declaration cites the reference interface (nncf 3.2.0, path relative to the
+ * reference project root) whose arithmetic it replaces.  "WC" abbreviates
+ * src/nncf/quantization/algorithms/weight_compression.
+ */
+#ifndef NNCF_B200_H_
+#define NNCF_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NNCFB_ABI_VERSION 1
+
+/* status codes */
+#define NNCFB_OK 0
+#define NNCFB_E_BAD_ARG (-1)      /* null pointer, bad enum, size <= 0 */
+#define NNCFB_E_GROUP_SIZE (-2)   /* reduce %% group_size != 0 (reference: InvalidGroupSizeError) */
+#define NNCFB_E_UNSUPPORTED (-3)  /* combination not implemented */
+#define NNCFB_E_ALIGNMENT (-4)    /* pointer not aligned as documented */
+#define NNCFB_E_CUDA (-5)         /* a CUDA runtime call or launch failed */
+#define NNCFB_E_TOO_LARGE (-6)    /* size beyond a documented maximum */
+#define NNCFB_E_TIMEOUT (-7)      /* a bounded device-side wait gave up */
+
+/* element types of weights / activations */
+#define NNCFB_F32 0
+#define NNCFB_F16 1
+#define NNCFB_BF16 2
+#define NNCFB_I32 3
+
+/* compression modes (same meaning as nncf.parameters.CompressWeightsMode, src/nncf/parameters.py:72-118) */
+#define NNCFB_INT8_SYM 0
+#define NNCFB_INT8_ASYM 1
+#define NNCFB_INT4_SYM 2
+#define NNCFB_INT4_ASYM 3
+#define NNCFB_NF4 4
+#define NNCFB_MXFP4 5
+#define NNCFB_FP4 6
+#define NNCFB_FP8_E4M3 7
+#define NNCFB_MXFP8_E4M3 8
+
+/* layout of codes_out */
+#define NNCFB_CODES_NONE 0
+#define NNCFB_CODES_BYTE 1   /* one byte per element: int8 (sym), uint8 (asym), format bit pattern (float modes) */
+#define NNCFB_CODES_NIBBLE 2 /* 4-bit modes: two codes per byte in flat element order, even index -> low nibble;
+                                INT4_SYM codes are stored with the +8 offset of pack_int4 */
+
+/*
+ * Arguments of nncfb_quantize.  The weight is viewed as [outer, reduce, inner] (row-major);
+ * quantisation parameters are shared by `group_size` consecutive elements along `reduce`
+ * (group_size == reduce: per channel).  nn.Linear / nn.Embedding weights have inner == 1.
+ * G = reduce / group_size.  All per-group tensors are laid out [outer, G, inner], which is
+ * the flat order of the reference's [a1, G, 1, a2] tensors.
+ */
+typedef struct nncfb_quantize_args {
+  const void* weight;     /* device, NNCFB_F32 / F16 / BF16, contiguous */
+  int32_t weight_dtype;
+  int32_t mode;           /* NNCFB_INT8_SYM ... NNCFB_MXFP8_E4M3 */
+  int64_t outer, reduce, inner;
+  int64_t group_size;
+  const float* pre_scale; /* optional precomputed scale [outer, G, inner]; NULL = compute from the weight */
+  const void* pre_zp;     /* optional precomputed zero point [outer, G, inner] (asym modes only) */
+  int32_t pre_zp_dtype;   /* NNCFB_I32 or NNCFB_F32 */
+  int32_t codes_format;   /* NNCFB_CODES_* */
+  void* codes_out;        /* [outer*reduce*inner] bytes, or half that for NNCFB_CODES_NIBBLE; may be NULL */
+  float* scale_out;       /* fp32 [outer, G, inner]; may be NULL */
+  int32_t* zp_out;        /* int32 [outer, G, inner], asym modes; may be NULL */
+  uint16_t* scale_f16_out;/* IEEE fp16 bits of the scale (the decompressor's `_scale` buffer); may be NULL */
+  uint8_t* scale_e8m0_out;/* MX modes: biased exponent byte of the power-of-two scale; may be NULL */
+  float* values_out;      /* float modes: decoded fp32 grid value per element (the reference's `tensor`); may be NULL */
+  float* dq_out;          /* dequantised fp32 weight per element; may be NULL */
+  float* sqerr_out;       /* fp32 [outer, G, inner]: sum over the group of (dq - w)^2; may be NULL */
+} nncfb_quantize_args;
+
+/*
+ * Group-wise min/max (or abs-max) reduction, scale / zero-point computation, quantise, clamp,
+ * pack and optional dequantise + squared error in ONE pass over the weight.
+ *
+ * Replaces, bit for bit (fp32 true division, separate zero-point add, round-half-even):
+ *   WC/weight_lowering.py:292-326  calculate_integer_quantization_params
+ *   src/nncf/quantization/fake_quantize.py:322-350  calculate_scale_zero_point
+ *   WC/weight_lowering.py:629-649  _calculate_signed_scale
+ *   WC/weight_lowering.py:652-684  _calculate_integer_quantized_weight
+ *   WC/weight_lowering.py:451-554  do_integer_quantization / integer_quantize_dequantize_weight
+ *   WC/weight_lowering.py:84-128   calculate_float_quantization_params
+ *   WC/weight_lowering.py:557-586  _calculate_float_quantized_weight (NF4, E2M1)
+ *   WC/fp8_conversion.py:211-228   fp32_to_fp8e4m3
+ *   WC/weight_lowering.py:329-374  get_integer_quantization_error (via sqerr_out)
+ *   src/nncf/torch/quantization/quantize_functions.py:417-461  pack_uint4 / pack_int4 (NNCFB_CODES_NIBBLE)
+ * Alignment: weight, codes_out, values_out, dq_out 16-byte aligned.
+ */
+int nncfb_quantize(const nncfb_quantize_args* args, void* stream);
+
+/*
+ * Nibble-pack n byte codes (n even) in flat order: out[i] = (in[2i] & 15) | (in[2i+1] << 4);
+ * `add` is added to every code first (8 for signed int4 codes).
+ * Replaces src/nncf/torch/quantization/quantize_functions.py:417-461 pack_uint4 / pack_int4.
+ */
+int nncfb_pack_nibbles(const void* codes, int64_t n, int32_t add, uint8_t* packed_out, void* stream);
+
+/* Inverse of nncfb_pack_nibbles: out[2i] = (in[i] & 15) - sub, out[2i+1] = (in[i] >> 4) - sub (int8 out).
+ * Replaces quantize_functions.py:436-444,464-473 unpack_uint4 / unpack_int4. */
+int nncfb_unpack_nibbles(const uint8_t* packed, int64_t n_bytes, int32_t sub, int8_t* codes_out, void* stream);
+
+/* Exhaustive-style self check of the in-kernel fp32 division against IEEE division on n
+ * pseudo-random operand pairs drawn from `seed`; writes the number of mismatches to
+ * *mismatch_out (device int64).  Test hook, no reference counterpart. */
+int nncfb_selftest_division(int64_t n, uint64_t seed, int64_t* mismatch_out, void* stream);
+
+/* Library information */
+int nncfb_abi_version(void);
+const char* nncfb_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNCF_B200_H_ */

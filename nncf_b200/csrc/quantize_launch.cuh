@@ -1,0 +1,93 @@
+// Host-side kernel selection for nncfb_quantize, instantiated once per source element type
+// (one translation unit each, so the three compile in parallel).
+#pragma once
+
+#include <algorithm>
+
+#include "quantize_kernels.cuh"
+
+namespace nncfb {
+
+// Which kernel serves a validated request.
+enum class QuantPath { kSubwarp, kWide, kGeneric, kColumn };
+
+inline QuantPath choose_path(int64_t group_size, int64_t inner, bool aligned) {
+  if (inner > 1) return QuantPath::kColumn;
+  if (aligned && group_size % 8 == 0) {
+    if (group_size <= 256 && (group_size & (group_size - 1)) == 0) return QuantPath::kSubwarp;
+    if (group_size >= 512) return QuantPath::kWide;
+  }
+  return QuantPath::kGeneric;
+}
+
+template <typename SrcT, int MODE>
+int launch_quantize_mode(const QArgs& a, QuantPath path, cudaStream_t stream) {
+  const int sms = sm_count();
+  constexpr int kThreads = 256;
+  switch (path) {
+    case QuantPath::kSubwarp: {
+      constexpr int U = 4;
+      const int L = static_cast<int>(a.group_size / 8);
+      const int64_t per_warp_iter = static_cast<int64_t>(32 / L) * U;
+      const int64_t iters = (a.n_groups + per_warp_iter - 1) / per_warp_iter;
+      const int64_t blocks_needed = (iters + (kThreads / 32) - 1) / (kThreads / 32);
+      const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks_needed, static_cast<int64_t>(sms) * 8)));
+      if (L == 16) {
+        quant_subwarp_kernel<SrcT, MODE, 16, U><<<grid, kThreads, 0, stream>>>(a);
+      } else if (L == 4) {
+        quant_subwarp_kernel<SrcT, MODE, 4, U><<<grid, kThreads, 0, stream>>>(a);
+      } else {
+        quant_subwarp_kernel<SrcT, MODE, 0, U><<<grid, kThreads, 0, stream>>>(a);
+      }
+      break;
+    }
+    case QuantPath::kWide: {
+      const int T = a.group_size <= 2048 ? 64 : (a.group_size <= 4096 ? 128 : 256);
+      const int64_t blocks_needed = (a.n_groups + (kThreads / T) - 1) / (kThreads / T);
+      const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks_needed, static_cast<int64_t>(sms) * 8)));
+      quant_wide_kernel<SrcT, MODE><<<grid, kThreads, 0, stream>>>(a, T);
+      break;
+    }
+    case QuantPath::kGeneric: {
+      const int64_t blocks_needed = (a.n_groups + (kThreads / 32) - 1) / (kThreads / 32);
+      const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks_needed, static_cast<int64_t>(sms) * 8)));
+      quant_generic_kernel<SrcT, MODE><<<grid, kThreads, 0, stream>>>(a);
+      break;
+    }
+    case QuantPath::kColumn: {
+      const int cpt = a.codes_format == NNCFB_CODES_NIBBLE ? 2 : 1;
+      const int64_t total = (a.n_groups / a.inner) * ((a.inner + cpt - 1) / cpt);
+      const int64_t blocks_needed = (total + kThreads - 1) / kThreads;
+      const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks_needed, static_cast<int64_t>(sms) * 8)));
+      quant_column_kernel<SrcT, MODE><<<grid, kThreads, 0, stream>>>(a);
+      break;
+    }
+  }
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+template <typename SrcT>
+int launch_quantize_t(const QArgs& a, int mode, QuantPath path, cudaStream_t stream) {
+  switch (mode) {
+    case NNCFB_INT8_SYM: return launch_quantize_mode<SrcT, NNCFB_INT8_SYM>(a, path, stream);
+    case NNCFB_INT8_ASYM: return launch_quantize_mode<SrcT, NNCFB_INT8_ASYM>(a, path, stream);
+    case NNCFB_INT4_SYM: return launch_quantize_mode<SrcT, NNCFB_INT4_SYM>(a, path, stream);
+    case NNCFB_INT4_ASYM: return launch_quantize_mode<SrcT, NNCFB_INT4_ASYM>(a, path, stream);
+    case NNCFB_NF4: return launch_quantize_mode<SrcT, NNCFB_NF4>(a, path, stream);
+    case NNCFB_MXFP4: return launch_quantize_mode<SrcT, NNCFB_MXFP4>(a, path, stream);
+    case NNCFB_FP4: return launch_quantize_mode<SrcT, NNCFB_FP4>(a, path, stream);
+    case NNCFB_FP8_E4M3: return launch_quantize_mode<SrcT, NNCFB_FP8_E4M3>(a, path, stream);
+    case NNCFB_MXFP8_E4M3: return launch_quantize_mode<SrcT, NNCFB_MXFP8_E4M3>(a, path, stream);
+    default: break;
+  }
+  set_error("unknown mode %d", mode);
+  return NNCFB_E_BAD_ARG;
+}
+
+// defined in quantize_f32.cu / quantize_f16.cu / quantize_bf16.cu
+int launch_quantize_f32(const QArgs& a, int mode, QuantPath path, cudaStream_t stream);
+int launch_quantize_f16(const QArgs& a, int mode, QuantPath path, cudaStream_t stream);
+int launch_quantize_bf16(const QArgs& a, int mode, QuantPath path, cudaStream_t stream);
+
+}  // namespace nncfb

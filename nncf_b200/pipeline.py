@@ -1,0 +1,278 @@
+"""Whole-weight-set compression pipeline.
+
+The reference compresses the weights of a model one after another in a Python loop
+(src/nncf/quantization/algorithms/weight_compression/torch_backend.py:442-481: compress_weight,
+range check, offset, pack per weight).  At B200 speed a whole 8B-parameter model is a few
+milliseconds of kernel time, so per-call host work would dominate.  ``CompressionPlan`` resolves
+everything once - tensor list, output buffers, kernel arguments - and replays the launches,
+optionally from a CUDA graph, so a step is pure kernel time.
+
+Work sharding over ranks (``partition_by_bytes``) is a longest-processing-time greedy split of the
+tensors by source bytes; every tensor (and every MoE expert) compresses independently, so ranks
+exchange nothing until the optional gather of the packed results.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from .config import WeightCompressionConfig
+from .parameters import CompressWeightsMode
+
+
+@dataclass
+class PlanItem:
+    name: str
+    weight: torch.Tensor
+    config: WeightCompressionConfig
+    reduction_axis: int = -1
+    # outputs (allocated by the plan)
+    packed: Optional[torch.Tensor] = None
+    scale: Optional[torch.Tensor] = None
+    scale_f16: Optional[torch.Tensor] = None
+    zero_point: Optional[torch.Tensor] = None
+    zero_point_packed: Optional[torch.Tensor] = None
+    scale_e8m0: Optional[torch.Tensor] = None
+    args: Optional[_lib.QuantizeArgs] = field(default=None, repr=False)
+
+    @property
+    def source_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def output_tensors(self) -> list[torch.Tensor]:
+        outs = [self.packed, self.scale_f16 if self.scale_f16 is not None else self.scale]
+        if self.zero_point_packed is not None:
+            outs.append(self.zero_point_packed)
+        elif self.zero_point is not None:
+            outs.append(self.zero_point)
+        if self.scale_e8m0 is not None:
+            outs.append(self.scale_e8m0)
+        return [t for t in outs if t is not None]
+
+    def algorithmic_bytes(self) -> int:
+        """Bytes that must cross HBM: the source once plus each stored output once
+        (codes, one scale per group, zero points / exponent bytes where the mode has them)."""
+        n = self.source_bytes + self.packed.numel()
+        n += self.scale.numel() * 4
+        if self.zero_point is not None:
+            n += self.zero_point.numel() * 4
+        if self.scale_e8m0 is not None:
+            n += self.scale_e8m0.numel()
+        return n
+
+
+def _split(shape: Sequence[int], axis: int) -> tuple[int, int, int]:
+    outer = 1
+    for d in shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in shape[axis + 1:]:
+        inner *= d
+    return outer, shape[axis], inner
+
+
+class CompressionPlan:
+    """Pre-resolved compression of a list of weights on one device.
+
+    ``items``: (name, weight, config[, reduction_axis]) tuples; weights are contiguous CUDA tensors.
+    Outputs are the stored form: nibble-packed codes for 4-bit modes (INT4_SYM with the +8
+    offset), byte codes for 8-bit modes, fp32 scales [groups], int32 zero points for asymmetric modes,
+    E8M0 exponent bytes for MX modes."""
+
+    def __init__(self, items: Sequence[tuple], device: Optional[torch.device] = None, fp16_scales: bool = False):
+        self.items: list[PlanItem] = []
+        self.device = torch.device(device) if device is not None else None
+        for it in items:
+            name, weight, config = it[0], it[1], it[2]
+            axis = it[3] if len(it) > 3 else -1
+            if not weight.is_cuda or not weight.is_contiguous():
+                msg = f"{name}: weights must be contiguous CUDA tensors"
+                raise ValueError(msg)
+            if self.device is None:
+                self.device = weight.device
+            self.items.append(PlanItem(name, weight, config, axis % weight.ndim))
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._fp16_scales = fp16_scales
+        for item in self.items:
+            self._resolve(item)
+
+    def _resolve(self, item: PlanItem) -> None:
+        w, cfg, dev = item.weight, item.config, self.device
+        outer, reduce, inner = _split(tuple(w.shape), item.reduction_axis)
+        gs = cfg.group_size if cfg.group_size != -1 else reduce
+        if reduce % gs != 0:
+            from .errors import InvalidGroupSizeError
+
+            msg = f"Channel size {reduce} should be divisible by size of group {gs}."
+            raise InvalidGroupSizeError(msg)
+        n, n_groups = w.numel(), outer * (reduce // gs) * inner
+        four_bit = cfg.num_bits == 4
+        nibble_ok = four_bit and n % 2 == 0 and ((inner > 1 and inner % 2 == 0) or (inner == 1 and gs % 2 == 0))
+        if four_bit and not nibble_ok:
+            msg = f"{item.name}: shape {tuple(w.shape)} cannot be nibble-packed in one pass"
+            raise ValueError(msg)
+        signed8 = cfg.is_integer and not cfg.is_asym_mode and not four_bit
+        item.packed = torch.empty(n // 2 if four_bit else n, dtype=torch.int8 if signed8 else torch.uint8, device=dev)
+        item.scale = torch.empty(n_groups, dtype=torch.float32, device=dev)
+        a = _lib.QuantizeArgs()
+        a.weight, a.weight_dtype, a.mode = w.data_ptr(), _lib.DTYPE_IDS[w.dtype], _lib.MODE_IDS[cfg.mode.value]
+        a.outer, a.reduce, a.inner, a.group_size = outer, reduce, inner, gs
+        a.codes_format = _lib.CODES_NIBBLE if four_bit else _lib.CODES_BYTE
+        a.codes_out, a.scale_out = item.packed.data_ptr(), item.scale.data_ptr()
+        if self._fp16_scales:
+            item.scale_f16 = torch.empty(n_groups, dtype=torch.float16, device=dev)
+            a.scale_f16_out = item.scale_f16.data_ptr()
+        if cfg.is_integer and cfg.is_asym_mode:
+            item.zero_point = torch.empty(n_groups, dtype=torch.int32, device=dev)
+            a.zp_out = item.zero_point.data_ptr()
+        if cfg.mode in (CompressWeightsMode.MXFP4, CompressWeightsMode.MXFP8_E4M3):
+            item.scale_e8m0 = torch.empty(n_groups, dtype=torch.uint8, device=dev)
+            a.scale_e8m0_out = item.scale_e8m0.data_ptr()
+        item.args = a
+
+    # -- execution --------------------------------------------------------------------------------
+    def launch(self, subset: Optional[Sequence[int]] = None) -> None:
+        """Enqueue the kernels on the current stream (no synchronisation)."""
+        stream = _lib.stream_handle(self.device)
+        fn = _lib.lib.nncfb_quantize
+        items = self.items if subset is None else [self.items[i] for i in subset]
+        for item in items:
+            rc = fn(item.args, stream)
+            if rc != 0:
+                _lib.check(rc)
+
+    def capture(self, subset: Optional[Sequence[int]] = None) -> torch.cuda.CUDAGraph:
+        """Capture the launches in a CUDA graph (the launch-bound loop becomes one replay)."""
+        with torch.cuda.device(self.device):
+            self.launch(subset)  # warm-up outside capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.launch(subset)
+        return graph
+
+    def run(self, use_graph: bool = True) -> None:
+        with torch.cuda.device(self.device):
+            if use_graph:
+                if self._graph is None:
+                    self._graph = self.capture()
+                self._graph.replay()
+            else:
+                self.launch()
+
+    # -- accounting -------------------------------------------------------------------------------
+    @property
+    def source_bytes(self) -> int:
+        return sum(i.source_bytes for i in self.items)
+
+    @property
+    def algorithmic_bytes(self) -> int:
+        return sum(i.algorithmic_bytes() for i in self.items)
+
+    @property
+    def output_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for i in self.items for t in i.output_tensors())
+
+
+def partition_by_bytes(sizes: Sequence[int], world_size: int) -> list[list[int]]:
+    """Longest-processing-time greedy split: indices sorted by size descending, each to the
+    currently lightest rank.  Deterministic, so every rank computes the same assignment.
+    (The reference has no counterpart: it walks the weights sequentially,
+    src/nncf/quantization/algorithms/weight_compression/algorithm.py:1198-1211.)"""
+    order = sorted(range(len(sizes)), key=lambda i: (-sizes[i], i))
+    loads = [0] * world_size
+    parts: list[list[int]] = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda k: (loads[k], k))
+        parts[r].append(i)
+        loads[r] += sizes[i]
+    for p in parts:
+        p.sort()
+    return parts
+
+
+def llama3_8b_weight_shapes(include_embeddings: bool = True) -> list[tuple[str, tuple[int, int]]]:
+    """(name, [out, in]) of every weight matrix of a Llama-3-8B decoder in module order:
+    32 layers, hidden 4096, MLP 14336, 32 query / 8 KV heads of 128, vocabulary 128256."""
+    hidden, mlp, kv, vocab, layers = 4096, 14336, 1024, 128256, 32
+    shapes: list[tuple[str, tuple[int, int]]] = []
+    if include_embeddings:
+        shapes.append(("model.embed_tokens", (vocab, hidden)))
+    for i in range(layers):
+        p = f"model.layers.{i}."
+        shapes += [
+            (p + "self_attn.q_proj", (hidden, hidden)), (p + "self_attn.k_proj", (kv, hidden)),
+            (p + "self_attn.v_proj", (kv, hidden)), (p + "self_attn.o_proj", (hidden, hidden)),
+            (p + "mlp.gate_proj", (mlp, hidden)), (p + "mlp.up_proj", (mlp, hidden)),
+            (p + "mlp.down_proj", (hidden, mlp)),
+        ]
+    if include_embeddings:
+        shapes.append(("lm_head", (vocab, hidden)))
+    return shapes
+
+
+class HostStreamingCompressor:
+    """Compress weights that live in (pinned) host memory and return the stored form to host
+    memory, overlapping the host->device copy of tensor i+1, the kernel of tensor i and the
+    device->host copy of tensor i-1 on three streams.
+
+    This is the end-to-end form of the per-weight loop of
+    src/nncf/quantization/algorithms/weight_compression/torch_backend.py:442-481 for a model
+    whose parameters are on the host (the reference's conformance setup loads the model with
+    device_map="cpu").  Device staging is a ring of ``depth`` slots sized for the largest tensor,
+    so device memory use is independent of the model size."""
+
+    def __init__(self, specs: Sequence[tuple], device: torch.device, depth: int = 3):
+        """``specs``: (name, shape, dtype, config) of the weights, in processing order."""
+        self.device = torch.device(device)
+        self.depth = depth
+        self.specs = list(specs)
+        with torch.cuda.device(self.device):
+            self.s_in, self.s_run, self.s_out = (torch.cuda.Stream() for _ in range(3))
+        max_elems = max(int(torch.Size(s[1]).numel()) for s in self.specs)
+        max_item = max(torch.empty(0, dtype=s[2]).element_size() for s in self.specs)
+        self.slots = [torch.empty(max_elems * max_item, dtype=torch.uint8, device=self.device) for _ in range(depth)]
+        self.slot_free = [torch.cuda.Event() for _ in range(depth)]   # kernel done reading slot
+        self.plans: list[CompressionPlan] = []
+        self.host_out: list[list[torch.Tensor]] = []
+        for k, (name, shape, dtype, cfg) in enumerate(self.specs):
+            n = int(torch.Size(shape).numel())
+            view = self.slots[k % depth][: n * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(*shape)
+            plan = CompressionPlan([(name, view, cfg)], self.device)
+            self.plans.append(plan)
+            self.host_out.append([torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                                  for t in plan.items[0].output_tensors()])
+        self.h2d_bytes = sum(int(torch.Size(s[1]).numel()) * torch.empty(0, dtype=s[2]).element_size() for s in self.specs)
+        self.d2h_bytes = sum(t.numel() * t.element_size() for outs in self.host_out for t in outs)
+
+    def run(self, host_weights: Sequence[torch.Tensor]) -> list[list[torch.Tensor]]:
+        """Enqueue one pass; returns the pinned host outputs (valid after ``synchronize``)."""
+        with torch.cuda.device(self.device):
+            loaded = [torch.cuda.Event() for _ in self.specs]
+            done = [torch.cuda.Event() for _ in self.specs]
+            for k, hw in enumerate(host_weights):
+                slot = k % self.depth
+                item = self.plans[k].items[0]
+                with torch.cuda.stream(self.s_in):
+                    if k >= self.depth:
+                        self.s_in.wait_event(self.slot_free[slot])
+                    item.weight.copy_(hw, non_blocking=True)
+                    loaded[k].record(self.s_in)
+                with torch.cuda.stream(self.s_run):
+                    self.s_run.wait_event(loaded[k])
+                    self.plans[k].launch()
+                    done[k].record(self.s_run)
+                    self.slot_free[slot].record(self.s_run)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(done[k])
+                    for dst, src in zip(self.host_out[k], item.output_tensors()):
+                        dst.copy_(src, non_blocking=True)
+        return self.host_out
+
+    def synchronize(self) -> None:
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.synchronize()

@@ -1,0 +1,228 @@
+"""GPU parity of the fused quantisation kernels (through the C ABI) against the reference's
+golden outputs and, on larger seeded inputs, against the CPU oracle.
+
+Bars: codes, scales, zero points and dequantised values are compared bit for bit (integer and
+byte work; fp32 scales come from the same IEEE operations in the same order).  The squared-error
+metric is a sum whose order differs, so it uses the reference test's tolerances
+(tests/openvino/optimized_functions/test_compression_functions.py:521-559: rtol 1e-4)."""
+
+import numpy as np
+import pytest
+import torch
+from conftest import golden
+
+pytestmark = pytest.mark.gpu
+
+TORCH_DTYPE = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def _cfg(mode, gs):
+    from nncf_b200 import CompressWeightsMode, WeightCompressionConfig
+
+    return WeightCompressionConfig(CompressWeightsMode(mode), gs)
+
+
+def _dev(w32, dtype):
+    return torch.from_numpy(np.ascontiguousarray(w32)).to("cuda").to(TORCH_DTYPE[dtype])
+
+
+def _eq(got: torch.Tensor, ref: np.ndarray, what: str):
+    g = got.detach().cpu().numpy()
+    assert g.shape == ref.shape, f"{what}: shape {g.shape} != {ref.shape}"
+    np.testing.assert_array_equal(g, ref, err_msg=what)
+
+
+@pytest.mark.parametrize("key", golden("quant").index("q"))
+def test_compress_weight_matches_reference_golden(key):
+    from nncf_b200 import weight_lowering as wl
+
+    g = golden("quant")
+    _, name, dtype, mode = key.split("/")
+    axis, gs = (int(v) for v in g[key + "/meta"])
+    w = _dev(g[f"q/{name}/{dtype}/w"], dtype)
+    cfg = _cfg(mode, gs)
+    cw = wl.compress_weight(w, axis, cfg)
+    _eq(cw.scale, g[key + "/scale"], "scale")
+    ref_t = g[key + "/tensor"]
+    assert str(cw.tensor.dtype).replace("torch.", "") == str(ref_t.dtype)
+    _eq(cw.tensor, ref_t, "tensor")
+    if cfg.is_asym_mode:
+        _eq(cw.zero_point, g[key + "/zp"], "zero_point")
+        assert cw.zero_point.dtype == torch.int32
+    else:
+        assert cw.zero_point is None
+    if cfg.is_integer:
+        dq = wl.integer_quantize_dequantize_weight(w, cfg, axis)
+    else:
+        dq = wl.float_quantize_dequantize_weight(w, cfg, axis)
+    _eq(dq, g[key + "/dq"], "dq")
+    if (key + "/err_max_mean") in g:
+        for red in ("max_mean", "frobenius"):
+            got = wl.get_integer_quantization_error(w, axis, cfg, red)
+            assert got == pytest.approx(float(g[key + f"/err_{red}"]), rel=1e-4, abs=1e-9)
+
+
+@pytest.mark.parametrize("key", golden("quant").index("pre"))
+def test_precomputed_parameters_match_reference_golden(key):
+    from nncf_b200 import CompressedWeight
+    from nncf_b200 import weight_lowering as wl
+
+    g = golden("quant")
+    mode = key.split("/")[1]
+    w = _dev(g[key + "/w"], "f32")
+    s = torch.from_numpy(g[key + "/scale"]).cuda()
+    zp = torch.from_numpy(g[key + "/zp"]).cuda() if (key + "/zp") in g else None
+    cw = wl.compress_weight(w, 1, _cfg(mode, 32), CompressedWeight(None, s, zp))
+    _eq(cw.tensor, g[key + "/tensor"], "tensor")
+    if zp is not None:
+        # the ScaleEstimation path hands the zero point over as fp32
+        cw2 = wl.compress_weight(w, 1, _cfg(mode, 32), CompressedWeight(None, s, zp.float()))
+        _eq(cw2.tensor, g[key + "/tensor"], "tensor (fp32 zero point)")
+
+
+def test_precomputed_asym_needs_both():
+    from nncf_b200 import weight_lowering as wl
+
+    w = torch.randn(4, 64, device="cuda")
+    s = torch.ones(4, 2, 1, device="cuda")
+    with pytest.raises(ValueError, match="both scale and zero point"):
+        wl.do_integer_quantization(w, _cfg("int4_asym", 32), 1, s, None)
+
+
+def test_invalid_group_size_raises_reference_error():
+    from nncf_b200 import InvalidGroupSizeError
+    from nncf_b200 import weight_lowering as wl
+
+    with pytest.raises(InvalidGroupSizeError, match="divisible"):
+        wl.compress_weight(torch.randn(4, 100, device="cuda"), 1, _cfg("int4_sym", 32))
+
+
+ORACLE_CASES = [
+    # rows, cols, gs, dtype, kind
+    (96, 4096, 128, "bf16", "normal"),
+    (64, 4096, 128, "f32", "normal"),
+    (33, 1024, 32, "bf16", "normal"),
+    (40, 1024, 64, "f16", "uniform"),
+    (17, 14336, -1, "bf16", "normal"),
+    (31, 4096, -1, "f16", "normal"),
+    (9, 2048, -1, "f32", "uniform"),
+    (5, 20480, -1, "bf16", "normal"),  # row longer than the register cache of the wide kernel
+    (12, 1000, 8, "bf16", "normal"),
+    (10, 768, 256, "f32", "normal"),
+    (7, 520, 520, "bf16", "normal"),    # wide kernel, one group per row, odd vector count
+    (6, 999, 333, "f32", "normal"),     # generic kernel
+]
+MODES = ["int8_sym", "int8_asym", "int4_sym", "int4_asym", "nf4", "mxfp4", "fp4", "fp8_e4m3", "mxfp8_e4m3"]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("rows,cols,gs,dtype,kind", ORACLE_CASES)
+def test_compress_weight_matches_oracle(rows, cols, gs, dtype, kind, mode):
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import weight_lowering as wl
+
+    gen = torch.Generator().manual_seed(rows * 7919 + cols)
+    if kind == "normal":
+        w = torch.randn(rows, cols, generator=gen) * 0.02
+    else:
+        w = torch.rand(rows, cols, generator=gen) * 2 - 1
+    w = w.to(TORCH_DTYPE[dtype])
+    w_np = w.float().numpy() if dtype != "f16" else w.numpy()
+    ref = O.compress_weight(w_np, 1, mode, gs)
+    cfg = _cfg(mode, gs)
+    cw = wl.compress_weight(w.cuda(), 1, cfg)
+    _eq(cw.scale, ref.scale, "scale")
+    _eq(cw.tensor, ref.tensor, "tensor")
+    if cfg.is_asym_mode:
+        _eq(cw.zero_point, ref.zero_point, "zp")
+    # storage path: nibble-packed codes straight from the kernel
+    packed = wl.compress_weight(w.cuda(), 1, cfg, pack=True)
+    if cfg.num_bits == 4 and cfg.is_integer:
+        ref_packed = O.pack_int4(ref.tensor) if mode == "int4_sym" else O.pack_uint4(ref.tensor)
+        _eq(packed.packed, ref_packed, "packed")
+    elif cfg.num_bits == 4:
+        codes = O.nibble_code_nf4(ref.tensor) if mode == "nf4" else O.nibble_code_e2m1(ref.tensor)
+        _eq(packed.packed, O.pack_uint4(codes), "packed float codes")
+    else:
+        if cfg.is_integer:
+            _eq(packed.packed, ref.tensor, "byte codes")
+    _eq(packed.scale_f16, ref.scale.astype(np.float16), "fp16 scale")
+    if mode in ("mxfp4", "mxfp8_e4m3"):
+        _eq(packed.scale_e8m0, O.e8m0_code(ref.scale), "e8m0")
+
+
+@pytest.mark.parametrize("mode", ["int4_sym", "int4_asym", "int8_asym", "nf4", "mxfp4"])
+@pytest.mark.parametrize("shape,axis,gs", [((256, 48), 0, 32), ((128, 30), 0, -1), ((3, 64, 20), 1, 16),
+                                           ((4, 8, 128), 2, 64), ((64, 7), 0, 32)])
+def test_strided_and_stacked_layouts_match_oracle(shape, axis, gs, mode):
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import weight_lowering as wl
+
+    gen = torch.Generator().manual_seed(sum(shape))
+    w = (torch.randn(*shape, generator=gen) * 0.05).to(torch.bfloat16)
+    ref = O.compress_weight(w.float().numpy(), axis, mode, gs)
+    cfg = _cfg(mode, gs)
+    cw = wl.compress_weight(w.cuda(), axis, cfg)
+    _eq(cw.scale, ref.scale, "scale")
+    _eq(cw.tensor, ref.tensor, "tensor")
+    if cfg.is_asym_mode:
+        _eq(cw.zero_point, ref.zero_point, "zp")
+    if cfg.num_bits == 4 and cfg.is_integer:
+        packed = wl.compress_weight(w.cuda(), axis, cfg, pack=True)
+        ref_packed = O.pack_int4(ref.tensor) if mode == "int4_sym" else O.pack_uint4(ref.tensor)
+        _eq(packed.packed, ref_packed, "packed")
+
+
+def test_division_selftest_has_no_mismatch():
+    from nncf_b200 import _lib
+
+    out = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for seed in (1, 2, 3):
+        _lib.check(_lib.lib.nncfb_selftest_division(1 << 28, seed, out.data_ptr(), _lib.stream_handle(out.device)))
+        assert int(out.item()) == 0
+
+
+def test_pack_unpack_round_trip():
+    from nncf_b200 import _lib
+
+    codes = torch.randint(-8, 8, (1 << 20,), dtype=torch.int8, device="cuda")
+    packed = torch.empty(codes.numel() // 2, dtype=torch.uint8, device="cuda")
+    back = torch.empty_like(codes)
+    st = _lib.stream_handle(codes.device)
+    _lib.check(_lib.lib.nncfb_pack_nibbles(codes.data_ptr(), codes.numel(), 8, packed.data_ptr(), st))
+    _lib.check(_lib.lib.nncfb_unpack_nibbles(packed.data_ptr(), packed.numel(), 8, back.data_ptr(), st))
+    assert torch.equal(codes, back)
+    ref = ((codes[0::2].to(torch.int16) + 8) | ((codes[1::2].to(torch.int16) + 8) << 4)).to(torch.uint8)
+    assert torch.equal(packed, ref)
+
+
+@pytest.mark.parametrize("mode,gs", [("int4_sym", 128), ("int4_asym", 128), ("int8_asym", -1), ("nf4", 128),
+                                     ("mxfp4", 32)])
+def test_full_size_properties(mode, gs):
+    """Llama-3-8B gate_proj size (14336 x 4096 bf16): size-independent properties.
+    (1) |dq - w| <= |scale| / 2 wherever the code is not clipped (integer modes);
+    (2) quantising the dequantised weight with the same parameters reproduces the codes."""
+    from nncf_b200 import CompressedWeight
+    from nncf_b200 import weight_lowering as wl
+
+    torch.manual_seed(1)
+    w = (torch.randn(14336, 4096, device="cuda") * 0.02).to(torch.bfloat16)
+    cfg = _cfg(mode, gs)
+    if cfg.is_integer:
+        dq, cw = wl.integer_quantize_dequantize_weight(w, cfg, 1, return_compressed_weight=True)
+    else:
+        dq, cw = wl.float_quantize_dequantize_weight(w, cfg, 1, return_compressed_weight=True)
+    wg = w.float().reshape(dq.shape)
+    if cfg.is_integer:
+        lo, hi = (0, 2 ** cfg.num_bits - 1) if cfg.is_asym_mode else (-(2 ** (cfg.num_bits - 1)), 2 ** (cfg.num_bits - 1) - 1)
+        inside = (cw.tensor > lo) & (cw.tensor < hi)
+        bound = cw.scale.abs() * 0.5 * (1 + 1e-5) + 1e-12
+        assert bool((((dq - wg).abs() <= bound) | ~inside).all())
+        again = wl.do_integer_quantization(dq, cfg, None, cw.scale, cw.zero_point)
+        assert torch.equal(again.tensor, cw.tensor)
+    else:
+        again = wl.do_float_quantization(dq, cfg, None, cw.scale)
+        assert torch.equal(again.tensor, cw.tensor)
+    assert cw.scale.shape == (14336, 4096 // gs if gs != -1 else 1, 1)[: cw.scale.ndim] or gs == -1
