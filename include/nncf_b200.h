@@ -105,6 +105,18 @@ typedef struct nncfb_quantize_args {
 int nncfb_quantize(const nncfb_quantize_args* args, void* stream);
 
 /*
+ * The per-weight loop of a whole model in as few launches as possible: `items` is a HOST array
+ * of n requests.  Consecutive requests that ask for the storage outputs only (codes in their
+ * stored format, scale, zero point; integer modes, inner == 1, same mode / dtype / group size)
+ * are served by ONE persistent kernel whose descriptor table travels as a kernel parameter;
+ * every other request is launched like nncfb_quantize.  Results are identical to n calls of
+ * nncfb_quantize.  Replaces the sequential loop of
+ * WC/torch_backend.py:442-481 (PTWeightCompressionAlgoBackend.transform_model) and
+ * WC/algorithm.py:1198-1211.
+ */
+int nncfb_quantize_batch(const nncfb_quantize_args* items, int32_t n, void* stream);
+
+/*
  * Nibble-pack n byte codes (n even) in flat order: out[i] = (in[2i] & 15) | (in[2i+1] << 4);
  * `add` is added to every code first (8 for signed int4 codes).
  * Replaces src/nncf/torch/quantization/quantize_functions.py:417-461 pack_uint4 / pack_int4.

@@ -57,6 +57,7 @@ def _load() -> C.CDLL:
         "nncfb_abi_version": ([], C.c_int),
         "nncfb_last_error": ([], C.c_char_p),
         "nncfb_quantize": ([C.POINTER(QuantizeArgs), vp], C.c_int),
+        "nncfb_quantize_batch": ([C.POINTER(QuantizeArgs), i32, vp], C.c_int),
         "nncfb_pack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_unpack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_selftest_division": ([i64, u64, vp, vp], C.c_int),
@@ -69,7 +70,7 @@ def _load() -> C.CDLL:
 
 
 lib = _load()
-EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
+EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_quantize_batch", "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
             "nncfb_selftest_division"]
 
 

@@ -3,7 +3,78 @@
 
 using namespace nncfb;
 
+namespace {
+
+int validate(const nncfb_quantize_args* p);
+int launch_general(const nncfb_quantize_args* p, cudaStream_t st);
+
+int launch_fast_run(const nncfb_quantize_args* items, int n, FastClass cls, cudaStream_t st) {
+  // the descriptor table travels as a kernel parameter (no device workspace, graph-capturable)
+  static thread_local FastBatch batch;
+  const size_t esz = items[0].weight_dtype == NNCFB_F32 ? 4 : 2;
+  batch.n_tensors = n;
+  batch.codes_nibble = mode_bits(items[0].mode) == 4;
+  batch.iter_start[0] = 0;
+  for (int i = 0; i < n; ++i) {
+    const nncfb_quantize_args& p = items[i];
+    FastTensor& t = batch.t[i];
+    t.weight = p.weight;
+    t.codes = static_cast<uint8_t*>(p.codes_out);
+    t.scale = p.scale_out;
+    t.zp = p.zp_out;
+    t.scale_f16 = p.scale_f16_out;
+    t.n_groups = p.outer * (p.reduce / p.group_size);
+    batch.iter_start[i + 1] = batch.iter_start[i] + fast_iterations(cls, t.n_groups, esz);
+  }
+  switch (items[0].weight_dtype) {
+    case NNCFB_F32: return launch_fast_f32(batch, items[0].mode, cls, st);
+    case NNCFB_F16: return launch_fast_f16(batch, items[0].mode, cls, st);
+    default: return launch_fast_bf16(batch, items[0].mode, cls, st);
+  }
+}
+
+}  // namespace
+
+extern "C" int nncfb_quantize_batch(const nncfb_quantize_args* items, int32_t n, void* stream) {
+  NNCFB_CHECK_ARG(items != nullptr || n == 0, NNCFB_E_BAD_ARG, "nncfb_quantize_batch: items is null");
+  NNCFB_CHECK_ARG(n >= 0, NNCFB_E_BAD_ARG, "nncfb_quantize_batch: negative count");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < n; ++i) {
+    const int rc = validate(&items[i]);
+    if (rc != NNCFB_OK) return rc;
+  }
+  int i = 0;
+  while (i < n) {
+    const FastClass cls = fast_class(items[i]);
+    if (cls.kind == 0) {
+      const int rc = launch_general(&items[i], st);
+      if (rc != NNCFB_OK) return rc;
+      ++i;
+      continue;
+    }
+    int j = i + 1;
+    while (j < n && j - i < kMaxBatchTensors && items[j].mode == items[i].mode &&
+           items[j].weight_dtype == items[i].weight_dtype && fast_class(items[j]) == cls)
+      ++j;
+    const int rc = launch_fast_run(items + i, j - i, cls, st);
+    if (rc != NNCFB_OK) return rc;
+    i = j;
+  }
+  return NNCFB_OK;
+}
+
 extern "C" int nncfb_quantize(const nncfb_quantize_args* p, void* stream) {
+  const int rc = validate(p);
+  if (rc != NNCFB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const FastClass cls = fast_class(*p);
+  if (cls.kind != 0) return launch_fast_run(p, 1, cls, st);
+  return launch_general(p, st);
+}
+
+namespace {
+
+int validate(const nncfb_quantize_args* p) {
   NNCFB_CHECK_ARG(p != nullptr, NNCFB_E_BAD_ARG, "nncfb_quantize: args is null");
   NNCFB_CHECK_ARG(p->weight != nullptr, NNCFB_E_BAD_ARG, "nncfb_quantize: weight is null");
   NNCFB_CHECK_ARG(p->outer > 0 && p->reduce > 0 && p->inner > 0, NNCFB_E_BAD_ARG,
@@ -44,6 +115,11 @@ extern "C" int nncfb_quantize(const nncfb_quantize_args* p, void* stream) {
                       "nncfb_quantize: nibble output needs an even group size; use byte codes and nncfb_pack_nibbles");
     }
   }
+  return NNCFB_OK;
+}
+
+int launch_general(const nncfb_quantize_args* p, cudaStream_t st) {
+  const bool asym = mode_is_asym(p->mode);
 
   QArgs a;
   a.weight = p->weight;
@@ -68,10 +144,11 @@ extern "C" int nncfb_quantize(const nncfb_quantize_args* p, void* stream) {
   const bool aligned = aligned16(p->weight) && aligned16(p->codes_out) && aligned16(p->values_out) &&
                        aligned16(p->dq_out);
   const QuantPath path = choose_path(p->group_size, p->inner, aligned);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (p->weight_dtype) {
     case NNCFB_F32: return launch_quantize_f32(a, p->mode, path, st);
     case NNCFB_F16: return launch_quantize_f16(a, p->mode, path, st);
     default: return launch_quantize_bf16(a, p->mode, path, st);
   }
 }
+
+}  // namespace

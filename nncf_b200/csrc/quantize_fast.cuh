@@ -1,0 +1,407 @@
+// Speed-of-light variants of the integer quantisation kernels for the storage path
+// (codes + scale [+ zero point] out, parameters computed from the weight itself).
+//
+// The general kernels in quantize_kernels.cuh are instruction-bound on B200: at ~2.5 B/element of
+// HBM traffic the SMs have about a dozen issue slots per element.  This file gets under that
+// budget while producing bit-identical results:
+//   * min/max on packed bf16x2 / f16x2 pairs, one packed shuffle per reduction step carrying
+//     (min, -max) together;
+//   * the exact division by the group's scale as multiply + two FMAs (see Divisor) issued as
+//     packed fp32x2 instructions (fmul2 / ffma2), selected per group, with the plain IEEE
+//     division as the fallback for divisors outside the exact range;
+//   * round-half-even by adding 1.5 * 2^23 (one packed add, no float->int conversions) and
+//     nibble / byte packing by Horner multiply-adds on the raw bit patterns;
+//   * ONE launch for a whole list of tensors (descriptor table in kernel parameters, persistent
+//     warps striding over all groups), so a model is not 200+ launch latencies.
+#pragma once
+
+#include <type_traits>
+
+#include "quantize_kernels.cuh"
+
+namespace nncfb {
+
+constexpr int kMaxBatchTensors = 256;
+
+struct FastTensor {
+  const void* weight;
+  uint8_t* codes;
+  float* scale;
+  int32_t* zp;
+  uint16_t* scale_f16;
+  int64_t n_groups;
+};
+
+struct FastBatch {
+  int n_tensors;
+  int codes_nibble;                            // 1: nibble-packed, 0: one byte per code
+  int64_t iter_start[kMaxBatchTensors + 1];    // prefix sum of warp iterations per tensor
+  FastTensor t[kMaxBatchTensors];
+};
+
+constexpr uint32_t kMagicBits = 0x4B400000u;  // 12582912.0f = 1.5 * 2^23
+
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+
+// (min, -max) of 8 elements packed as two 16-bit floats of the source type (exact: the
+// extremes are source values).  For fp32 sources the pair is kept as two floats.
+struct MinNegMax {
+  uint32_t packed;  // 16-bit sources
+  float mn, nmx;    // fp32 sources
+};
+
+template <typename SrcT, int VPL>
+__device__ __forceinline__ MinNegMax min_negmax(const Raw8<SrcT> (&raw)[VPL]) {
+  MinNegMax r;
+  if constexpr (sizeof(SrcT) == 2) {
+    using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
+    V2 lo, hi;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      const V2* p = reinterpret_cast<const V2*>(&raw[v].r);
+      const V2 l = __hmin2(__hmin2(p[0], p[1]), __hmin2(p[2], p[3]));
+      const V2 h = __hmax2(__hmax2(p[0], p[1]), __hmax2(p[2], p[3]));
+      lo = v == 0 ? l : __hmin2(lo, l);
+      hi = v == 0 ? h : __hmax2(hi, h);
+    }
+    const uint32_t L = *reinterpret_cast<const uint32_t*>(&lo);
+    const uint32_t H = *reinterpret_cast<const uint32_t*>(&hi) ^ 0x80008000u;  // negate both halves
+    const uint32_t a = __byte_perm(L, H, 0x5410);                               // (lo.x, -hi.x)
+    const uint32_t b = __byte_perm(L, H, 0x7632);                               // (lo.y, -hi.y)
+    const V2 m = __hmin2(*reinterpret_cast<const V2*>(&a), *reinterpret_cast<const V2*>(&b));
+    r.packed = *reinterpret_cast<const uint32_t*>(&m);
+    r.mn = r.nmx = 0.0f;
+  } else {
+    float mn = 0.f, mx = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      float a, b;
+      minmax8(raw[v], a, b);
+      mn = v == 0 ? a : fminf(mn, a);
+      mx = v == 0 ? b : fmaxf(mx, b);
+    }
+    r.mn = mn;
+    r.nmx = -mx;
+    r.packed = 0;
+  }
+  return r;
+}
+
+template <typename SrcT>
+__device__ __forceinline__ void reduce_step(MinNegMax& m, int offset) {
+  if constexpr (sizeof(SrcT) == 2) {
+    using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
+    const uint32_t o = __shfl_xor_sync(0xffffffffu, m.packed, offset);
+    const V2 x = __hmin2(*reinterpret_cast<const V2*>(&m.packed), *reinterpret_cast<const V2*>(&o));
+    m.packed = *reinterpret_cast<const uint32_t*>(&x);
+  } else {
+    m.mn = fminf(m.mn, __shfl_xor_sync(0xffffffffu, m.mn, offset));
+    m.nmx = fminf(m.nmx, __shfl_xor_sync(0xffffffffu, m.nmx, offset));
+  }
+}
+
+template <typename SrcT>
+__device__ __forceinline__ void finish_minmax(const MinNegMax& m, float& mn, float& mx) {
+  if constexpr (std::is_same<SrcT, __nv_bfloat16>::value) {
+    mn = __uint_as_float(m.packed << 16);
+    mx = -__uint_as_float(m.packed & 0xffff0000u);
+  } else if constexpr (std::is_same<SrcT, __half>::value) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&m.packed));
+    mn = f.x;
+    mx = -f.y;
+  } else {
+    mn = m.mn;
+    mx = -m.nmx;
+  }
+}
+
+__device__ __forceinline__ void unpack8_pairs(const Raw8<float>& x, float2 (&v)[4]) {
+  v[0] = f2(x.a.x, x.a.y); v[1] = f2(x.a.z, x.a.w); v[2] = f2(x.b.x, x.b.y); v[3] = f2(x.b.z, x.b.w);
+}
+__device__ __forceinline__ void unpack8_pairs(const Raw8<__nv_bfloat16>& x, float2 (&v)[4]) {
+  const uint32_t w[4] = {x.r.x, x.r.y, x.r.z, x.r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = f2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+}
+__device__ __forceinline__ void unpack8_pairs(const Raw8<__half>& x, float2 (&v)[4]) {
+  const uint32_t w[4] = {x.r.x, x.r.y, x.r.z, x.r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+}
+
+// Integer codes of 8 elements as Horner-packed bit patterns.
+//   NIB: returns one word of 8 nibbles (INT4_SYM with the +8 storage offset);
+//   else: returns two words of 4 bytes (signed modes as two's complement).
+// EXACT selects the multiply/FMA division (divisor in the exact range) or the IEEE division.
+template <int MODE, bool EXACT>
+__device__ __forceinline__ uint2 encode8_int(const float2 (&v)[4], float s, float r, float zp) {
+  constexpr bool kAsym = mode_is_asym(MODE);
+  constexpr int kBits = mode_bits(MODE);
+  constexpr float kLow = kAsym ? 0.0f : -static_cast<float>(1 << (kBits - 1));
+  constexpr float kHigh = kAsym ? static_cast<float>((1 << kBits) - 1) : static_cast<float>((1 << (kBits - 1)) - 1);
+  constexpr float kBias = kAsym ? 0.0f : static_cast<float>(1 << (kBits - 1));  // digit = code + bias >= 0
+  const float2 r2 = f2(r, r), ns2 = f2(-s, -s), zp2 = f2(zp, zp), magic2 = f2(12582912.0f + kBias, 12582912.0f + kBias);
+  uint32_t bits[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 q;
+    if constexpr (EXACT) {
+      const float2 q0 = __fmul2_rn(v[i], r2);
+      const float2 e = __ffma2_rn(ns2, q0, v[i]);
+      q = __ffma2_rn(e, r2, q0);
+    } else {
+      q = f2(__fdiv_rn(v[i].x, s), __fdiv_rn(v[i].y, s));
+    }
+    if constexpr (kAsym) q = __fadd2_rn(q, zp2);  // separate fp32 add, as the reference does
+    // clamp-then-round equals round-then-clamp for integer bounds
+    q.x = fmaxf(fminf(q.x, kHigh), kLow);
+    q.y = fmaxf(fminf(q.y, kHigh), kLow);
+    const float2 t = __fadd2_rn(q, magic2);  // round half to even into the low mantissa bits
+    bits[2 * i] = __float_as_uint(t.x);
+    bits[2 * i + 1] = __float_as_uint(t.y);
+  }
+  uint2 out;
+  if constexpr (kBits == 4) {
+    uint32_t acc = bits[7];
+#pragma unroll
+    for (int i = 6; i >= 0; --i) acc = acc * 16u + bits[i];
+    out.x = acc - kMagicBits * 0x11111111u;
+    out.y = 0u;
+  } else {
+    uint32_t a0 = bits[3], a1 = bits[7];
+#pragma unroll
+    for (int i = 2; i >= 0; --i) {
+      a0 = a0 * 256u + bits[i];
+      a1 = a1 * 256u + bits[4 + i];
+    }
+    a0 -= kMagicBits * 0x01010101u;
+    a1 -= kMagicBits * 0x01010101u;
+    if constexpr (!kAsym) {  // offset binary -> two's complement
+      a0 ^= 0x80808080u;
+      a1 ^= 0x80808080u;
+    }
+    out.x = a0;
+    out.y = a1;
+  }
+  return out;
+}
+
+template <int MODE>
+__device__ __forceinline__ void int_params(float mn, float mx, float& s, float& zp) {
+  if constexpr (mode_is_asym(MODE)) {
+    const GroupParams p = asym_params<mode_bits(MODE)>(mn, mx);
+    s = p.scale;
+    zp = p.zp;
+  } else {
+    s = signed_scale<mode_bits(MODE)>(mn, mx);
+    zp = 0.0f;
+  }
+}
+
+__device__ __forceinline__ bool divisor_exact(float s) {
+  const uint32_t e = (__float_as_uint(s) >> 23) & 0xffu;
+  return (e >= 127u - 40u) && (e <= 127u + 40u);
+}
+
+// =====================================================================================================
+// Batched row-group kernel: group_size = 8 * L * VPL (L lanes, VPL 16-byte vectors per lane; lane j
+// owns vectors j, j+L, ... of its group so that every warp load and store is fully coalesced).
+// =====================================================================================================
+template <typename SrcT, int MODE, int L, int VPL, int U>
+__global__ void __launch_bounds__(256, 4) quant_rows_batch_kernel(const __grid_constant__ FastBatch b) {
+  constexpr int GPW = 32 / L;
+  constexpr int GS = 8 * L * VPL;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / L;
+  const int lig = lane % L;
+  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t total_iters = b.iter_start[b.n_tensors];
+
+  for (int64_t it = warp; it < total_iters; it += n_warps) {
+    int lo = 0, hi = b.n_tensors;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (b.iter_start[mid] <= it) lo = mid; else hi = mid;
+    }
+    const FastTensor& T = b.t[lo];
+    const SrcT* __restrict__ src = reinterpret_cast<const SrcT*>(T.weight);
+    const int64_t n_groups = T.n_groups;
+    const int64_t g0 = (it - b.iter_start[lo]) * (GPW * U) + sub;
+
+    Raw8<SrcT> raw[U][VPL];
+#pragma unroll
+    for (int p = 0; p < U; ++p) {
+      const int64_t g = g0 + p * GPW;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        raw[p][v] = g < n_groups ? load_raw8<SrcT>(src + g * GS + (lig + v * L) * 8) : zero_raw8<SrcT>();
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < U; ++p) {
+      const int64_t g = g0 + p * GPW;
+      const bool valid = g < n_groups;
+      MinNegMax m = min_negmax<SrcT, VPL>(raw[p]);
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
+      float mn, mx, s, zp;
+      finish_minmax<SrcT>(m, mn, mx);
+      int_params<MODE>(mn, mx, s, zp);
+      const float r = __frcp_rn(s);
+      const bool exact = __all_sync(0xffffffffu, divisor_exact(s));
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        float2 x[4];
+        unpack8_pairs(raw[p][v], x);
+        const uint2 w = exact ? encode8_int<MODE, true>(x, s, r, zp) : encode8_int<MODE, false>(x, s, r, zp);
+        if (valid) {
+          const int64_t e0 = g * GS + (lig + v * L) * 8;
+          if constexpr (mode_bits(MODE) == 4) {
+            __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
+          } else {
+            __stcs(reinterpret_cast<uint2*>(T.codes + e0), w);
+          }
+        }
+      }
+      if (valid && lig == 0) {
+        T.scale[g] = s;
+        if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
+        if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+      }
+    }
+  }
+}
+
+// =====================================================================================================
+// Batched per-channel kernel (one group per row, row length % 8 == 0): TPR threads per row keep the
+// row in registers (K vectors each); rows longer than TPR*K*8 re-read the tail from L2.
+// =====================================================================================================
+template <typename SrcT, int MODE, int TPR>
+__global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __grid_constant__ FastBatch b,
+                                                                     const int64_t row_len) {
+  constexpr int K = WideCache<SrcT>::K;
+  constexpr int RPB = 256 / TPR;  // rows per block
+  constexpr int WPR = TPR / 32;   // warps per row
+  __shared__ uint32_t red16[8];
+  __shared__ float red_mn[8], red_nmx[8];
+  const int tir = threadIdx.x % TPR;
+  const int rib = threadIdx.x / TPR;
+  const int warp_in_block = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int first_warp = rib * WPR;
+  const int64_t nvec = row_len >> 3;
+  const int64_t total_iters = b.iter_start[b.n_tensors];  // iterations of RPB rows
+
+  for (int64_t it = blockIdx.x; it < total_iters; it += gridDim.x) {
+    int lo = 0, hi = b.n_tensors;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (b.iter_start[mid] <= it) lo = mid; else hi = mid;
+    }
+    const FastTensor& T = b.t[lo];
+    const int64_t g = (it - b.iter_start[lo]) * RPB + rib;
+    const bool valid = g < T.n_groups;
+    const SrcT* __restrict__ row = reinterpret_cast<const SrcT*>(T.weight) + (valid ? g : 0) * row_len;
+
+    Raw8<SrcT> cache[K];
+    bool have[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int64_t j = tir + static_cast<int64_t>(k) * TPR;
+      have[k] = valid && j < nvec;
+      cache[k] = have[k] ? load_raw8<SrcT>(row + j * 8) : zero_raw8<SrcT>();
+    }
+    // thread-local (min, -max), starting from the neutral element (+inf, +inf) so that vectors which
+    // do not exist contribute nothing
+    MinNegMax m;
+    if constexpr (std::is_same<SrcT, __nv_bfloat16>::value) m.packed = 0x7f807f80u;
+    else if constexpr (std::is_same<SrcT, __half>::value) m.packed = 0x7c007c00u;
+    else m.packed = 0u;
+    m.mn = __uint_as_float(0x7f800000u);
+    m.nmx = __uint_as_float(0x7f800000u);
+    auto fold = [&m](const Raw8<SrcT>& vec) {
+      Raw8<SrcT> one[1] = {vec};
+      const MinNegMax x = min_negmax<SrcT, 1>(one);
+      if constexpr (sizeof(SrcT) == 2) {
+        using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
+        const V2 y = __hmin2(*reinterpret_cast<const V2*>(&m.packed), *reinterpret_cast<const V2*>(&x.packed));
+        m.packed = *reinterpret_cast<const uint32_t*>(&y);
+      } else {
+        m.mn = fminf(m.mn, x.mn);
+        m.nmx = fminf(m.nmx, x.nmx);
+      }
+    };
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      if (have[k]) fold(cache[k]);
+    }
+    for (int64_t j = tir + static_cast<int64_t>(K) * TPR; valid && j < nvec; j += TPR) fold(load_raw8<SrcT>(row + j * 8));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
+    if (lane == 0) {
+      red16[warp_in_block] = m.packed;
+      red_mn[warp_in_block] = m.mn;
+      red_nmx[warp_in_block] = m.nmx;
+    }
+    __syncthreads();
+    float mn, mx;
+    {
+      MinNegMax t;
+      t.packed = red16[first_warp];
+      t.mn = red_mn[first_warp];
+      t.nmx = red_nmx[first_warp];
+#pragma unroll
+      for (int w = 1; w < WPR; ++w) {
+        if constexpr (sizeof(SrcT) == 2) {
+          using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
+          const uint32_t o = red16[first_warp + w];
+          const V2 y = __hmin2(*reinterpret_cast<const V2*>(&t.packed), *reinterpret_cast<const V2*>(&o));
+          t.packed = *reinterpret_cast<const uint32_t*>(&y);
+        } else {
+          t.mn = fminf(t.mn, red_mn[first_warp + w]);
+          t.nmx = fminf(t.nmx, red_nmx[first_warp + w]);
+        }
+      }
+      finish_minmax<SrcT>(t, mn, mx);
+    }
+    float s, zp;
+    int_params<MODE>(mn, mx, s, zp);
+    const float r = __frcp_rn(s);
+    const bool exact = divisor_exact(s);  // uniform over the row; rows of a warp may differ only if TPR < 32
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      if (have[k]) {
+        const int64_t j = tir + static_cast<int64_t>(k) * TPR;
+        float2 x[4];
+        unpack8_pairs(cache[k], x);
+        const uint2 w = exact ? encode8_int<MODE, true>(x, s, r, zp) : encode8_int<MODE, false>(x, s, r, zp);
+        const int64_t e0 = g * row_len + j * 8;
+        if constexpr (mode_bits(MODE) == 4) {
+          __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
+        } else {
+          __stcs(reinterpret_cast<uint2*>(T.codes + e0), w);
+        }
+      }
+    }
+    for (int64_t j = tir + static_cast<int64_t>(K) * TPR; valid && j < nvec; j += TPR) {
+      float2 x[4];
+      unpack8_pairs(load_raw8<SrcT>(row + j * 8), x);
+      const uint2 w = exact ? encode8_int<MODE, true>(x, s, r, zp) : encode8_int<MODE, false>(x, s, r, zp);
+      const int64_t e0 = g * row_len + j * 8;
+      if constexpr (mode_bits(MODE) == 4) {
+        __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
+      } else {
+        __stcs(reinterpret_cast<uint2*>(T.codes + e0), w);
+      }
+    }
+    if (valid && tir == 0) {
+      T.scale[g] = s;
+      if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
+      if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+    }
+    __syncthreads();  // red* reused by the next iteration
+  }
+}
+
+}  // namespace nncfb

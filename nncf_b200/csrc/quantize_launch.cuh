@@ -4,6 +4,7 @@
 
 #include <algorithm>
 
+#include "quantize_fast.cuh"
 #include "quantize_kernels.cuh"
 
 namespace nncfb {
@@ -85,7 +86,90 @@ int launch_quantize_t(const QArgs& a, int mode, QuantPath path, cudaStream_t str
   return NNCFB_E_BAD_ARG;
 }
 
+// ---- fast batched path -----------------------------------------------------------------------------
+// Shape class of a batch: every tensor of a batch shares it.
+struct FastClass {
+  int kind;         // 0: not eligible, 1: row groups, 2: per channel
+  int64_t group;    // group size (kind 1) or row length (kind 2)
+  bool operator==(const FastClass& o) const { return kind == o.kind && group == o.group; }
+};
+
+inline FastClass fast_class(const nncfb_quantize_args& p) {
+  FastClass none{0, 0};
+  if (!mode_is_integer(p.mode) || p.inner != 1 || p.pre_scale || p.pre_zp || p.values_out || p.dq_out ||
+      p.sqerr_out || p.scale_e8m0_out || !p.scale_out || !p.codes_out)
+    return none;
+  if (mode_is_asym(p.mode) && !p.zp_out) return none;
+  const bool four = mode_bits(p.mode) == 4;
+  if (p.codes_format != (four ? NNCFB_CODES_NIBBLE : NNCFB_CODES_BYTE)) return none;
+  if (!aligned16(p.weight) || !aligned16(p.codes_out)) return none;
+  if (p.group_size == 128 || p.group_size == 64 || p.group_size == 32) return FastClass{1, p.group_size};
+  if (p.group_size == p.reduce && p.reduce % 8 == 0 && p.reduce >= 512) return FastClass{2, p.reduce};
+  return none;
+}
+
+template <typename SrcT, int MODE>
+int launch_fast_mode(const FastBatch& b, FastClass cls, cudaStream_t stream) {
+  const int sms = sm_count();
+  if (cls.kind == 1) {
+    constexpr int U = 2;
+    const int grid = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>((b.iter_start[b.n_tensors] + 7) / 8, static_cast<int64_t>(sms) * 4)));
+    if (cls.group == 128) {
+      quant_rows_batch_kernel<SrcT, MODE, 8, 2, U><<<grid, 256, 0, stream>>>(b);
+    } else if (cls.group == 64) {
+      quant_rows_batch_kernel<SrcT, MODE, 4, 2, U><<<grid, 256, 0, stream>>>(b);
+    } else {
+      quant_rows_batch_kernel<SrcT, MODE, 4, 1, U><<<grid, 256, 0, stream>>>(b);
+    }
+  } else {
+    const int grid = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>(b.iter_start[b.n_tensors], static_cast<int64_t>(sms) * 3)));
+    const int64_t nvec = cls.group / 8;
+    constexpr int K = WideCache<SrcT>::K;
+    if (nvec <= 64 * K) {
+      quant_channel_batch_kernel<SrcT, MODE, 64><<<grid, 256, 0, stream>>>(b, cls.group);
+    } else if (nvec <= 128 * K) {
+      quant_channel_batch_kernel<SrcT, MODE, 128><<<grid, 256, 0, stream>>>(b, cls.group);
+    } else {
+      quant_channel_batch_kernel<SrcT, MODE, 256><<<grid, 256, 0, stream>>>(b, cls.group);
+    }
+  }
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+template <typename SrcT>
+int launch_fast_t(const FastBatch& b, int mode, FastClass cls, cudaStream_t stream) {
+  switch (mode) {
+    case NNCFB_INT8_SYM: return launch_fast_mode<SrcT, NNCFB_INT8_SYM>(b, cls, stream);
+    case NNCFB_INT8_ASYM: return launch_fast_mode<SrcT, NNCFB_INT8_ASYM>(b, cls, stream);
+    case NNCFB_INT4_SYM: return launch_fast_mode<SrcT, NNCFB_INT4_SYM>(b, cls, stream);
+    case NNCFB_INT4_ASYM: return launch_fast_mode<SrcT, NNCFB_INT4_ASYM>(b, cls, stream);
+    default: break;
+  }
+  set_error("fast path: unsupported mode %d", mode);
+  return NNCFB_E_UNSUPPORTED;
+}
+
+// iterations one tensor contributes to a batch of class `cls`
+inline int64_t fast_iterations(const FastClass& cls, int64_t n_groups, size_t elem_size) {
+  if (cls.kind == 1) {
+    const int L = cls.group == 128 ? 8 : 4;
+    const int64_t per_iter = (32 / L) * 2;  // GPW * U
+    return (n_groups + per_iter - 1) / per_iter;
+  }
+  const int K = elem_size == 4 ? 4 : 8;
+  const int64_t nvec = cls.group / 8;
+  const int tpr = nvec <= 64 * K ? 64 : (nvec <= 128 * K ? 128 : 256);
+  const int rpb = 256 / tpr;
+  return (n_groups + rpb - 1) / rpb;
+}
+
 // defined in quantize_f32.cu / quantize_f16.cu / quantize_bf16.cu
+int launch_fast_f32(const FastBatch& b, int mode, FastClass cls, cudaStream_t stream);
+int launch_fast_f16(const FastBatch& b, int mode, FastClass cls, cudaStream_t stream);
+int launch_fast_bf16(const FastBatch& b, int mode, FastClass cls, cudaStream_t stream);
 int launch_quantize_f32(const QArgs& a, int mode, QuantPath path, cudaStream_t stream);
 int launch_quantize_f16(const QArgs& a, int mode, QuantPath path, cudaStream_t stream);
 int launch_quantize_bf16(const QArgs& a, int mode, QuantPath path, cudaStream_t stream);

@@ -97,6 +97,7 @@ class CompressionPlan:
             self.items.append(PlanItem(name, weight, config, axis % weight.ndim))
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._fp16_scales = fp16_scales
+        self._arg_arrays: dict = {}
         for item in self.items:
             self._resolve(item)
 
@@ -138,12 +139,13 @@ class CompressionPlan:
     def launch(self, subset: Optional[Sequence[int]] = None) -> None:
         """Enqueue the kernels on the current stream (no synchronisation)."""
         stream = _lib.stream_handle(self.device)
-        fn = _lib.lib.nncfb_quantize
-        items = self.items if subset is None else [self.items[i] for i in subset]
-        for item in items:
-            rc = fn(item.args, stream)
-            if rc != 0:
-                _lib.check(rc)
+        key = None if subset is None else tuple(subset)
+        arr = self._arg_arrays.get(key)
+        if arr is None:
+            items = self.items if subset is None else [self.items[i] for i in subset]
+            arr = (_lib.QuantizeArgs * len(items))(*[it.args for it in items])
+            self._arg_arrays[key] = arr
+        _lib.check(_lib.lib.nncfb_quantize_batch(arr, len(arr), stream))
 
     def capture(self, subset: Optional[Sequence[int]] = None) -> torch.cuda.CUDAGraph:
         """Capture the launches in a CUDA graph (the launch-bound loop becomes one replay)."""
