@@ -180,7 +180,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a graph")
     ap.add_argument("--profile-case", action="store_true",
-                    help="small case for profilers: 4 decoder matrices, no e2e / cpu arm, 1 warm-up, 1 step")
+                    help="small case for profilers: one decoder layer, no e2e / cpu arm, 1 warm-up, 1 step")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -203,7 +203,7 @@ def main():
 
     items = build_weight_set(device, seed=1 + rank)
     if args.profile_case:
-        items = items[1:5]
+        items = items[1:8]  # one decoder layer: 436 MB of weights, larger than L2
         args.steps, args.no_e2e, args.no_cpu_baseline = 1, True, True
     plan = CompressionPlan(items, device)
     idx4 = [i for i, it in enumerate(plan.items) if it.config.num_bits == 4]
@@ -316,7 +316,7 @@ def main():
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD if not args.profile_case else "profile case: 4 decoder matrices",
+        "config": {"workload": WORKLOAD if not args.profile_case else "profile case: one decoder layer (7 matrices, 436 MB)",
                    "per_rank_source_bytes": src_bytes, "launch": "per-call" if (args.no_graph or args.profile_case) else "cuda-graph replay",
                    "l2": "inputs (16 GB per step) exceed L2 (126 MB); no flush needed",
                    "seed": "1 + rank", "distribution": "N(0, 0.02^2) bf16"},

@@ -121,7 +121,8 @@ __device__ __forceinline__ void unpack8_pairs(const Raw8<float>& x, float2 (&v)[
 __device__ __forceinline__ void unpack8_pairs(const Raw8<__nv_bfloat16>& x, float2 (&v)[4]) {
   const uint32_t w[4] = {x.r.x, x.r.y, x.r.z, x.r.w};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] = f2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  // low half by an integer multiply (FMA pipe) rather than a shift: the ALU pipe is the busy one
+  for (int i = 0; i < 4; ++i) v[i] = f2(__uint_as_float(w[i] * 65536u), __uint_as_float(w[i] & 0xffff0000u));
 }
 __device__ __forceinline__ void unpack8_pairs(const Raw8<__half>& x, float2 (&v)[4]) {
   const uint32_t w[4] = {x.r.x, x.r.y, x.r.z, x.r.w};
@@ -133,7 +134,10 @@ __device__ __forceinline__ void unpack8_pairs(const Raw8<__half>& x, float2 (&v)
 //   NIB: returns one word of 8 nibbles (INT4_SYM with the +8 storage offset);
 //   else: returns two words of 4 bytes (signed modes as two's complement).
 // EXACT selects the multiply/FMA division (divisor in the exact range) or the IEEE division.
-template <int MODE, bool EXACT>
+// CLAMP: 2 = clip to [low, high]; 1 = upper bound only; 0 = no clip.  The caller proves per group
+// which bounds a quotient can cross (see int_params); every skipped bound saves one instruction per
+// element on the busiest (ALU) pipe.
+template <int MODE, bool EXACT, int CLAMP>
 __device__ __forceinline__ uint2 encode8_int(const float2 (&v)[4], float s, float r, float zp) {
   constexpr bool kAsym = mode_is_asym(MODE);
   constexpr int kBits = mode_bits(MODE);
@@ -154,8 +158,13 @@ __device__ __forceinline__ uint2 encode8_int(const float2 (&v)[4], float s, floa
     }
     if constexpr (kAsym) q = __fadd2_rn(q, zp2);  // separate fp32 add, as the reference does
     // clamp-then-round equals round-then-clamp for integer bounds
-    q.x = fmaxf(fminf(q.x, kHigh), kLow);
-    q.y = fmaxf(fminf(q.y, kHigh), kLow);
+    if constexpr (CLAMP == 2) {
+      q.x = fmaxf(fminf(q.x, kHigh), kLow);
+      q.y = fmaxf(fminf(q.y, kHigh), kLow);
+    } else if constexpr (CLAMP == 1) {
+      q.x = fminf(q.x, kHigh);
+      q.y = fminf(q.y, kHigh);
+    }
     const float2 t = __fadd2_rn(q, magic2);  // round half to even into the low mantissa bits
     bits[2 * i] = __float_as_uint(t.x);
     bits[2 * i + 1] = __float_as_uint(t.y);
@@ -186,15 +195,31 @@ __device__ __forceinline__ uint2 encode8_int(const float2 (&v)[4], float s, floa
   return out;
 }
 
+// Scale and zero point of a group plus `need_clamp`: false only when every quotient of the group
+// provably rounds into the code range, so that the clip of WC/weight_lowering.py:682 is a no-op.
+//   symmetric: |w| <= 2^(b-1) |s| always (s = m / 2^(b-1) exactly), so codes lie in
+//     [-2^(b-1), 2^(b-1)]: the lower bound never binds, the upper one does whenever the weaker
+//     extreme is within half a step of the stronger one, so it is always applied (need_clamp only
+//     reports non-finite scales);
+//   asymmetric: with an unclipped zero point, q + zp lies in [-0.5, levels - 1 + f + 2e-4] where
+//     f = min/s - round(min/s); the top rounds out of range only if f is within ~1e-4 of 0.5.
 template <int MODE>
-__device__ __forceinline__ void int_params(float mn, float mx, float& s, float& zp) {
+__device__ __forceinline__ void int_params(float mn, float mx, float& s, float& zp, bool& need_clamp) {
+  constexpr int kBits = mode_bits(MODE);
   if constexpr (mode_is_asym(MODE)) {
-    const GroupParams p = asym_params<mode_bits(MODE)>(mn, mx);
-    s = p.scale;
-    zp = p.zp;
+    constexpr int kHigh = (1 << kBits) - 1;
+    s = __fdiv_rn(__fsub_rn(mx, mn), static_cast<float>(kHigh));
+    s = (fabsf(s) < kEps32) ? kEps32 : s;
+    const float qm = __fdiv_rn(mn, s);
+    const float rq = rintf(qm);
+    const float z = __fsub_rn(0.0f, rq);
+    const float zc = fminf(fmaxf(z, 0.0f), static_cast<float>(kHigh));
+    zp = zc + 0.0f;  // -0 -> +0
+    need_clamp = !(zc == z) || !(__fsub_rn(qm, rq) < 0.49f);
   } else {
-    s = signed_scale<mode_bits(MODE)>(mn, mx);
+    s = signed_scale<kBits>(mn, mx);
     zp = 0.0f;
+    need_clamp = !(fabsf(s) < 3.0e38f);
   }
 }
 
@@ -217,13 +242,10 @@ __global__ void __launch_bounds__(256, 4) quant_rows_batch_kernel(const __grid_c
   const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t total_iters = b.iter_start[b.n_tensors];
+  int lo = 0;  // tensor of the current iteration; iterations only move forward
 
   for (int64_t it = warp; it < total_iters; it += n_warps) {
-    int lo = 0, hi = b.n_tensors;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (b.iter_start[mid] <= it) lo = mid; else hi = mid;
-    }
+    while (b.iter_start[lo + 1] <= it) ++lo;
     const FastTensor& T = b.t[lo];
     const SrcT* __restrict__ src = reinterpret_cast<const SrcT*>(T.weight);
     const int64_t n_groups = T.n_groups;
@@ -246,15 +268,21 @@ __global__ void __launch_bounds__(256, 4) quant_rows_batch_kernel(const __grid_c
 #pragma unroll
       for (int o = L / 2; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
       float mn, mx, s, zp;
+      bool need_clamp;
       finish_minmax<SrcT>(m, mn, mx);
-      int_params<MODE>(mn, mx, s, zp);
+      int_params<MODE>(mn, mx, s, zp, need_clamp);
       const float r = __frcp_rn(s);
       const bool exact = __all_sync(0xffffffffu, divisor_exact(s));
+      const bool clamp = __any_sync(0xffffffffu, need_clamp);
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
         float2 x[4];
         unpack8_pairs(raw[p][v], x);
-        const uint2 w = exact ? encode8_int<MODE, true>(x, s, r, zp) : encode8_int<MODE, false>(x, s, r, zp);
+        uint2 w;
+        constexpr int kLight = mode_is_asym(MODE) ? 0 : 1;
+        if (!exact) w = encode8_int<MODE, false, 2>(x, s, r, zp);
+        else if (clamp) w = encode8_int<MODE, true, 2>(x, s, r, zp);
+        else w = encode8_int<MODE, true, kLight>(x, s, r, zp);
         if (valid) {
           const int64_t e0 = g * GS + (lig + v * L) * 8;
           if constexpr (mode_bits(MODE) == 4) {
@@ -293,12 +321,9 @@ __global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __gri
   const int64_t nvec = row_len >> 3;
   const int64_t total_iters = b.iter_start[b.n_tensors];  // iterations of RPB rows
 
+  int lo = 0;
   for (int64_t it = blockIdx.x; it < total_iters; it += gridDim.x) {
-    int lo = 0, hi = b.n_tensors;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (b.iter_start[mid] <= it) lo = mid; else hi = mid;
-    }
+    while (b.iter_start[lo + 1] <= it) ++lo;
     const FastTensor& T = b.t[lo];
     const int64_t g = (it - b.iter_start[lo]) * RPB + rib;
     const bool valid = g < T.n_groups;
@@ -366,16 +391,23 @@ __global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __gri
       finish_minmax<SrcT>(t, mn, mx);
     }
     float s, zp;
-    int_params<MODE>(mn, mx, s, zp);
+    bool clamp;
+    int_params<MODE>(mn, mx, s, zp, clamp);
     const float r = __frcp_rn(s);
-    const bool exact = divisor_exact(s);  // uniform over the row; rows of a warp may differ only if TPR < 32
+    const bool exact = divisor_exact(s);  // uniform over the row, hence over the warp (TPR >= 32)
+    auto encode = [&](const float2 (&x)[4]) -> uint2 {
+      constexpr int kLight = mode_is_asym(MODE) ? 0 : 1;
+      if (!exact) return encode8_int<MODE, false, 2>(x, s, r, zp);
+      if (clamp) return encode8_int<MODE, true, 2>(x, s, r, zp);
+      return encode8_int<MODE, true, kLight>(x, s, r, zp);
+    };
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (have[k]) {
         const int64_t j = tir + static_cast<int64_t>(k) * TPR;
         float2 x[4];
         unpack8_pairs(cache[k], x);
-        const uint2 w = exact ? encode8_int<MODE, true>(x, s, r, zp) : encode8_int<MODE, false>(x, s, r, zp);
+        const uint2 w = encode(x);
         const int64_t e0 = g * row_len + j * 8;
         if constexpr (mode_bits(MODE) == 4) {
           __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
@@ -387,7 +419,7 @@ __global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __gri
     for (int64_t j = tir + static_cast<int64_t>(K) * TPR; valid && j < nvec; j += TPR) {
       float2 x[4];
       unpack8_pairs(load_raw8<SrcT>(row + j * 8), x);
-      const uint2 w = exact ? encode8_int<MODE, true>(x, s, r, zp) : encode8_int<MODE, false>(x, s, r, zp);
+      const uint2 w = encode(x);
       const int64_t e0 = g * row_len + j * 8;
       if constexpr (mode_bits(MODE) == 4) {
         __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
