@@ -91,6 +91,26 @@ __global__ void __launch_bounds__(256) division_selftest_kernel(int64_t n, uint6
     const float q = div_by(w, dv);
     const float ref = __fdiv_rn(w, sdiv);
     if (__float_as_uint(q) != __float_as_uint(ref)) ++bad;
+    // The batched kernels use the multiply/FMA sequence without a range check, for scales in
+    // [2^-23, 2^125] (a computed scale is never below eps).  Check it over that whole range
+    // wherever the quotient is finite and not vanishingly small.
+    const uint64_t r3 = splitmix64(s);
+    const uint32_t se2 = 104u + static_cast<uint32_t>((r3 >> 40) % 149u);  // 2^-23 .. 2^125
+    const float s2 = __uint_as_float((static_cast<uint32_t>(r3) & 0x007fffffu) | (se2 << 23));
+    const int we2 = static_cast<int>(se2) - 30 + static_cast<int>((r3 >> 48) % 50u);  // quotient 2^-30 .. 2^19
+    if (we2 > 0 && we2 < 255) {
+      float w2 = __uint_as_float((static_cast<uint32_t>(r3 >> 9) & 0x807fffffu) | (static_cast<uint32_t>(we2) << 23));
+      if (r3 & 1u) {  // land next to a rounding tie of the quotient
+        const float k = static_cast<float>(static_cast<int>((r3 >> 20) % 512u) - 256) + 0.5f;
+        w2 = __uint_as_float(__float_as_uint(__fmul_rn(k, s2)) + static_cast<int>((r3 >> 30) % 9u) - 4);
+      }
+      const float rr = __frcp_rn(s2);
+      const float q0 = __fmul_rn(w2, rr);
+      const float e = __fmaf_rn(-s2, q0, w2);
+      const float q2 = __fmaf_rn(e, rr, q0);
+      const float ref2 = __fdiv_rn(w2, s2);
+      if (isfinite(ref2) && isfinite(w2) && __float_as_uint(q2) != __float_as_uint(ref2)) ++bad;
+    }
   }
   if (bad) atomicAdd(mismatches, bad);
 }

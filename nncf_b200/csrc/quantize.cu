@@ -27,8 +27,10 @@ int launch_fast_run(const nncfb_quantize_args* items, int n, FastClass cls, cuda
     batch.iter_start[i + 1] = batch.iter_start[i] + fast_iterations(cls, t.n_groups, esz);
   }
   switch (items[0].weight_dtype) {
+#ifndef NNCFB_ONLY_BF16  // tuning builds link the bf16 kernels only
     case NNCFB_F32: return launch_fast_f32(batch, items[0].mode, cls, st);
     case NNCFB_F16: return launch_fast_f16(batch, items[0].mode, cls, st);
+#endif
     default: return launch_fast_bf16(batch, items[0].mode, cls, st);
   }
 }
@@ -145,8 +147,10 @@ int launch_general(const nncfb_quantize_args* p, cudaStream_t st) {
                        aligned16(p->dq_out);
   const QuantPath path = choose_path(p->group_size, p->inner, aligned);
   switch (p->weight_dtype) {
+#ifndef NNCFB_ONLY_BF16
     case NNCFB_F32: return launch_quantize_f32(a, p->mode, path, st);
     case NNCFB_F16: return launch_quantize_f16(a, p->mode, path, st);
+#endif
     default: return launch_quantize_bf16(a, p->mode, path, st);
   }
 }

@@ -133,11 +133,13 @@ __device__ __forceinline__ void unpack8_pairs(const Raw8<__half>& x, float2 (&v)
 // Integer codes of 8 elements as Horner-packed bit patterns.
 //   NIB: returns one word of 8 nibbles (INT4_SYM with the +8 storage offset);
 //   else: returns two words of 4 bytes (signed modes as two's complement).
-// EXACT selects the multiply/FMA division (divisor in the exact range) or the IEEE division.
+// The division is the multiply/FMA sequence of `Divisor`: in these kernels the scale is computed
+// from the data, so it lies in [eps, 2^125], where the sequence equals the IEEE quotient whenever
+// the quotient can decide a code (see exact_quotient).
 // CLAMP: 2 = clip to [low, high]; 1 = upper bound only; 0 = no clip.  The caller proves per group
 // which bounds a quotient can cross (see int_params); every skipped bound saves one instruction per
 // element on the busiest (ALU) pipe.
-template <int MODE, bool EXACT, int CLAMP>
+template <int MODE, int CLAMP>
 __device__ __forceinline__ uint2 encode8_int(const float2 (&v)[4], float s, float r, float zp) {
   constexpr bool kAsym = mode_is_asym(MODE);
   constexpr int kBits = mode_bits(MODE);
@@ -148,14 +150,9 @@ __device__ __forceinline__ uint2 encode8_int(const float2 (&v)[4], float s, floa
   uint32_t bits[8];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 q;
-    if constexpr (EXACT) {
-      const float2 q0 = __fmul2_rn(v[i], r2);
-      const float2 e = __ffma2_rn(ns2, q0, v[i]);
-      q = __ffma2_rn(e, r2, q0);
-    } else {
-      q = f2(__fdiv_rn(v[i].x, s), __fdiv_rn(v[i].y, s));
-    }
+    const float2 q0 = __fmul2_rn(v[i], r2);
+    const float2 e = __ffma2_rn(ns2, q0, v[i]);
+    float2 q = __ffma2_rn(e, r2, q0);
     if constexpr (kAsym) q = __fadd2_rn(q, zp2);  // separate fp32 add, as the reference does
     // clamp-then-round equals round-then-clamp for integer bounds
     if constexpr (CLAMP == 2) {
@@ -203,29 +200,41 @@ __device__ __forceinline__ uint2 encode8_int(const float2 (&v)[4], float s, floa
 //     reports non-finite scales);
 //   asymmetric: with an unclipped zero point, q + zp lies in [-0.5, levels - 1 + f + 2e-4] where
 //     f = min/s - round(min/s); the top rounds out of range only if f is within ~1e-4 of 0.5.
+// RN(a / b) for a divisor b whose correctly rounded reciprocal rb is known (Markstein): exact when
+// nothing under/overflows, which holds for b in [2^-23, 2^125] and |a / b| >= 2^-80; smaller
+// quotients are off by at most an ulp of a number that rounds to code 0 anyway, and quotients that
+// overflow give NaN instead of inf, which the clip maps to the same bound.
+__device__ __forceinline__ float exact_quotient(float a, float b, float rb) {
+  const float q0 = __fmul_rn(a, rb);
+  const float e = __fmaf_rn(-b, q0, a);
+  return __fmaf_rn(e, rb, q0);
+}
+
 template <int MODE>
-__device__ __forceinline__ void int_params(float mn, float mx, float& s, float& zp, bool& need_clamp) {
+__device__ __forceinline__ void int_params(float mn, float mx, float& s, float& r, float& zp, bool& need_clamp) {
   constexpr int kBits = mode_bits(MODE);
   if constexpr (mode_is_asym(MODE)) {
     constexpr int kHigh = (1 << kBits) - 1;
-    s = __fdiv_rn(__fsub_rn(mx, mn), static_cast<float>(kHigh));
+    constexpr float kLevels = static_cast<float>(kHigh);
+    constexpr float kRcpLevels = 1.0f / kLevels;  // correctly rounded at compile time
+    s = exact_quotient(__fsub_rn(mx, mn), kLevels, kRcpLevels);
     s = (fabsf(s) < kEps32) ? kEps32 : s;
-    const float qm = __fdiv_rn(mn, s);
+    r = __frcp_rn(s);
+    const float qm = exact_quotient(mn, s, r);
     const float rq = rintf(qm);
     const float z = __fsub_rn(0.0f, rq);
-    const float zc = fminf(fmaxf(z, 0.0f), static_cast<float>(kHigh));
+    const float zc = fminf(fmaxf(z, 0.0f), kLevels);
     zp = zc + 0.0f;  // -0 -> +0
     need_clamp = !(zc == z) || !(__fsub_rn(qm, rq) < 0.49f);
   } else {
-    s = signed_scale<kBits>(mn, mx);
+    // where(|min| >= max, |min|, -max) / 2^(b-1): the division by a power of two is a multiply
+    const float amin = fabsf(mn);
+    s = ((amin >= mx) ? amin : -mx) * (1.0f / static_cast<float>(1 << (kBits - 1)));
+    s = (fabsf(s) < kEps32) ? kEps32 : s;
+    r = __frcp_rn(s);
     zp = 0.0f;
-    need_clamp = !(fabsf(s) < 3.0e38f);
+    need_clamp = false;  // the upper bound is always applied, the lower one never binds
   }
-}
-
-__device__ __forceinline__ bool divisor_exact(float s) {
-  const uint32_t e = (__float_as_uint(s) >> 23) & 0xffu;
-  return (e >= 127u - 40u) && (e <= 127u + 40u);
 }
 
 // =====================================================================================================
@@ -267,22 +276,22 @@ __global__ void __launch_bounds__(256, 4) quant_rows_batch_kernel(const __grid_c
       MinNegMax m = min_negmax<SrcT, VPL>(raw[p]);
 #pragma unroll
       for (int o = L / 2; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
-      float mn, mx, s, zp;
+      float mn, mx, s, r, zp;
       bool need_clamp;
       finish_minmax<SrcT>(m, mn, mx);
-      int_params<MODE>(mn, mx, s, zp, need_clamp);
-      const float r = __frcp_rn(s);
-      const bool exact = __all_sync(0xffffffffu, divisor_exact(s));
-      const bool clamp = __any_sync(0xffffffffu, need_clamp);
+      int_params<MODE>(mn, mx, s, r, zp, need_clamp);
+      bool clamp = false;
+      if constexpr (mode_is_asym(MODE)) clamp = __any_sync(0xffffffffu, need_clamp);
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
         float2 x[4];
         unpack8_pairs(raw[p][v], x);
         uint2 w;
-        constexpr int kLight = mode_is_asym(MODE) ? 0 : 1;
-        if (!exact) w = encode8_int<MODE, false, 2>(x, s, r, zp);
-        else if (clamp) w = encode8_int<MODE, true, 2>(x, s, r, zp);
-        else w = encode8_int<MODE, true, kLight>(x, s, r, zp);
+        if constexpr (mode_is_asym(MODE)) {
+          w = clamp ? encode8_int<MODE, 2>(x, s, r, zp) : encode8_int<MODE, 0>(x, s, r, zp);
+        } else {
+          w = encode8_int<MODE, 1>(x, s, r, zp);
+        }
         if (valid) {
           const int64_t e0 = g * GS + (lig + v * L) * 8;
           if constexpr (mode_bits(MODE) == 4) {
@@ -390,16 +399,15 @@ __global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __gri
       }
       finish_minmax<SrcT>(t, mn, mx);
     }
-    float s, zp;
-    bool clamp;
-    int_params<MODE>(mn, mx, s, zp, clamp);
-    const float r = __frcp_rn(s);
-    const bool exact = divisor_exact(s);  // uniform over the row, hence over the warp (TPR >= 32)
+    float s, r, zp;
+    bool clamp;  // uniform over the row, hence over the warp (TPR >= 32)
+    int_params<MODE>(mn, mx, s, r, zp, clamp);
     auto encode = [&](const float2 (&x)[4]) -> uint2 {
-      constexpr int kLight = mode_is_asym(MODE) ? 0 : 1;
-      if (!exact) return encode8_int<MODE, false, 2>(x, s, r, zp);
-      if (clamp) return encode8_int<MODE, true, 2>(x, s, r, zp);
-      return encode8_int<MODE, true, kLight>(x, s, r, zp);
+      if constexpr (mode_is_asym(MODE)) {
+        return clamp ? encode8_int<MODE, 2>(x, s, r, zp) : encode8_int<MODE, 0>(x, s, r, zp);
+      } else {
+        return encode8_int<MODE, 1>(x, s, r, zp);
+      }
     };
 #pragma unroll
     for (int k = 0; k < K; ++k) {
