@@ -117,6 +117,60 @@ int nncfb_quantize(const nncfb_quantize_args* args, void* stream);
 int nncfb_quantize_batch(const nncfb_quantize_args* items, int32_t n, void* stream);
 
 /*
+ * ScaleEstimation: refined per-group scales for a weight [rows, cols] (groups of `group_size`
+ * consecutive columns) from the activation statistics of its input:
+ *   importance [cols]        max |X| over the calibration samples (fp32)
+ *   x          [cols, n]     per-sample channel means, fp32, row-major (n <= 256)
+ * One warp runs the whole sweep of a (row, group): baseline quantisation, `initial_steps`
+ * rectifications and `scale_steps` grid points, each scored by mean_n ((W_g - Q_g) X_g)^2
+ * (+ weight_penalty * mean (Q - W)^2 when weight_penalty > 0).  Outputs: scale_out fp32 [rows, G],
+ * zp_out int32 [rows, G] (asymmetric modes; the zero point of the baseline quantisation).
+ * Limits: group_size <= 512 and group_size x n small enough for 200 KiB of shared memory.
+ * Replaces WC/scale_estimation.py:160-409 (ScaleEstimation.calculate_quantization_params after
+ * process_stats, estimate_scales, get_target_zero_mask).
+ */
+int nncfb_scale_estimation(const void* weight, int32_t weight_dtype, int64_t rows, int64_t cols, int64_t group_size,
+                           int32_t mode, const float* importance, const float* x, int32_t n_samples,
+                           int32_t initial_steps, int32_t scale_steps, float weight_penalty, float* scale_out,
+                           int32_t* zp_out, void* stream);
+
+/*
+ * AWQ alpha grid search for `n_groups` groups of a weight [rows, cols]:
+ *   group_index [n_groups]      device int32, group number (column offset / group_size)
+ *   group_scale [n_groups, gs]  device fp32, activation magnitudes of the group clipped to
+ *                               [quantile(0.1), 100] (WC/awq.py:302-304)
+ *   x           [cols, n]       device fp32 per-sample channel means
+ *   alphas      [n_alpha]       device fp32 grid (alpha_min + k * step, accumulated like the reference)
+ *   prev_w      [cols] or NULL  mean |weight| per channel of the layer the scale is merged into, with
+ *                               prev_s = max activation magnitude of that layer, prev_rdim = its
+ *                               reduction size and threshold = 0.25 * 65504 (fp16 overflow guard)
+ *   scale_io    [cols]          device fp32, holds 1.0 on entry; columns of groups for which a better
+ *                               alpha exists receive s^alpha
+ * `workspace` is caller-provided scratch of nncfb_awq_workspace_bytes() bytes (per-block partial
+ * sums; contents need not be initialised).  Replaces WC/awq.py:243-361 (AWQ._data_aware_step,
+ * _clamp_scale).
+ */
+size_t nncfb_awq_workspace_bytes(int64_t rows, int32_t n_groups, int32_t n_alpha);
+int nncfb_awq_search(const void* weight, int32_t weight_dtype, int64_t rows, int64_t cols, int32_t mode,
+                     int64_t group_size, const int32_t* group_index, int32_t n_groups, const float* group_scale,
+                     const float* x, int32_t n_samples, const float* alphas, int32_t n_alpha, const float* prev_w,
+                     float prev_s, float prev_rdim, float threshold, float* scale_io, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/*
+ * Per-channel statistics of an activation [tokens, channels] (channel last) in one pass; every
+ * output is optional (NULL):
+ *   mean_out    [channels] in the activation's dtype (fp32 accumulate, one rounding)
+ *   var_out     [channels] fp32 population variance
+ *   absmax_out  [channels] fp32 max |x|
+ *   sumsq_out   [channels] fp64 sum of squares
+ * Replaces src/nncf/common/tensor_statistics/collectors.py:512-540 (MeanReducer,
+ * MeanVarianceReducer, MaxVarianceReducer, MeanAbsMaxReducer) and :924-936 (HAWQ trace input).
+ */
+int nncfb_channel_stats(const void* x, int32_t dtype, int64_t tokens, int64_t channels, void* mean_out, float* var_out,
+                        float* absmax_out, double* sumsq_out, void* stream);
+
+/*
  * Nibble-pack n byte codes (n even) in flat order: out[i] = (in[2i] & 15) | (in[2i+1] << 4);
  * `add` is added to every code first (8 for signed int4 codes).
  * Replaces src/nncf/torch/quantization/quantize_functions.py:417-461 pack_uint4 / pack_int4.

@@ -58,6 +58,11 @@ def _load() -> C.CDLL:
         "nncfb_last_error": ([], C.c_char_p),
         "nncfb_quantize": ([C.POINTER(QuantizeArgs), vp], C.c_int),
         "nncfb_quantize_batch": ([C.POINTER(QuantizeArgs), i32, vp], C.c_int),
+        "nncfb_scale_estimation": ([vp, i32, i64, i64, i64, i32, vp, vp, i32, i32, i32, C.c_float, vp, vp, vp], C.c_int),
+        "nncfb_awq_workspace_bytes": ([i64, i32, i32], C.c_size_t),
+        "nncfb_awq_search": ([vp, i32, i64, i64, i32, i64, vp, i32, vp, vp, i32, vp, i32, vp, C.c_float, C.c_float,
+                              C.c_float, vp, vp, C.c_size_t, vp], C.c_int),
+        "nncfb_channel_stats": ([vp, i32, i64, i64, vp, vp, vp, vp, vp], C.c_int),
         "nncfb_pack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_unpack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_selftest_division": ([i64, u64, vp, vp], C.c_int),
@@ -70,7 +75,9 @@ def _load() -> C.CDLL:
 
 
 lib = _load()
-EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_quantize_batch", "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
+EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_quantize_batch",
+            "nncfb_scale_estimation", "nncfb_awq_workspace_bytes", "nncfb_awq_search", "nncfb_channel_stats",
+            "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
             "nncfb_selftest_division"]
 
 
