@@ -147,7 +147,8 @@ def test_channel_stats_match_reference_golden(dtype):
     st = channel_stats(x, -1, ("var", "absmax", "sumsq"))
     assert float(st["var"].mean()) == pytest.approx(float(g[key + "/mean_var"]), rel=5e-3)
     assert float(st["var"].max()) == pytest.approx(float(g[key + "/max_var"]), rel=5e-3)
-    assert float(st["absmax"].mean()) == pytest.approx(float(g[key + "/mean_abs_max"]), rel=1e-6)
+    # the reference averages the per-channel maxima in the activation's dtype
+    assert float(st["absmax"].mean()) == pytest.approx(float(g[key + "/mean_abs_max"]), rel=max(tol, 1e-6))
     assert float(st["sumsq"].sum()) == pytest.approx(float(g[key + "/sumsq"]), rel=1e-9)
 
 
