@@ -158,6 +158,37 @@ int nncfb_awq_search(const void* weight, int32_t weight_dtype, int64_t rows, int
                      size_t workspace_bytes, void* stream);
 
 /*
+ * GPTQ Hessian accumulation: hessian [channels, channels] fp32 (device, symmetric) is replaced by
+ *   alpha * hessian + beta * X^T X,   X = activation [tokens, channels] (fp32 / fp16 / bf16, channel last).
+ * The running form of the reference (H *= n/(n+b); n += b; H += (2/n) X^T X) is alpha = n/(n+b),
+ * beta = 2/(n+b) per call.  With allow_tensor_cores != 0 and a 16-bit activation whose channel count is a
+ * multiple of 64 (>= 256) the contraction runs on tcgen05 tensor cores (exact 16-bit products, fp32
+ * accumulation in tensor memory, operands by TMA); otherwise an fp32 CUDA-core kernel runs.  The
+ * tensor-core kernel bounds every wait; nncfb_hessian_status() (synchronises the stream) returns
+ * NNCFB_E_TIMEOUT if one gave up.  workspace is reserved (may be NULL).
+ * Replaces WC/gptq.py:200-242 (GPTQ._calculate_hessian).
+ */
+int nncfb_hessian_accumulate(float* hessian, int64_t channels, const void* x, int32_t dtype, int64_t tokens,
+                             float alpha, float beta, int32_t allow_tensor_cores, void* workspace,
+                             size_t workspace_bytes, void* stream);
+int nncfb_hessian_status(void* stream);
+
+/*
+ * GPTQ blocked column sweep.  weight [rows, cols] fp32 is the tensor-level weight: it is UPDATED IN PLACE by
+ * the trailing updates, as in the reference (pass a clone).  hinv [cols, cols] fp32 is the upper Cholesky
+ * factor of the inverse damped Hessian.  For every block of `block_size` (<= 128) columns: group parameters
+ * at each group start from the tensor-level weight, quantise-dequantise column by column with error feedback
+ * inside the block, then weight[:, i2:] -= Err @ hinv[i1:i2, i2:].  Outputs: q_out [rows, cols] fp32
+ * dequantised weight, scale_out [rows, G] fp32, zp_out [rows, G] int32 (asymmetric modes).
+ * workspace: caller-provided scratch of nncfb_gptq_workspace_bytes(rows) bytes.
+ * Replaces WC/gptq.py:297-379 (the loop of GPTQ._quantize_weights).
+ */
+size_t nncfb_gptq_workspace_bytes(int64_t rows);
+int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode, int64_t group_size,
+                        int32_t block_size, float* q_out, float* scale_out, int32_t* zp_out, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/*
  * Per-channel statistics of an activation [tokens, channels] (channel last) in one pass; every
  * output is optional (NULL):
  *   mean_out    [channels] in the activation's dtype (fp32 accumulate, one rounding)

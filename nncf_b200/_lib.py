@@ -45,7 +45,7 @@ class QuantizeArgs(C.Structure):
 
 def _load() -> C.CDLL:
     if not LIB_PATH.exists():
-        msg = (f"{LIB_PATH} not found. Build it with `python -m nncf_b200.build` (needs nvcc); "
+        msg = (f"{LIB_PATH} not found. Build it with `python nncf_b200/build.py` (needs nvcc); "
                "nncf_b200 has no CPU fallback.")
         raise LibraryNotBuiltError(msg)
     try:
@@ -63,6 +63,10 @@ def _load() -> C.CDLL:
         "nncfb_awq_search": ([vp, i32, i64, i64, i32, i64, vp, i32, vp, vp, i32, vp, i32, vp, C.c_float, C.c_float,
                               C.c_float, vp, vp, C.c_size_t, vp], C.c_int),
         "nncfb_channel_stats": ([vp, i32, i64, i64, vp, vp, vp, vp, vp], C.c_int),
+        "nncfb_hessian_accumulate": ([vp, i64, vp, i32, i64, C.c_float, C.c_float, i32, vp, C.c_size_t, vp], C.c_int),
+        "nncfb_hessian_status": ([vp], C.c_int),
+        "nncfb_gptq_workspace_bytes": ([i64], C.c_size_t),
+        "nncfb_gptq_quantize": ([vp, i64, i64, vp, i32, i64, i32, vp, vp, vp, vp, C.c_size_t, vp], C.c_int),
         "nncfb_pack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_unpack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_selftest_division": ([i64, u64, vp, vp], C.c_int),
@@ -77,6 +81,7 @@ def _load() -> C.CDLL:
 lib = _load()
 EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_quantize_batch",
             "nncfb_scale_estimation", "nncfb_awq_workspace_bytes", "nncfb_awq_search", "nncfb_channel_stats",
+            "nncfb_hessian_accumulate", "nncfb_hessian_status", "nncfb_gptq_workspace_bytes", "nncfb_gptq_quantize",
             "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
             "nncfb_selftest_division"]
 

@@ -1,7 +1,9 @@
 """Ahead-of-time build of libnncf_b200.so (nvcc, sm_100a only).
 
-    python -m nncf_b200.build            # build if sources are newer than the library
-    python -m nncf_b200.build --force
+    python nncf_b200/build.py            # build if sources are newer than the library
+    python nncf_b200/build.py --force
+
+(run it as a script: importing the package needs the library this builds)
 
 The library is built in-tree (nncf_b200/libnncf_b200.so); nothing is JIT-compiled at import.
 """

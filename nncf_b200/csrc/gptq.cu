@@ -1,0 +1,323 @@
+// GPTQ: blocked column sweep with error feedback, the lazy-batch trailing update and the fp32
+// (CUDA-core) Hessian accumulation.
+//
+// Restates GPTQ._quantize_weights of the reference
+// (src/nncf/quantization/algorithms/weight_compression/gptq.py:297-379) after its Hessian
+// preparation (dead columns, damping, Cholesky inverse: host-side library calls).  The reference
+// walks the columns in Python with ~8 small tensor operations per column; here one C call runs
+//   gptq_sweep_kernel     once per 128-column block: a thread owns an output row; the block's weights,
+//                         the matching Hinv block and the error columns live in shared memory;
+//                         group parameters are taken at each group start from the tensor-level weight
+//                         (updated at block ends only), exactly as the reference indexes it;
+//   gptq_trailing_kernel  W[:, i2:] -= Err_blk @ Hinv[i1:i2, i2:] as a tiled fp32 contraction.
+// Rounding follows the reference: quotients are true fp32 divisions, the in-block update is a
+// product rounded to fp32 followed by a subtraction (what `w -= outer(err, h)` does).  The trailing
+// contraction accumulates in fp32 in ascending k; BLAS libraries use another order, and GPTQ
+// amplifies such last-bit differences into occasional flipped codes.
+#include <algorithm>
+
+#include "quantize_kernels.cuh"
+
+namespace nncfb {
+
+constexpr int kGptqMaxBlock = 128;
+constexpr int kSweepRows = 64;
+constexpr int kSweepLd = kSweepRows + 1;
+
+struct GptqArgs {
+  float* w;            // [rows, cols] tensor-level weight, updated in place
+  const float* hinv;   // [cols, cols] upper Cholesky factor of H^-1
+  float* q;            // [rows, cols] dequantised result
+  float* err;          // [rows, kGptqMaxBlock] scratch: error columns of the current block
+  float* scale;        // [rows, G]
+  int32_t* zp;         // [rows, G] or null
+  int64_t rows, cols;
+  int64_t gs, G;
+  int i1, count;       // current block: columns [i1, i1 + count)
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  float* hs = smem;                                   // [128][128] Hinv block (row i, col j >= i used)
+  float* ws = hs + kGptqMaxBlock * kGptqMaxBlock;     // [128][65]  weights, column-major per thread
+  float* es = ws + kGptqMaxBlock * kSweepLd;          // [128][65]  error columns
+  const int t = threadIdx.x;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kSweepRows;
+  const int64_t row = row0 + t;
+  const bool valid = row < a.rows;
+  const int count = a.count, i1 = a.i1;
+
+  for (int idx = t; idx < count * count; idx += kSweepRows) {
+    const int i = idx / count, j = idx - i * count;
+    hs[i * kGptqMaxBlock + j] = a.hinv[static_cast<int64_t>(i1 + i) * a.cols + (i1 + j)];
+  }
+  // weight tile: rows are read along their columns (coalesced), stored column-major per thread
+  for (int r = 0; r < kSweepRows; ++r) {
+    const int64_t rr = row0 + r;
+    if (rr >= a.rows) break;
+    for (int j = t; j < count; j += kSweepRows) ws[j * kSweepLd + r] = a.w[rr * a.cols + i1 + j];
+  }
+  __syncthreads();
+
+  Codec<MODE> c;
+  c.from_given(1.0f, 0.0f);
+  for (int i = 0; i < count; ++i) {
+    const int64_t col = i1 + i;
+    if (col % a.gs == 0 && valid) {
+      // parameters from the tensor-level weight of this group (WC/gptq.py:312-335)
+      const int64_t end = min(col + a.gs, a.cols);
+      const float* wr = a.w + row * a.cols;
+      float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
+      for (int64_t k = col; k < end; ++k) {
+        const float v = wr[k];
+        mn = fminf(mn, v);
+        mx = fmaxf(mx, v);
+      }
+      c.from_stats(mn, mx);
+      const int64_t g = col / a.gs;
+      a.scale[row * a.G + g] = c.scale;
+      if (a.zp) a.zp[row * a.G + g] = static_cast<int32_t>(c.zp);
+    }
+    const float d = hs[i * kGptqMaxBlock + i];
+    const float w = ws[i * kSweepLd + t];
+    float u = 0.0f;
+    if (valid) c.encode(w, u);
+    const float dq = __fmul_rn(u, c.scale);
+    const float e = __fdiv_rn(__fsub_rn(w, dq), d);
+    ws[i * kSweepLd + t] = dq;  // the slot of a finished column carries its result
+    es[i * kSweepLd + t] = e;
+    const float* hrow = hs + i * kGptqMaxBlock;
+    for (int j = i + 1; j < count; ++j) {
+      ws[j * kSweepLd + t] = __fsub_rn(ws[j * kSweepLd + t], __fmul_rn(e, hrow[j]));
+    }
+  }
+  __syncthreads();
+  for (int r = 0; r < kSweepRows; ++r) {
+    const int64_t rr = row0 + r;
+    if (rr >= a.rows) break;
+    for (int j = t; j < count; j += kSweepRows) {
+      a.q[rr * a.cols + i1 + j] = ws[j * kSweepLd + r];
+      a.err[rr * kGptqMaxBlock + j] = es[j * kSweepLd + r];
+    }
+  }
+}
+
+// W[:, c0 + ...] -= Err[rows, count] @ Hinv[i1 : i1+count, c0 : cols]; 64 x 64 tile per block, 4 x 4 per thread.
+__global__ void __launch_bounds__(256) gptq_trailing_kernel(const GptqArgs a, const int64_t c0) {
+  constexpr int KC = 64;  // k chunk held in shared memory
+  __shared__ __align__(16) float e_s[KC][64 + 4];  // [k][row]
+  __shared__ __align__(16) float h_s[KC][64 + 4];  // [k][col]
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 64, cb = c0 + static_cast<int64_t>(blockIdx.x) * 64;
+  const int count = a.count;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  for (int k0 = 0; k0 < count; k0 += KC) {
+    const int kc = min(KC, count - k0);
+    for (int idx = threadIdx.x; idx < kc * 64; idx += 256) {
+      const int r = idx / kc, k = idx - r * kc;  // Err rows are contiguous along k
+      e_s[k][r] = (r0 + r < a.rows) ? a.err[(r0 + r) * kGptqMaxBlock + k0 + k] : 0.0f;
+    }
+    for (int idx = threadIdx.x; idx < kc * 64; idx += 256) {
+      const int k = idx >> 6, cc = idx & 63;
+      h_s[k][cc] = (cb + cc < a.cols) ? a.hinv[static_cast<int64_t>(a.i1 + k0 + k) * a.cols + cb + cc] : 0.0f;
+    }
+    __syncthreads();
+    for (int k = 0; k < kc; ++k) {
+      const float4 ev = *reinterpret_cast<const float4*>(&e_s[k][ty * 4]);
+      const float4 hv = *reinterpret_cast<const float4*>(&h_s[k][tx * 4]);
+      const float e4[4] = {ev.x, ev.y, ev.z, ev.w}, h4[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(e4[i], h4[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t r = r0 + ty * 4 + i;
+    if (r >= a.rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t cc = cb + tx * 4 + j;
+      if (cc < a.cols) a.w[r * a.cols + cc] = __fsub_rn(a.w[r * a.cols + cc], acc[i][j]);
+    }
+  }
+}
+
+template <int MODE>
+int run_gptq(GptqArgs a, int block, cudaStream_t st) {
+  const size_t smem = (static_cast<size_t>(kGptqMaxBlock) * kGptqMaxBlock + 2 * kGptqMaxBlock * kSweepLd) * sizeof(float);
+  NNCFB_CUDA(cudaFuncSetAttribute(gptq_sweep_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
+  const unsigned row_blocks = static_cast<unsigned>((a.rows + kSweepRows - 1) / kSweepRows);
+  for (int64_t i1 = 0; i1 < a.cols; i1 += block) {
+    a.i1 = static_cast<int>(i1);
+    a.count = static_cast<int>(std::min<int64_t>(block, a.cols - i1));
+    gptq_sweep_kernel<MODE><<<row_blocks, kSweepRows, smem, st>>>(a);
+    const int64_t c0 = i1 + a.count;
+    if (c0 < a.cols) {
+      const dim3 grid(static_cast<unsigned>((a.cols - c0 + 63) / 64), static_cast<unsigned>((a.rows + 63) / 64));
+      gptq_trailing_kernel<<<grid, 256, 0, st>>>(a, c0);
+    }
+  }
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+// ---- Hessian, CUDA-core fp32 path --------------------------------------------------------------
+// H[i0.., j0..] = alpha * H + beta * X^T X for one 64 x 64 tile with j-tile >= i-tile; the lower
+// triangle is mirrored afterwards.  Exact fp32 products and fp32 accumulation in token order.
+template <typename SrcT>
+__global__ void __launch_bounds__(256) hessian_simt_kernel(float* __restrict__ H, const SrcT* __restrict__ x,
+                                                           int64_t tokens, int64_t C, float alpha, float beta) {
+  if (blockIdx.x < blockIdx.y) return;  // upper triangle of tiles only
+  __shared__ __align__(16) float a_s[32][64 + 4], b_s[32][64 + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int64_t i0 = static_cast<int64_t>(blockIdx.y) * 64, j0 = static_cast<int64_t>(blockIdx.x) * 64;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  for (int64_t t0 = 0; t0 < tokens; t0 += 32) {
+    for (int idx = threadIdx.x; idx < 32 * 64; idx += 256) {
+      const int k = idx >> 6, cc = idx & 63;
+      const bool tk = t0 + k < tokens;
+      a_s[k][cc] = (tk && i0 + cc < C) ? to_f32<SrcT>(x[(t0 + k) * C + i0 + cc]) : 0.0f;
+      b_s[k][cc] = (tk && j0 + cc < C) ? to_f32<SrcT>(x[(t0 + k) * C + j0 + cc]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+      const float4 av = *reinterpret_cast<const float4*>(&a_s[k][ty * 4]);
+      const float4 bv = *reinterpret_cast<const float4*>(&b_s[k][tx * 4]);
+      const float a4[4] = {av.x, av.y, av.z, av.w}, b4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(a4[i], b4[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t r = i0 + ty * 4 + i;
+    if (r >= C) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t cc = j0 + tx * 4 + j;
+      if (cc < C) H[r * C + cc] = __fmaf_rn(beta, acc[i][j], __fmul_rn(alpha, H[r * C + cc]));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) mirror_upper_kernel(float* __restrict__ H, int64_t C) {
+  __shared__ float tile[32][33];
+  if (blockIdx.x <= blockIdx.y && !(blockIdx.x == blockIdx.y)) return;  // source tiles: strictly upper + diagonal
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 32, c0 = static_cast<int64_t>(blockIdx.x) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int k = ty; k < 32; k += 8) {
+    const int64_t r = r0 + k, cc = c0 + tx;
+    tile[k][tx] = (r < C && cc < C) ? H[r * C + cc] : 0.0f;
+  }
+  __syncthreads();
+  for (int k = ty; k < 32; k += 8) {
+    const int64_t r = c0 + k, cc = r0 + tx;  // transposed position
+    if (r < C && cc < C && r > cc) H[r * C + cc] = tile[tx][k];
+  }
+}
+
+}  // namespace nncfb
+
+using namespace nncfb;
+
+extern "C" size_t nncfb_gptq_workspace_bytes(int64_t rows) {
+  return rows > 0 ? static_cast<size_t>(rows) * kGptqMaxBlock * sizeof(float) : 0;
+}
+
+extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
+                                   int64_t group_size, int32_t block_size, float* q_out, float* scale_out,
+                                   int32_t* zp_out, void* workspace, size_t workspace_bytes, void* stream) {
+  NNCFB_CHECK_ARG(weight && hinv && q_out && scale_out && workspace, NNCFB_E_BAD_ARG, "nncfb_gptq_quantize: null pointer");
+  NNCFB_CHECK_ARG(rows > 0 && cols > 0, NNCFB_E_BAD_ARG, "nncfb_gptq_quantize: bad shape");
+  NNCFB_CHECK_ARG(group_size > 0 && cols % group_size == 0, NNCFB_E_GROUP_SIZE,
+                  "Channel size %lld should be divisible by size of group %lld.", (long long)cols, (long long)group_size);
+  NNCFB_CHECK_ARG(block_size > 0 && block_size <= kGptqMaxBlock, NNCFB_E_TOO_LARGE,
+                  "nncfb_gptq_quantize: block size %d is outside (0, %d]", block_size, kGptqMaxBlock);
+  NNCFB_CHECK_ARG(!mode_is_asym(mode) || zp_out, NNCFB_E_BAD_ARG, "nncfb_gptq_quantize: zp_out is null");
+  NNCFB_CHECK_ARG(workspace_bytes >= nncfb_gptq_workspace_bytes(rows), NNCFB_E_BAD_ARG,
+                  "nncfb_gptq_quantize: workspace of %zu bytes is smaller than nncfb_gptq_workspace_bytes() = %zu",
+                  workspace_bytes, nncfb_gptq_workspace_bytes(rows));
+  GptqArgs a;
+  a.w = weight;
+  a.hinv = hinv;
+  a.q = q_out;
+  a.err = static_cast<float*>(workspace);
+  a.scale = scale_out;
+  a.zp = mode_is_asym(mode) ? zp_out : nullptr;
+  a.rows = rows;
+  a.cols = cols;
+  a.gs = group_size;
+  a.G = cols / group_size;
+  a.i1 = 0;
+  a.count = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (mode) {
+    case NNCFB_INT4_SYM: return run_gptq<NNCFB_INT4_SYM>(a, block_size, st);
+    case NNCFB_INT4_ASYM: return run_gptq<NNCFB_INT4_ASYM>(a, block_size, st);
+    case NNCFB_INT8_SYM: return run_gptq<NNCFB_INT8_SYM>(a, block_size, st);
+    case NNCFB_INT8_ASYM: return run_gptq<NNCFB_INT8_ASYM>(a, block_size, st);
+    case NNCFB_NF4: return run_gptq<NNCFB_NF4>(a, block_size, st);
+    case NNCFB_FP4: return run_gptq<NNCFB_FP4>(a, block_size, st);
+    case NNCFB_MXFP4: return run_gptq<NNCFB_MXFP4>(a, block_size, st);
+    default: break;
+  }
+  set_error("nncfb_gptq_quantize: mode %d is not supported", mode);
+  return NNCFB_E_UNSUPPORTED;
+}
+
+namespace nncfb {
+// tensor-core path for 16-bit activations (hessian_tc.cu); returns NNCFB_E_UNSUPPORTED when the
+// shape does not fit its tiling, in which case the CUDA-core kernel above runs.
+int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t tokens, float alpha, float beta,
+                          void* workspace, size_t workspace_bytes, cudaStream_t st);
+}  // namespace nncfb
+
+extern "C" int nncfb_hessian_accumulate(float* hessian, int64_t channels, const void* x, int32_t dtype, int64_t tokens,
+                                        float alpha, float beta, int32_t allow_tensor_cores, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  NNCFB_CHECK_ARG(hessian && x, NNCFB_E_BAD_ARG, "nncfb_hessian_accumulate: null pointer");
+  NNCFB_CHECK_ARG(channels > 0 && tokens > 0, NNCFB_E_BAD_ARG, "nncfb_hessian_accumulate: bad shape");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (allow_tensor_cores && (dtype == NNCFB_BF16 || dtype == NNCFB_F16)) {
+    const int rc = hessian_tc_accumulate(hessian, channels, x, dtype, tokens, alpha, beta, workspace, workspace_bytes, st);
+    if (rc != NNCFB_E_UNSUPPORTED) return rc;
+  }
+  const dim3 grid(static_cast<unsigned>((channels + 63) / 64), static_cast<unsigned>((channels + 63) / 64));
+  switch (dtype) {
+    case NNCFB_F32:
+      hessian_simt_kernel<float><<<grid, 256, 0, st>>>(hessian, static_cast<const float*>(x), tokens, channels, alpha, beta);
+      break;
+    case NNCFB_F16:
+      hessian_simt_kernel<__half><<<grid, 256, 0, st>>>(hessian, static_cast<const __half*>(x), tokens, channels, alpha, beta);
+      break;
+    case NNCFB_BF16:
+      hessian_simt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(hessian, static_cast<const __nv_bfloat16*>(x), tokens,
+                                                               channels, alpha, beta);
+      break;
+    default:
+      set_error("nncfb_hessian_accumulate: unsupported dtype %d", dtype);
+      return NNCFB_E_BAD_ARG;
+  }
+  NNCFB_CUDA(cudaGetLastError());
+  const dim3 mgrid(static_cast<unsigned>((channels + 31) / 32), static_cast<unsigned>((channels + 31) / 32));
+  mirror_upper_kernel<<<mgrid, 256, 0, st>>>(hessian, channels);
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}

@@ -1,0 +1,366 @@
+// GPTQ Hessian accumulation H = alpha * H + beta * X^T X on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory, operands staged by TMA).
+//
+// Restates the contraction of GPTQ._calculate_hessian
+// (src/nncf/quantization/algorithms/weight_compression/gptq.py:200-242): X is an activation
+// [tokens, C] in bf16 / fp16, H is fp32 [C, C].  Products of 16-bit values are exact in fp32 and the
+// accumulation is fp32 in tensor memory, so the result is fp32-faithful without operand splitting;
+// the scale factors are applied once in the epilogue instead of to every element of X.
+//
+// Both operands are the SAME matrix X read "MN-major": A = X^T (M = channels i, K = tokens) and
+// B = X (K = tokens, N = channels j) both have the channel index contiguous in memory, so no
+// transposed copy of X is ever made.  A TMA box of 64 channels x 64 tokens with 128-byte swizzle is
+// exactly one canonical MN-major swizzle-128B operand atom column (8 token rows per 1024-byte atom).
+//
+// One CTA computes one 128 x 256 tile of the upper triangle of H over all tokens:
+//   warp 0        TMA producer (one elected lane), 4-stage ring, mbarrier expect-tx
+//   warp 1        tensor-memory allocation, MMA issue (one elected lane), tcgen05.commit
+//   warps 2..5    epilogue: tcgen05.ld of the fp32 accumulators, H = alpha*H + beta*acc
+// Every wait is bounded: after kSpinLimit polls a role records an error code in a global flag
+// and leaves; the other roles then time out the same way, tensor memory is released and the
+// kernel returns (the host reports NNCFB_E_TIMEOUT).  No multicast, no cluster, no peer memory.
+#include <cuda.h>
+
+#include "nncfb_common.cuh"
+
+namespace nncfb {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 256;
+constexpr int kBoxC = 64;    // channels per TMA box (128 bytes of bf16)
+constexpr int kBlockK = 64;  // tokens per pipeline stage
+constexpr int kStages = 4;
+constexpr int kBoxBytes = kBoxC * kBlockK * 2;                           // 8192
+constexpr int kStageBytes = (kTileM / kBoxC + kTileN / kBoxC) * kBoxBytes;  // 49152
+constexpr int kTmemCols = 256;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false after kSpinLimit unsuccessful polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// MN-major, 128-byte swizzle shared-memory operand descriptor:
+//   start address >> 4 | LBO (stride between 64-element atoms along M/N) >> 4 at bit 16 |
+//   SBO (stride between groups of 8 K rows) >> 4 at bit 32 | version 1 at bit 46 | layout 2 (SW128) at bit 61
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(kBoxBytes >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_c),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct __align__(8) Control {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_ready;
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+__global__ void __launch_bounds__(192, 1)
+hessian_tc_kernel(const __grid_constant__ CUtensorMap xmap, float* __restrict__ H, int64_t C, int64_t tokens,
+                  float alpha, float beta, uint32_t idesc, int n_tiles_n, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte aligned operand ring (swizzle-128B atoms must start on 1 KiB), control block behind it
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Control* ctl = reinterpret_cast<Control*>(ring + kStages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // tile -> (mi, nj) with nj >= mi / 2 (tiles that touch the upper triangle)
+  int mi = 0, rem = blockIdx.x;
+  for (;;) {
+    const int row_tiles = n_tiles_n - mi / 2;
+    if (rem < row_tiles) break;
+    rem -= row_tiles;
+    ++mi;
+  }
+  const int nj = mi / 2 + rem;
+  const int m0 = mi * kTileM, n0 = nj * kTileN;
+  const int k_iters = static_cast<int>((tokens + kBlockK - 1) / kBlockK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    mbar_init(&ctl->acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer ------------------------------------------------------------------------
+      bool ok = true;
+      int issued = 0;
+      for (int it = 0; it < k_iters && ok; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        ok = mbar_wait(&ctl->empty[s], ph ^ 1);
+        if (!ok) {
+          atomicExch(status, 1);
+          break;
+        }
+        uint8_t* stage = ring + s * kStageBytes;
+        mbar_expect_tx(&ctl->full[s], kStageBytes);
+        const int tok = it * kBlockK;
+#pragma unroll
+        for (int b = 0; b < kTileM / kBoxC; ++b) tma_load_2d(stage + b * kBoxBytes, &xmap, m0 + b * kBoxC, tok, &ctl->full[s]);
+#pragma unroll
+        for (int b = 0; b < kTileN / kBoxC; ++b)
+          tma_load_2d(stage + (kTileM / kBoxC + b) * kBoxBytes, &xmap, n0 + b * kBoxC, tok, &ctl->full[s]);
+        ++issued;
+      }
+      // do not leave while a copy into this CTA's shared memory may still be in flight: wait (bounded)
+      // for the last copies issued to each stage
+      for (int it = max(0, issued - kStages); it < issued; ++it) {
+        if (!mbar_wait(&ctl->full[it % kStages], (it / kStages) & 1)) {
+          atomicExch(status, 4);
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----------------------------------------------------------------------------
+      bool ok = true;
+      for (int it = 0; it < k_iters && ok; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        ok = mbar_wait(&ctl->full[s], ph);
+        if (!ok) {
+          atomicExch(status, 2);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(ring + s * kStageBytes);
+        const uint32_t b_addr = a_addr + (kTileM / kBoxC) * kBoxBytes;
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k) {
+          // 16 tokens per instruction = two groups of eight 128-byte rows = 2048 bytes
+          const uint64_t adesc = make_desc(a_addr + k * 2048);
+          const uint64_t bdesc = make_desc(b_addr + k * 2048);
+          umma_f16(tmem_base, adesc, bdesc, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
+      }
+      umma_commit(&ctl->acc_ready);   // accumulator complete (or abandoned: the epilogue checks status)
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ------------------------------
+    const bool ok = mbar_wait(&ctl->acc_ready, 0);
+    if (!ok && lane == 0) atomicExch(status, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool good = ok && (*reinterpret_cast<volatile int*>(status) == 0);
+    if (good) {
+      const int q = warp & 3;
+      const int64_t r = static_cast<int64_t>(m0) + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < kTileN; c += 32) {
+        uint32_t acc[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c), acc);
+        if (r < C) {
+          float* hrow = H + r * C + n0 + c;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            if (n0 + c + j + 3 < C) {
+              float4 h = *reinterpret_cast<float4*>(hrow + j);
+              h.x = __fmaf_rn(beta, __uint_as_float(acc[j]), __fmul_rn(alpha, h.x));
+              h.y = __fmaf_rn(beta, __uint_as_float(acc[j + 1]), __fmul_rn(alpha, h.y));
+              h.z = __fmaf_rn(beta, __uint_as_float(acc[j + 2]), __fmul_rn(alpha, h.z));
+              h.w = __fmaf_rn(beta, __uint_as_float(acc[j + 3]), __fmul_rn(alpha, h.w));
+              *reinterpret_cast<float4*>(hrow + j) = h;
+            } else {
+              for (int jj = j; jj < j + 4; ++jj) {
+                if (n0 + c + jj < C) hrow[jj] = __fmaf_rn(beta, __uint_as_float(acc[jj]), __fmul_rn(alpha, hrow[jj]));
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+__global__ void __launch_bounds__(256) mirror_upper_tc_kernel(float* __restrict__ H, int64_t C) {
+  __shared__ float tile[32][33];
+  if (blockIdx.x < blockIdx.y) return;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 32, c0 = static_cast<int64_t>(blockIdx.x) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int k = ty; k < 32; k += 8) {
+    const int64_t r = r0 + k, cc = c0 + tx;
+    tile[k][tx] = (r < C && cc < C) ? H[r * C + cc] : 0.0f;
+  }
+  __syncthreads();
+  for (int k = ty; k < 32; k += 8) {
+    const int64_t r = c0 + k, cc = r0 + tx;
+    if (r < C && cc < C && r > cc) H[r * C + cc] = tile[tx][k];
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+}  // namespace
+
+// Per-device error flag of the tensor-core kernel (static device memory: nothing is allocated).
+__device__ int g_hessian_status;
+
+int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t tokens, float alpha, float beta,
+                          void* /*workspace*/, size_t /*workspace_bytes*/, cudaStream_t st) {
+  if (C % 64 != 0 || C < 256 || !aligned16(x) || !aligned16(H) || tokens <= 0 || tokens > 0x7fffffff ||
+      C > 0x7fffffff / 2)
+    return NNCFB_E_UNSUPPORTED;
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return NNCFB_E_UNSUPPORTED;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(C) * 2};
+  const cuuint32_t box[2] = {kBoxC, kBlockK};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult cr = encode(&map, dtype == NNCFB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                             2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code %d", static_cast<int>(cr));
+    return NNCFB_E_CUDA;
+  }
+  const int tiles_m = static_cast<int>((C + kTileM - 1) / kTileM);
+  const int tiles_n = static_cast<int>((C + kTileN - 1) / kTileN);
+  int n_tiles = 0;
+  for (int mi = 0; mi < tiles_m; ++mi) n_tiles += tiles_n - mi / 2;
+  // instruction descriptor: fp32 accumulate, A/B format, both operands MN-major, N >> 3, M >> 4
+  const uint32_t fmt = dtype == NNCFB_BF16 ? 1u : 0u;
+  const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) |
+                         (static_cast<uint32_t>(kTileN >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+  const size_t smem = static_cast<size_t>(kStages) * kStageBytes + sizeof(Control) + 1024;
+  NNCFB_CUDA(cudaFuncSetAttribute(hessian_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  int* status = nullptr;
+  NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_hessian_status));
+  NNCFB_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  hessian_tc_kernel<<<n_tiles, 192, smem, st>>>(map, H, C, tokens, alpha, beta, idesc, tiles_n, status);
+  NNCFB_CUDA(cudaGetLastError());
+  const dim3 mgrid(static_cast<unsigned>((C + 31) / 32), static_cast<unsigned>((C + 31) / 32));
+  mirror_upper_tc_kernel<<<mgrid, 256, 0, st>>>(H, C);
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+// Reads the error flag of the last tensor-core Hessian launch on this device (synchronises the stream).
+int hessian_tc_status(cudaStream_t st) {
+  int* status = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_hessian_status) != cudaSuccess) return -1;
+  int h = 0;
+  if (cudaMemcpyAsync(&h, status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
+  return h;
+}
+
+}  // namespace nncfb
+
+extern "C" int nncfb_hessian_status(void* stream) {
+  const int s = nncfb::hessian_tc_status(static_cast<cudaStream_t>(stream));
+  if (s < 0) {
+    nncfb::set_error("nncfb_hessian_status: could not read the status flag");
+    return NNCFB_E_CUDA;
+  }
+  if (s != 0) {
+    nncfb::set_error("tensor-core Hessian kernel gave up a bounded wait (role %d: 1 = producer, 2 = MMA, 3 = epilogue)", s);
+    return NNCFB_E_TIMEOUT;
+  }
+  return NNCFB_OK;
+}

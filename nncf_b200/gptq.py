@@ -1,0 +1,114 @@
+"""GPTQ: host mirror of src/nncf/quantization/algorithms/weight_compression/gptq.py
+(``_calculate_hessian`` :200-242 and ``_quantize_weights`` :244-379, same argument meaning and
+result shapes).  The Hessian contraction runs on the tcgen05 tensor cores (``nncfb_hessian_accumulate``),
+the blocked column sweep and its trailing updates in ``nncfb_gptq_quantize``; dead-column fix-up, damping
+and the three Cholesky steps are small library calls (torch.linalg / cuSOLVER) like in the reference."""
+
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from .config import WeightCompressionConfig
+from .parameters import CompressWeightsMode
+
+
+class GPTQ:
+    def __init__(self, damp_percent: float = 0.1, block_size: int = 128, subset_size: int = 128,
+                 scale_estimation: bool = False, tensor_cores: bool = True):
+        self._damp_percent = damp_percent
+        self._block_size = block_size
+        self._subset_size = subset_size
+        if scale_estimation:
+            msg = "scale estimation inside GPTQ is not supported"
+            raise NotImplementedError(msg)
+        self._tensor_cores = tensor_cores
+
+    # ------------------------------------------------------------------------------------------
+    def _calculate_hessian(self, node, inputs: Sequence[torch.Tensor], is_3d_weight: bool = False) -> torch.Tensor:
+        """gptq.py:200-242 for a 2-D weight: running H = sum (2/n) X^T X over the calibration inputs.
+        ``inputs``: activations [b, T, C] or [T, C] (channel last).  Returns [1, C, C] fp32 like the
+        reference.  ``node`` is accepted for signature compatibility and ignored."""
+        if is_3d_weight:
+            msg = "stacked (3-D) weights: call per expert"
+            raise NotImplementedError(msg)
+        C = inputs[0].shape[-1]
+        dev = inputs[0].device
+        H = torch.zeros((C, C), dtype=torch.float32, device=dev)
+        nsamples = 0
+        with torch.cuda.device(dev):
+            st = _lib.stream_handle(dev)
+            for inp in inputs:
+                batch = inp.shape[0] if inp.ndim == 3 else 1
+                x = inp.reshape(-1, C).contiguous()
+                if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+                    x = x.float()
+                alpha = nsamples / (nsamples + batch)
+                nsamples += batch
+                beta = 2.0 / nsamples
+                _lib.check(_lib.lib.nncfb_hessian_accumulate(
+                    _lib.ptr(H), C, _lib.ptr(x), _lib.DTYPE_IDS[x.dtype], x.shape[0], alpha, beta,
+                    1 if self._tensor_cores else 0, None, 0, st))
+            _lib.check(_lib.lib.nncfb_hessian_status(st))
+        return H.unsqueeze(0)
+
+    def accumulate_hessian(self, H: torch.Tensor, x: torch.Tensor, nsamples: int, batch: int) -> int:
+        """One step of the running accumulation for callers that stream activations layer by layer:
+        H <- H * n/(n+b) + (2/(n+b)) X^T X.  Returns the new sample count."""
+        C = H.shape[-1]
+        x = x.reshape(-1, C).contiguous()
+        dev = H.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.nncfb_hessian_accumulate(
+                _lib.ptr(H), C, _lib.ptr(x), _lib.DTYPE_IDS[x.dtype], x.shape[0], nsamples / (nsamples + batch),
+                2.0 / (nsamples + batch), 1 if self._tensor_cores else 0, None, 0, _lib.stream_handle(dev)))
+        return nsamples + batch
+
+    # ------------------------------------------------------------------------------------------
+    def prepare_hessian_inverse(self, hessian: torch.Tensor, weight_tensor: torch.Tensor) -> torch.Tensor:
+        """gptq.py:269-295: dead columns, damping, upper Cholesky factor of the inverse.  Mutates both
+        arguments like the reference."""
+        diag = torch.diagonal(hessian)
+        dead = diag == 0
+        diag[dead] = 1
+        weight_tensor[:, dead] = 0
+        damp = self._damp_percent * torch.mean(torch.diagonal(hessian))
+        torch.diagonal(hessian).add_(damp)
+        L = torch.linalg.cholesky(hessian)
+        Hinv = torch.cholesky_inverse(L)
+        return torch.linalg.cholesky(Hinv, upper=True).contiguous()
+
+    def _quantize_weights(self, wc_params, hessian: torch.Tensor, weight_tensor: torch.Tensor,
+                          inputs: Optional[Sequence[torch.Tensor]] = None):
+        """gptq.py:244-379.  ``weight_tensor`` [out, C] fp32 is modified in place (trailing updates) like the
+        reference's; returns (dequantised weight [out, C] fp32, scales [out, G, 1], zero points or None)."""
+        config: WeightCompressionConfig = wc_params.compression_config
+        assert hessian.ndim == 2, "Hessian should be 2D"
+        if weight_tensor.dtype != torch.float32 or not weight_tensor.is_contiguous():
+            msg = "weight_tensor must be a contiguous fp32 tensor (the sweep updates it in place)"
+            raise ValueError(msg)
+        hinv = self.prepare_hessian_inverse(hessian, weight_tensor)
+        rows, cols = weight_tensor.shape
+        gs = config.group_size if config.group_size != -1 else cols
+        dev = weight_tensor.device
+        G = cols // gs
+        q = torch.empty_like(weight_tensor)
+        scale = torch.empty((rows, G), dtype=torch.float32, device=dev)
+        zp = torch.empty((rows, G), dtype=torch.int32, device=dev) if config.is_asym_mode else None
+        ws_bytes = int(_lib.lib.nncfb_gptq_workspace_bytes(rows))
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib.nncfb_gptq_quantize(
+                _lib.ptr(weight_tensor), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[config.mode.value], gs,
+                self._block_size, _lib.ptr(q), _lib.ptr(scale), _lib.ptr(zp), _lib.ptr(workspace), ws_bytes,
+                _lib.stream_handle(dev)))
+        scales = scale.reshape(rows, G, 1)
+        zero_points = zp.reshape(rows, G, 1) if zp is not None else None
+        if config.group_size == -1:
+            scales = scales.squeeze(-1)
+            zero_points = zero_points.squeeze(-1) if zero_points is not None else None
+        if config.mode not in (CompressWeightsMode.INT8_ASYM, CompressWeightsMode.INT4_ASYM):
+            zero_points = None
+        return q, scales, zero_points
