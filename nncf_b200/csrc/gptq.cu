@@ -62,6 +62,11 @@ __global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a
 
   Codec<MODE> c;
   c.from_given(1.0f, 0.0f);
+  if (valid && i1 % a.gs != 0) {
+    // the block starts inside a group that an earlier block opened: take its stored parameters
+    const int64_t g = i1 / a.gs;
+    c.from_given(a.scale[row * a.G + g], a.zp ? static_cast<float>(a.zp[row * a.G + g]) : 0.0f);
+  }
   for (int i = 0; i < count; ++i) {
     const int64_t col = i1 + i;
     if (col % a.gs == 0 && valid) {

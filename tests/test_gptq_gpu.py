@@ -55,8 +55,10 @@ def test_tensor_core_hessian_matches_fp64(dtype, C, tokens):
     H_tc = GPTQ(tensor_cores=True)._calculate_hessian(None, [x])[0]
     H_cc = GPTQ(tensor_cores=False)._calculate_hessian(None, [x])[0]
     scale = ref.abs().max().item()
-    assert (H_tc - ref).abs().max().item() <= 2e-6 * scale * max(1.0, tokens / 1000)
-    assert (H_cc - ref).abs().max().item() <= 2e-6 * scale * max(1.0, tokens / 1000)
+    # fp32 accumulation of `tokens` exact products: error grows like sqrt(tokens) * 2^-24 * |H|
+    tol = 4e-7 * scale * max(1.0, tokens ** 0.5)
+    assert (H_tc - ref).abs().max().item() <= tol
+    assert (H_cc - ref).abs().max().item() <= tol
     assert torch.equal(H_tc, H_tc.T)
     # running form over two chunks equals one pass within fp32 rounding
     h = GPTQ(tensor_cores=True)
@@ -66,7 +68,7 @@ def test_tensor_core_hessian_matches_fp64(dtype, C, tokens):
     _lib.check(_lib.lib.nncfb_hessian_status(None))
     ref2 = ((x[: tokens // 2].double().T @ x[: tokens // 2].double()) +
             (x[tokens // 2:].double().T @ x[tokens // 2:].double())).float()
-    assert (H2 - ref2).abs().max().item() <= 4e-6 * scale
+    assert (H2 - ref2).abs().max().item() <= 2 * tol
 
 
 @pytest.mark.parametrize("case", GPTQ_CASES, ids=[c[0] for c in GPTQ_CASES])
