@@ -189,6 +189,25 @@ int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* 
                         size_t workspace_bytes, void* stream);
 
 /*
+ * nncfb_gptq_quantize for callers that cannot provide scratch memory.  It has no counterpart in the
+ * reference.  Who needs it: a program that embeds the library but cannot allocate device memory itself -
+ * its runtime handed all of HBM to a private arena at start-up and exposes no allocation hook, or it runs
+ * in a loop where cudaMalloc's device-wide synchronisation is forbidden.  Same arguments and results as
+ * nncfb_gptq_quantize minus the workspace: the error-column scratch is a fixed 8 MiB array inside the
+ * library (held by every GPU that loads the library until the process exits).
+ *   - rows <= 16384; larger problems return NNCFB_E_TOO_LARGE (use nncfb_gptq_quantize).
+ *   - The first call on a device looks up the array's device address (once per device, with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents (nothing in it needs to be
+ *     zero: every value is written before it is read).  Calls whose kernels can overlap on the GPU - other
+ *     streams or host threads - race on it: issue them on one stream or serialise them.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ */
+int nncfb_gptq_quantize_noalloc(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
+                                int64_t group_size, int32_t block_size, float* q_out, float* scale_out, int32_t* zp_out,
+                                void* stream);
+
+/*
  * Per-channel statistics of an activation [tokens, channels] (channel last) in one pass; every
  * output is optional (NULL):
  *   mean_out    [channels] in the activation's dtype (fp32 accumulate, one rounding)

@@ -15,6 +15,7 @@
 // contraction accumulates in fp32 in ascending k; BLAS libraries use another order, and GPTQ
 // amplifies such last-bit differences into occasional flipped codes.
 #include <algorithm>
+#include <mutex>
 
 #include "quantize_kernels.cuh"
 
@@ -285,6 +286,56 @@ extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, co
   }
   set_error("nncfb_gptq_quantize: mode %d is not supported", mode);
   return NNCFB_E_UNSUPPORTED;
+}
+
+// ---- GPTQ sweep for callers that cannot hand over scratch memory -----------------------------------
+// Some programs that embed this library have no device allocator to offer: a runtime that gave every
+// byte of HBM to its own arena at start-up and exposes no allocation hook through a C interface, or a
+// service loop in which cudaMalloc (which synchronises the whole device) must never run.  For them the
+// error-column scratch of the sweep lives in this fixed array instead of a caller buffer.  It is part of
+// the library image: every GPU that loads the library holds these 8 MiB until the process exits.
+namespace nncfb {
+constexpr int64_t kNoAllocMaxRows = 16384;
+static __device__ __align__(256) float g_gptq_noalloc_scratch[kNoAllocMaxRows * kGptqMaxBlock];
+
+namespace {
+std::mutex g_noalloc_mutex;
+float* g_noalloc_ptr[64] = {};  // device address of the array, per device ordinal
+}  // namespace
+
+// Device address of the scratch array on the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, so it is resolved once per device (with that
+// device current) through cudaGetSymbolAddress and cached.
+static int noalloc_scratch(float** out) {
+  int dev = 0;
+  NNCFB_CUDA(cudaGetDevice(&dev));
+  NNCFB_CHECK_ARG(dev >= 0 && dev < 64, NNCFB_E_UNSUPPORTED, "nncfb_gptq_quantize_noalloc: device ordinal %d >= 64", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_gptq_noalloc_scratch));
+    NNCFB_CHECK_ARG(p != nullptr, NNCFB_E_CUDA, "nncfb_gptq_quantize_noalloc: scratch symbol has no device address");
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return NNCFB_OK;
+}
+}  // namespace nncfb
+
+extern "C" int nncfb_gptq_quantize_noalloc(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
+                                           int64_t group_size, int32_t block_size, float* q_out, float* scale_out,
+                                           int32_t* zp_out, void* stream) {
+  NNCFB_CHECK_ARG(rows <= kNoAllocMaxRows, NNCFB_E_TOO_LARGE,
+                  "nncfb_gptq_quantize_noalloc: %lld rows exceed the built-in scratch (maximum %lld rows); use "
+                  "nncfb_gptq_quantize with a caller workspace",
+                  (long long)rows, (long long)kNoAllocMaxRows);
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != NNCFB_OK) return rc;
+  // Nothing in the scratch has to start at zero: each block's sweep writes every error column of every
+  // row before the trailing update reads it, so contents left by an earlier call are never observed.
+  return nncfb_gptq_quantize(weight, rows, cols, hinv, mode, group_size, block_size, q_out, scale_out, zp_out, scratch,
+                             static_cast<size_t>(kNoAllocMaxRows) * kGptqMaxBlock * sizeof(float), stream);
 }
 
 namespace nncfb {
