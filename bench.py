@@ -255,6 +255,31 @@ def main():
     ms_per_step = float(t.item()) / args.steps
     value = world * src_bytes / (ms_per_step * 1e-3) / 1e9
 
+    # ---- the one exchange step of the multi-GPU path: packed results to rank 0 (NCCL) ------------------
+    gather = None
+    if world > 1 and not args.profile_case:
+        from nncf_b200.sharding import gather_results
+
+        named = {f"r{rank}/{it.name}": it.output_tensors() for it in plan.items}
+        gather_results(named, dst=0)  # warm-up (communicator set-up)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(3):
+            merged = gather_results(named, dst=0)
+            del merged
+        g1.record()
+        barrier()
+        gt = torch.tensor([g0.elapsed_time(g1) / 3], dtype=torch.float64, device=device)
+        dist.all_reduce(gt, op=dist.ReduceOp.MAX)
+        gms = float(gt.item())
+        gather = {"ms_per_step": round(gms, 3), "bytes_into_rank0": (world - 1) * out_bytes,
+                  "ingest_GBps": round((world - 1) * out_bytes / (gms * 1e-3) / 1e9, 1),
+                  "value_with_gather": round(world * src_bytes / ((ms_per_step + gms) * 1e-3) / 1e9, 2),
+                  "how": "torch.distributed isend/irecv (NCCL) of one flat buffer per rank, not overlapped with compute"}
+        del named
+        torch.cuda.empty_cache()
+
     # ---- end to end through host buffers ---------------------------------------------------------
     e2e = None
     if not args.no_e2e:
@@ -320,7 +345,7 @@ def main():
                    "per_rank_source_bytes": src_bytes, "launch": "per-call" if (args.no_graph or args.profile_case) else "cuda-graph replay",
                    "l2": "inputs (16 GB per step) exceed L2 (126 MB); no flush needed",
                    "seed": "1 + rank", "distribution": "N(0, 0.02^2) bf16"},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * 2, "clocks": clocks,
+        "roofline": roofline, "e2e": e2e, "gather_to_rank0": gather, "gpu_launches": args.steps * 2, "clocks": clocks,
     }
     if world == 1 and not args.no_cpu_baseline:
         threads = host_threads()
