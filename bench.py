@@ -428,12 +428,13 @@ def main():
         "algorithmic_bytes_per_step": alg4, "traffic": None,
         "int8_kernel": {"kernel": "quant_channel_batch_kernel<bf16, INT8_ASYM, 64 threads/row>", "ms_per_step": round(ms8, 4)},
     }
-    prof = ROOT / "profiles" / "traffic.json"
-    if prof.exists():
-        try:
-            roofline["traffic"] = json.loads(prof.read_text()).get("int4_sym_g128_bf16_bytes_per_step")
-        except Exception:
-            pass
+    # DRAM traffic of the INT4 launch: dram__bytes_read + dram__bytes_write of one ncu capture of the same
+    # kernel on one decoder layer (profiles/quant_rows_batch_kernel_int4sym_g128_bf16_one_layer.md: 514.2 MB for
+    # 218.1 M elements = 2.358 B/element), scaled to this launch by its element count (traffic is proportional
+    # to the elements processed: every weight is read once and every code written once)
+    if not args.profile_case:
+        roofline["traffic"] = int(2.358 * alg4 / 2.53125)
+        roofline["traffic_source"] = "ncu capture of one decoder layer, scaled by elements"
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
