@@ -23,6 +23,7 @@ int launch_fast_run(const nncfb_quantize_args* items, int n, FastClass cls, cuda
     t.scale = p.scale_out;
     t.zp = p.zp_out;
     t.scale_f16 = p.scale_f16_out;
+    t.e8m0 = p.scale_e8m0_out;
     t.n_groups = p.outer * (p.reduce / p.group_size);
     batch.iter_start[i + 1] = batch.iter_start[i] + fast_iterations(cls, t.n_groups, esz);
   }

@@ -29,6 +29,7 @@ struct FastTensor {
   float* scale;
   int32_t* zp;
   uint16_t* scale_f16;
+  uint8_t* e8m0;
   int64_t n_groups;
 };
 
@@ -237,6 +238,92 @@ __device__ __forceinline__ void int_params(float mn, float mx, float& s, float& 
   }
 }
 
+// ---- float (code-book) modes ---------------------------------------------------------------------------
+// NF4 and E2M1 indices without a search: the quotient q is bucketed by one FMA (bucket width smaller than
+// the smallest gap between decision boundaries, so a bucket holds at most one boundary) and a 32-entry
+// table spread over the lanes of the warp - fetched with two shuffles - gives the number of boundaries
+// below the bucket and the one boundary inside it:  index = base[k] + (q > bound[k]).
+// NF4: k = rint(q * 15.49 + 16) in [1, 31] for q in [-1, 1]; bounds are the reference's 15 literals
+// (WC/constants.py:84-103), '>' reproduces searchsorted(side='left').
+// E2M1: k = rint(4 |q|) in [0, 24]; the seven thresholds sit at bucket centres; a '>=' threshold (ties that
+// go up to an even mantissa) is stored as the float just below it, so one '>' serves both kinds.
+constexpr float kLutNone = 3.0e38f;
+__device__ __constant__ const float kNf4LutBound[32] = {
+    kLutNone, kLutNone, kLutNone, -0.8480964303016663f, kLutNone, kLutNone, kLutNone, -0.6106328964233398f,
+    kLutNone, -0.4599952697753906f, kLutNone, -0.33967941999435425f, -0.23460739850997925f, kLutNone,
+    -0.13791173696517944f, -0.045525018125772476f, kLutNone, 0.03979014977812767f, 0.1202552542090416f,
+    0.2035212516784668f, kLutNone, 0.2920137643814087f, 0.3893125355243683f, kLutNone, 0.5016633868217468f,
+    kLutNone, 0.6427869200706482f, kLutNone, kLutNone, 0.8614783883094788f, kLutNone, kLutNone};
+__device__ __constant__ const int kNf4LutBase[32] = {0, 0, 0, 0, 1, 1, 1, 1, 2, 2, 3, 3, 4, 5, 5, 6,
+                                                     7, 7, 8, 9, 10, 10, 11, 12, 12, 13, 13, 14, 14, 14, 15, 15};
+__device__ __constant__ const float kE2m1LutBound[32] = {
+    kLutNone, 0.25f, kLutNone, 0.7499999403953552f, kLutNone, 1.25f, kLutNone, 1.7499998807907104f,
+    kLutNone, kLutNone, 2.5f, kLutNone, kLutNone, kLutNone, 3.499999761581421f, kLutNone,
+    kLutNone, kLutNone, kLutNone, kLutNone, 5.0f, kLutNone, kLutNone, kLutNone,
+    kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone};
+__device__ __constant__ const int kE2m1LutBase[32] = {0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 4, 5, 5, 5, 5, 6,
+                                                      6, 6, 6, 6, 6, 7, 7, 7, 7, 7, 7, 7, 7, 7, 7, 7};
+
+__host__ __device__ constexpr bool mode_is_fast_float(int m) { return m == NNCFB_NF4 || m == NNCFB_FP4 || m == NNCFB_MXFP4; }
+
+// Scale of a float-mode group, WC/weight_lowering.py:106-126: max|w| (/ 6 for E2M1), eps guard, power of
+// two for MX.  `r` is the correctly rounded reciprocal (exact for a power of two).
+template <int MODE>
+__device__ __forceinline__ void float_params(float mn, float mx, float& s, float& r, int& e8) {
+  float a = fmaxf(fabsf(mn), fabsf(mx));
+  if constexpr (MODE != NNCFB_NF4) a = exact_quotient(a, 6.0f, 1.0f / 6.0f);
+  a = (a < kEps32) ? kEps32 : a;
+  e8 = 0;
+  if constexpr (MODE == NNCFB_MXFP4) {
+    e8 = e8m0_exponent(a);
+    s = exp2_int(e8);
+    r = exp2_int(-e8);
+  } else {
+    s = a;
+    r = __frcp_rn(a);
+  }
+}
+
+// Nibble codes of 8 elements: NF4 table index, or E2M1 bit pattern sign|index (zero is stored as +0).
+template <int MODE>
+__device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s, float r, float lut_bound, int lut_base) {
+  const float2 r2 = f2(r, r), ns2 = f2(-s, -s);
+  uint32_t acc = 0;
+#pragma unroll
+  for (int i = 3; i >= 0; --i) {
+    const float2 q0 = __fmul2_rn(v[i], r2);
+    const float2 e = __ffma2_rn(ns2, q0, v[i]);
+    const float2 q = __ffma2_rn(e, r2, q0);
+    uint32_t d[2];
+    if constexpr (MODE == NNCFB_NF4) {
+      const float2 t = __ffma2_rn(q, f2(15.49f, 15.49f), f2(12582928.0f, 12582928.0f));
+      const float qq[2] = {q.x, q.y};
+      const uint32_t kk[2] = {__float_as_uint(t.x), __float_as_uint(t.y)};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float b = __shfl_sync(0xffffffffu, lut_bound, kk[h]);
+        const int base = __shfl_sync(0xffffffffu, lut_base, kk[h]);
+        d[h] = static_cast<uint32_t>(base + (qq[h] > b ? 1 : 0));
+      }
+    } else {
+      const float2 a = f2(fabsf(q.x), fabsf(q.y));
+      const float2 t = __ffma2_rn(a, f2(4.0f, 4.0f), f2(12582912.0f, 12582912.0f));
+      const float aa[2] = {a.x, a.y}, qq[2] = {q.x, q.y};
+      const uint32_t kk[2] = {__float_as_uint(t.x), __float_as_uint(t.y)};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float b = __shfl_sync(0xffffffffu, lut_bound, kk[h]);
+        const int base = __shfl_sync(0xffffffffu, lut_base, kk[h]);
+        const uint32_t idx = static_cast<uint32_t>(base + (aa[h] > b ? 1 : 0));
+        const uint32_t s8 = (__float_as_uint(qq[h]) >> 28) & 8u;
+        d[h] = idx | (s8 & (idx + 7u));  // sign bit only for non-zero magnitudes
+      }
+    }
+    acc = (acc * 16u + d[1]) * 16u + d[0];
+  }
+  return acc;
+}
+
 // =====================================================================================================
 // Batched row-group kernel: group_size = 8 * L * VPL (L lanes, VPL 16-byte vectors per lane; lane j
 // owns vectors j, j+L, ... of its group so that every warp load and store is fully coalesced).
@@ -252,6 +339,15 @@ __global__ void __launch_bounds__(256, 4) quant_rows_batch_kernel(const __grid_c
   const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t total_iters = b.iter_start[b.n_tensors];
   int lo = 0;  // tensor of the current iteration; iterations only move forward
+  float lut_bound = 0.0f;
+  int lut_base = 0;
+  if constexpr (MODE == NNCFB_NF4) {
+    lut_bound = kNf4LutBound[lane];
+    lut_base = kNf4LutBase[lane];
+  } else if constexpr (mode_is_fast_float(MODE)) {
+    lut_bound = kE2m1LutBound[lane];
+    lut_base = kE2m1LutBase[lane];
+  }
 
   for (int64_t it = warp; it < total_iters; it += n_warps) {
     while (b.iter_start[lo + 1] <= it) ++lo;
@@ -279,6 +375,25 @@ __global__ void __launch_bounds__(256, 4) quant_rows_batch_kernel(const __grid_c
       float mn, mx, s, r, zp;
       bool need_clamp;
       finish_minmax<SrcT>(m, mn, mx);
+      if constexpr (mode_is_fast_float(MODE)) {
+        int e8;
+        float_params<MODE>(mn, mx, s, r, e8);
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          float2 x[4];
+          unpack8_pairs(raw[p][v], x);
+          const uint32_t w = encode8_float<MODE>(x, s, r, lut_bound, lut_base);  // shuffles inside: all lanes
+          if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
+        }
+        if (valid && lig == 0) {
+          if (T.scale) T.scale[g] = s;
+          if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
+          if constexpr (MODE == NNCFB_MXFP4) {
+            if (T.e8m0) T.e8m0[g] = static_cast<uint8_t>(e8 + 127);
+          }
+        }
+        continue;
+      }
       int_params<MODE>(mn, mx, s, r, zp, need_clamp);
       bool clamp = false;
       if constexpr (mode_is_asym(MODE)) clamp = __any_sync(0xffffffffu, need_clamp);

@@ -96,14 +96,18 @@ struct FastClass {
 
 inline FastClass fast_class(const nncfb_quantize_args& p) {
   FastClass none{0, 0};
-  if (!mode_is_integer(p.mode) || p.inner != 1 || p.pre_scale || p.pre_zp || p.values_out || p.dq_out ||
-      p.sqerr_out || p.scale_e8m0_out || !p.scale_out || !p.codes_out)
+  const bool fast_float = mode_is_fast_float(p.mode);
+  if (!(mode_is_integer(p.mode) || fast_float) || p.inner != 1 || p.pre_scale || p.pre_zp || p.values_out ||
+      p.dq_out || p.sqerr_out || !p.codes_out)
     return none;
+  if (p.scale_e8m0_out && p.mode != NNCFB_MXFP4) return none;
+  if (!p.scale_out && !(p.mode == NNCFB_MXFP4 && p.scale_e8m0_out)) return none;
   if (mode_is_asym(p.mode) && !p.zp_out) return none;
   const bool four = mode_bits(p.mode) == 4;
   if (p.codes_format != (four ? NNCFB_CODES_NIBBLE : NNCFB_CODES_BYTE)) return none;
   if (!aligned16(p.weight) || !aligned16(p.codes_out)) return none;
   if (p.group_size == 128 || p.group_size == 64 || p.group_size == 32) return FastClass{1, p.group_size};
+  if (fast_float) return none;  // per-channel float modes use the general kernels
   if (p.group_size == p.reduce && p.reduce % 8 == 0 && p.reduce >= 512) return FastClass{2, p.reduce};
   return none;
 }
@@ -111,6 +115,12 @@ inline FastClass fast_class(const nncfb_quantize_args& p) {
 template <typename SrcT, int MODE>
 int launch_fast_mode(const FastBatch& b, FastClass cls, cudaStream_t stream) {
   const int sms = sm_count();
+  if constexpr (mode_is_fast_float(MODE)) {
+    if (cls.kind != 1) {
+      set_error("fast path: float modes support group sizes 32, 64 and 128 only");
+      return NNCFB_E_UNSUPPORTED;
+    }
+  }
   if (cls.kind == 1) {
     constexpr int U = 2;
     const int grid = static_cast<int>(std::max<int64_t>(
@@ -122,7 +132,7 @@ int launch_fast_mode(const FastBatch& b, FastClass cls, cudaStream_t stream) {
     } else {
       quant_rows_batch_kernel<SrcT, MODE, 4, 1, U><<<grid, 256, 0, stream>>>(b);
     }
-  } else {
+  } else if constexpr (!mode_is_fast_float(MODE)) {
     const int grid = static_cast<int>(std::max<int64_t>(
         1, std::min<int64_t>(b.iter_start[b.n_tensors], static_cast<int64_t>(sms) * 3)));
     const int64_t nvec = cls.group / 8;
@@ -146,6 +156,9 @@ int launch_fast_t(const FastBatch& b, int mode, FastClass cls, cudaStream_t stre
     case NNCFB_INT8_ASYM: return launch_fast_mode<SrcT, NNCFB_INT8_ASYM>(b, cls, stream);
     case NNCFB_INT4_SYM: return launch_fast_mode<SrcT, NNCFB_INT4_SYM>(b, cls, stream);
     case NNCFB_INT4_ASYM: return launch_fast_mode<SrcT, NNCFB_INT4_ASYM>(b, cls, stream);
+    case NNCFB_NF4: return launch_fast_mode<SrcT, NNCFB_NF4>(b, cls, stream);
+    case NNCFB_FP4: return launch_fast_mode<SrcT, NNCFB_FP4>(b, cls, stream);
+    case NNCFB_MXFP4: return launch_fast_mode<SrcT, NNCFB_MXFP4>(b, cls, stream);
     default: break;
   }
   set_error("fast path: unsupported mode %d", mode);

@@ -230,7 +230,8 @@ def test_full_size_properties(mode, gs):
 
 
 @pytest.mark.parametrize("mode,gs", [("int4_sym", 128), ("int4_asym", 128), ("int4_sym", 64), ("int4_asym", 32),
-                                     ("int8_asym", -1), ("int8_sym", -1), ("int8_sym", 128), ("int4_sym", -1)])
+                                     ("int8_asym", -1), ("int8_sym", -1), ("int8_sym", 128), ("int4_sym", -1),
+                                     ("nf4", 128), ("nf4", 32), ("mxfp4", 32), ("fp4", 64), ("fp4", 128)])
 @pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
 def test_batched_plan_matches_oracle(mode, gs, dtype):
     """One launch over a list of ragged tensors (the whole-model path) equals the oracle per tensor,
@@ -259,7 +260,12 @@ def test_batched_plan_matches_oracle(mode, gs, dtype):
         _eq(it.scale, ref.scale.reshape(-1), "scale")
         if cfg.is_asym_mode:
             _eq(it.zero_point, ref.zero_point.reshape(-1), "zp")
-        if cfg.num_bits == 4:
+        if not cfg.is_integer:
+            codes = O.nibble_code_nf4(ref.tensor) if mode == "nf4" else O.nibble_code_e2m1(ref.tensor)
+            _eq(it.packed, O.pack_uint4(codes).reshape(-1), "packed float codes")
+            if mode == "mxfp4":
+                _eq(it.scale_e8m0, O.e8m0_code(ref.scale).reshape(-1), "e8m0")
+        elif cfg.num_bits == 4:
             ref_packed = O.pack_int4(ref.tensor) if mode == "int4_sym" else O.pack_uint4(ref.tensor)
             _eq(it.packed, ref_packed.reshape(-1), "packed")
         else:
@@ -299,3 +305,35 @@ def test_extreme_scales_take_the_ieee_division_path():
         else:
             ref_packed = O.pack_int4(ref.tensor) if mode == "int4_sym" else O.pack_uint4(ref.tensor)
             _eq(plan.items[0].packed, ref_packed.reshape(-1), "packed")
+
+
+@pytest.mark.parametrize("mode", ["nf4", "fp4", "mxfp4"])
+def test_float_codes_at_and_next_to_every_decision_boundary(mode):
+    """Every decision boundary of the code book, the floats just below and above it, and the bucket edges
+    of the in-kernel lookup, with a group scale of exactly one, through the batched (storage) path."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200.pipeline import CompressionPlan
+
+    if mode == "nf4":
+        bounds, top = O.NF4_BOUNDS, 1.0
+        edges = (np.arange(0, 33) - 16.5) / np.float32(15.49)
+    else:
+        bounds, top = O.E2M1_BOUNDS, 6.0
+        edges = np.concatenate([(np.arange(0, 26) - 0.5) / 4.0, -(np.arange(0, 26) - 0.5) / 4.0])
+    pts = np.concatenate([bounds, np.nextafter(bounds, np.float32(9)), np.nextafter(bounds, np.float32(-9)),
+                          edges.astype(np.float32), np.nextafter(edges.astype(np.float32), np.float32(9)),
+                          np.float32([0.0, -0.0, top, -top, 1e-30, -1e-30])]).astype(np.float32)
+    pts = pts[np.abs(pts) <= top]
+    gs = 32 if mode == "mxfp4" else 128
+    rows = []
+    for i in range(0, len(pts), gs - 1):      # every group carries the value `top` so that its scale is one
+        chunk = pts[i:i + gs - 1]
+        rows.append(np.concatenate([chunk, np.full(gs - len(chunk), top, np.float32)]))
+    w = np.stack(rows)
+    ref = O.compress_weight(w, 1, mode, gs)
+    assert np.all(ref.scale == 1.0)
+    plan = CompressionPlan([("w", torch.from_numpy(w).cuda(), _cfg(mode, gs))])
+    plan.run(use_graph=False)
+    codes = O.nibble_code_nf4(ref.tensor) if mode == "nf4" else O.nibble_code_e2m1(ref.tensor)
+    _eq(plan.items[0].packed, O.pack_uint4(codes).reshape(-1), "packed")
