@@ -221,6 +221,20 @@ int nncfb_channel_stats(const void* x, int32_t dtype, int64_t tokens, int64_t ch
                         float* absmax_out, double* sumsq_out, void* stream);
 
 /*
+ * Decompression of stored weights in one pass: codes (nibble-packed for 4-bit modes, bytes for 8-bit) +
+ * per-group scale (+ zero point) -> n_elements values of out_dtype (NNCFB_F32 / F16 / BF16), groups of
+ * `group_size` consecutive elements (a multiple of 8).
+ *   integer modes: scale = fp16 [n_groups] (the decompressor's `_scale` buffer); zero_point = uint8 per group
+ *                  (INT8_ASYM) or nibble-packed in flat group order (INT4_ASYM), NULL for symmetric modes;
+ *                  arithmetic in fp16 exactly as the reference: (x.f16 - zp.f16) * scale.f16, then the cast;
+ *   NF4 / FP4:     scale = fp32 [n_groups];   MXFP4: scale = E8M0 bytes [n_groups].
+ * Replaces src/nncf/torch/quantization/layers.py:1334-1338,1364-1368,1406-1416,1453-1460 (the forward of the
+ * INT8/INT4 weight decompressors) and src/nncf/torch/quantization/quantize_functions.py:389-414,436-473.
+ */
+int nncfb_decompress(const void* codes, int32_t mode, int64_t n_elements, int64_t group_size, const void* scale,
+                     const void* zero_point, void* out, int32_t out_dtype, void* stream);
+
+/*
  * Nibble-pack n byte codes (n even) in flat order: out[i] = (in[2i] & 15) | (in[2i+1] << 4);
  * `add` is added to every code first (8 for signed int4 codes).
  * Replaces src/nncf/torch/quantization/quantize_functions.py:417-461 pack_uint4 / pack_int4.

@@ -15,5 +15,6 @@ from .config import CompressedWeight, WCTensorStatistic, WeightCompressionConfig
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is missing)
 from . import weight_lowering
 from .weight_lowering import compress_weight
+from .compress_api import Dataset, compress_weights
 
 __version__ = "0.1.0"

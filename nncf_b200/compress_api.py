@@ -1,0 +1,552 @@
+"""``compress_weights`` for torch models: the drop-in entry point.
+
+Mirrors ``nncf.compress_weights`` (src/nncf/quantization/quantize_model.py:396-696) and the
+orchestration of ``WeightCompression`` (src/nncf/quantization/algorithms/weight_compression/
+algorithm.py: option validation :140-295, defaults :74-137, which weights get the primary / backup
+precision :540-575 and :961-1088, mixed precision :622-650, group-size validation :652-780,
+algorithm order in apply_with_parameters :1127-1232, transform_model in torch_backend.py:424-485) for
+models made of ``nn.Linear`` and ``nn.Embedding`` layers.  The reference finds weights by tracing the
+model into a graph; here they are found as modules (in first-execution order when a dataset sample is
+available, else in registration order), which is the same set for transformer-style models.  All tensor
+work goes through the CUDA library; the per-weight loop is one batched launch (``CompressionPlan``).
+
+The stored result uses torch parametrizations: ``module.weight`` becomes a parametrized attribute whose
+stored tensor is the packed weight and whose parametrization is the decompressor module, so the model
+keeps running and ``state_dict()`` carries packed weights, fp16 scales and packed zero points.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable, Iterable, Optional
+
+import torch
+from torch import nn
+from torch.nn.utils import parametrize
+
+from .activation_stats import StatisticsCollector, channel_stats
+from .awq import AWQ
+from .config import CompressedWeight, WCTensorStatistic, WeightCompressionConfig, WeightCompressionParameters
+from .decompressors import (FloatCodebookWeightsDecompressor, INT4AsymmetricWeightsDecompressor,
+                            INT4SymmetricWeightsDecompressor, INT8AsymmetricWeightsDecompressor,
+                            INT8SymmetricWeightsDecompressor)
+from .errors import InvalidGroupSizeError, ParameterNotSupportedError, ValidationError
+from .gptq import GPTQ
+from .parameters import (AdvancedCompressionParameters, BackupMode, CompressionFormat, CompressWeightsMode,
+                         GroupSizeFallbackMode, SensitivityMetric)
+from .pipeline import CompressionPlan
+from .scale_estimation import ScaleEstimation
+from .weight_lowering import get_integer_quantization_error
+
+_M = CompressWeightsMode
+INT8_MODES = (_M.INT8_SYM, _M.INT8_ASYM)
+SUPPORTED_MODES = (_M.INT8_SYM, _M.INT8_ASYM, _M.INT4_SYM, _M.INT4_ASYM, _M.NF4, _M.MXFP4, _M.FP4)
+
+
+class Dataset:
+    """Iterable of calibration items with an optional transform, like nncf.Dataset
+    (src/nncf/data/dataset.py:18-136)."""
+
+    def __init__(self, data_source: Iterable, transform_func: Optional[Callable] = None):
+        self._data = data_source
+        self._transform = transform_func
+
+    def get_inference_data(self, indices=None):
+        for i, item in enumerate(self._data):
+            if indices is not None and i not in indices:
+                continue
+            yield self._transform(item) if self._transform else item
+
+
+def _run(model: nn.Module, item: Any) -> None:
+    if isinstance(item, dict):
+        model(**item)
+    elif isinstance(item, (tuple, list)):
+        model(*item)
+    else:
+        model(item)
+
+
+# --------------------------------------------------------------------------------------------------
+# validation and defaults
+# --------------------------------------------------------------------------------------------------
+def check_user_compression_configuration(mode, subset_size, dataset, ratio, group_size, all_layers, awq,
+                                         scale_estimation, gptq, lora_correction, sensitivity_metric, backup_mode,
+                                         compression_format, advanced_parameters) -> None:
+    """algorithm.py:140-295 and the torch-specific guards of quantize_model.py:497-533."""
+    if mode not in SUPPORTED_MODES:
+        msg = f"Torch backend does not support {mode.value} mode for weight compression."
+        raise ParameterNotSupportedError(msg)
+    if lora_correction:
+        msg = "Torch backend does not support the lora_correction option."
+        raise ParameterNotSupportedError(msg)
+    if compression_format != CompressionFormat.DQ:
+        msg = f"{compression_format.value} compression format is not supported: only the default DQ format is."
+        raise ParameterNotSupportedError(msg)
+    if advanced_parameters and advanced_parameters.statistics_path:
+        msg = "Torch does not support statistics caching."
+        raise ParameterNotSupportedError(msg)
+    if mode in INT8_MODES:
+        if (ratio and ratio != 1) or (group_size and group_size != -1):
+            msg = ("INT8 modes require per-channel quantization of all layers in 8 bit. "
+                   "Default values of `ratio` (1) and `group_size` (-1) cannot be overridden.")
+            raise ParameterNotSupportedError(msg)
+        unsupported = {"all_layers": all_layers, "sensitivity_metric": sensitivity_metric, "dataset": dataset,
+                       "awq": awq, "scale_estimation": scale_estimation, "gptq": gptq,
+                       "lora_correction": lora_correction, "backup_mode": backup_mode}
+        bad = [k for k, v in unsupported.items() if v is not None]
+        if bad:
+            msg = f"INT8 modes do not support {', '.join(bad)} option(s). Set them to None."
+            raise ParameterNotSupportedError(msg)
+    if ratio is not None and not (0 <= ratio <= 1):
+        msg = f"The ratio should be between 0 and 1, but ratio={ratio} is specified."
+        raise ValidationError(msg)
+    sizes = [subset_size]
+    if advanced_parameters:
+        sizes += [advanced_parameters.awq_params.subset_size, advanced_parameters.scale_estimation_params.subset_size,
+                  advanced_parameters.gptq_params.subset_size]
+    for size in sizes:
+        if size <= 0:
+            msg = f"The subset_size value should be positive, but subset_size={size} is given."
+            raise ValidationError(msg)
+    if ratio and dataset is None and sensitivity_metric is not None and \
+            sensitivity_metric != SensitivityMetric.WEIGHT_QUANTIZATION_ERROR:
+        msg = (f"Mixed precision selection with sensitivity metric={sensitivity_metric.value} "
+               "requires a dataset, but it's not provided.")
+        raise ValidationError(msg)
+    if mode == _M.MXFP4 and group_size not in (None, 32):
+        msg = f"MXFP4 and MXFP8_E4M3 types only support group size of 32, group size of {group_size} is given"
+        raise ValidationError(msg)
+    if (awq or scale_estimation or gptq) and dataset is None and not (awq and not scale_estimation and not gptq):
+        msg = "Scale estimation and GPTQ require a dataset."
+        raise ValidationError(msg)
+
+
+def get_weight_compression_configuration(mode, dataset, ratio, group_size, all_layers, awq, scale_estimation, gptq,
+                                         sensitivity_metric, backup_mode, advanced_parameters) -> dict:
+    """algorithm.py:74-137."""
+    if group_size is None:
+        group_size = -1 if mode in INT8_MODES else (32 if mode == _M.MXFP4 else 128)
+    if backup_mode is None:
+        backup_mode = BackupMode.INT8_ASYM  # MXFP8 / FP8 backups are served by the INT8 default here
+    if sensitivity_metric is None:
+        sensitivity_metric = (SensitivityMetric.WEIGHT_QUANTIZATION_ERROR if dataset is None
+                              else SensitivityMetric.MAX_ACTIVATION_VARIANCE)
+    return {"mode": mode, "ratio": ratio or 1, "group_size": group_size, "all_layers": all_layers or False,
+            "awq": awq or False, "scale_estimation": scale_estimation or False, "gptq": gptq or False,
+            "sensitivity_metric": sensitivity_metric, "backup_mode": backup_mode,
+            "advanced_parameters": advanced_parameters or AdvancedCompressionParameters()}
+
+
+def _backup_config(backup_mode: BackupMode) -> Optional[WeightCompressionConfig]:
+    """algorithm.py:577-603."""
+    if backup_mode == BackupMode.NONE:
+        return None
+    if backup_mode == BackupMode.INT8_SYM:
+        return WeightCompressionConfig(_M.INT8_SYM, -1)
+    return WeightCompressionConfig(_M.INT8_ASYM, -1)
+
+
+# --------------------------------------------------------------------------------------------------
+# weights of the model
+# --------------------------------------------------------------------------------------------------
+def _execution_order(model: nn.Module, sample: Any) -> dict:
+    """First-call order of the leaf modules during one forward pass."""
+    order: dict = {}
+    handles = []
+
+    def hook(mod, args):
+        order.setdefault(id(mod), len(order))
+
+    for m in model.modules():
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            handles.append(m.register_forward_pre_hook(hook))
+    try:
+        with torch.no_grad():
+            _run(model, sample)
+    finally:
+        for h in handles:
+            h.remove()
+    return order
+
+
+def get_weight_compression_parameters(model: nn.Module, ignored_scope: Optional[Iterable[str]] = None,
+                                      sample: Any = None) -> list[WeightCompressionParameters]:
+    """All Linear (matmul) and Embedding weights in execution order (algorithm.py:961-1088 for the
+    two layer kinds handled here; reduction axis = last for both, src/nncf/torch/model_graph_manager.py:350-383)."""
+    ignored = set(ignored_scope or [])
+    order = _execution_order(model, sample) if sample is not None else {}
+    params = []
+    for idx, (name, m) in enumerate(model.named_modules()):
+        if not isinstance(m, (nn.Linear, nn.Embedding)) or name in ignored:
+            continue
+        if m.weight.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            continue
+        params.append(WeightCompressionParameters(
+            weight_name=name, module=m, weight_attr="weight", reduction_axes=(1,),
+            is_embedding=isinstance(m, nn.Embedding), order=order.get(id(m), 10 ** 9 + idx)))
+    params.sort(key=lambda p: p.order)
+    return params
+
+
+def _ratio_defining(params, mode, all_layers):
+    """algorithm.py:540-575."""
+    if mode in INT8_MODES:
+        return list(params)
+    rd = [p for p in params if not p.is_embedding]
+    if not all_layers:
+        rd = rd[:-1]
+    if all_layers:
+        rd += [p for p in params if p.is_embedding]
+    return rd
+
+
+# --------------------------------------------------------------------------------------------------
+# statistics
+# --------------------------------------------------------------------------------------------------
+class _ActivationStats:
+    """Forward pre-hooks on the Linear layers: per-sample channel means (AWQ / ScaleEstimation) and the
+    mixed-precision metrics (collectors.py:519-540, :924-936), all from one pass over each activation."""
+
+    def __init__(self, params, subset_size: int, metric: Optional[SensitivityMetric]):
+        self.collectors = {p.weight_name: StatisticsCollector(-1, subset_size) for p in params if not p.is_embedding}
+        self.metric = metric
+        self.metric_values = {p.weight_name: [] for p in params if not p.is_embedding}
+        self.hawq = {p.weight_name: 0.0 for p in params if not p.is_embedding}
+        self._handles = []
+        for p in params:
+            if p.is_embedding:
+                continue
+            self._handles.append(p.module.register_forward_pre_hook(self._make_hook(p.weight_name)))
+
+    def _make_hook(self, name):
+        def hook(mod, args):
+            x = args[0]
+            col = self.collectors[name]
+            if col.num_samples is not None and len(col.stat.mean_values) >= col.num_samples:
+                return
+            col.register(x)
+            if self.metric in (SensitivityMetric.MEAN_ACTIVATION_VARIANCE, SensitivityMetric.MAX_ACTIVATION_VARIANCE):
+                # variance over the sequence axis (-2) per batch row, then mean / max
+                vals = [channel_stats(row, -1, ("var",))["var"] for row in x.reshape(-1, x.shape[-2], x.shape[-1])]
+                v = torch.stack(vals)
+                self.metric_values[name].append(float(v.mean()) if self.metric == SensitivityMetric.MEAN_ACTIVATION_VARIANCE
+                                                else float(v.max()))
+            elif self.metric == SensitivityMetric.MEAN_ACTIVATION_MAGNITUDE:
+                vals = [channel_stats(row, -1, ("absmax",))["absmax"] for row in
+                        x.reshape(-1, x.shape[-2], x.shape[-1])]
+                self.metric_values[name].append(float(torch.stack(vals).mean()))
+            elif self.metric == SensitivityMetric.HESSIAN_INPUT_ACTIVATION:
+                ss = float(channel_stats(x, -1, ("sumsq",))["sumsq"].sum())
+                self.hawq[name] = (self.hawq[name] + ss) / x.numel()
+                self.metric_values[name].append(0.0)
+        return hook
+
+    def remove(self):
+        for h in self._handles:
+            h.remove()
+
+    def statistics(self) -> dict:
+        return {k: c.stat for k, c in self.collectors.items() if c.stat.mean_values}
+
+    def activation_score(self, name: str) -> float:
+        n = max(len(self.metric_values[name]), 1)
+        if self.metric == SensitivityMetric.HESSIAN_INPUT_ACTIVATION:
+            return self.hawq[name] * 2 / n
+        return sum(self.metric_values[name]) / n
+
+
+# --------------------------------------------------------------------------------------------------
+# AWQ pattern: Linear -> (elementwise multiply) -> Linear
+# --------------------------------------------------------------------------------------------------
+def find_mul_merge_pairs(model: nn.Module, sample: Any, targets: dict) -> dict:
+    """{target name: merge module} for every target Linear whose input is the product of a multiply that
+    directly consumes another Linear's output (the MatMul -> Multiply -> MatMul pattern of
+    awq_patterns.py:20-43, e.g. up_proj -> (* act(gate)) -> down_proj).  Found by following tensor
+    identities through one forward pass."""
+    from torch.overrides import TorchFunctionMode
+
+    produced_by: dict = {}   # id(output tensor) -> Linear module
+    mul_inputs: dict = {}    # id(mul output) -> ids of its tensor operands
+    keep = []                # keeps every seen tensor alive so that ids stay unique
+    pairs: dict = {}
+    by_module = {id(m): n for n, m in targets.items()}
+
+    class Tracer(TorchFunctionMode):
+        def __torch_function__(self, func, types, args=(), kwargs=None):
+            out = func(*args, **(kwargs or {}))
+            if getattr(func, "__name__", "") in ("mul", "__mul__", "multiply", "__rmul__") and isinstance(out, torch.Tensor):
+                ids = [id(a) for a in args if isinstance(a, torch.Tensor)]
+                mul_inputs[id(out)] = ids
+                keep.extend([out, *[a for a in args if isinstance(a, torch.Tensor)]])
+            return out
+
+    handles = []
+
+    def post(mod, args, out):
+        if isinstance(out, torch.Tensor):
+            produced_by[id(out)] = mod
+            keep.append(out)
+
+    def pre(mod, args):
+        x = args[0]
+        name = by_module.get(id(mod))
+        if name is None or not isinstance(x, torch.Tensor):
+            return
+        for src in mul_inputs.get(id(x), []):
+            merge = produced_by.get(src)
+            if merge is not None and merge is not mod:
+                pairs.setdefault(name, merge)
+
+    for m in model.modules():
+        if isinstance(m, nn.Linear):
+            handles.append(m.register_forward_hook(post))
+            handles.append(m.register_forward_pre_hook(pre))
+    try:
+        with torch.no_grad(), Tracer():
+            _run(model, sample)
+    finally:
+        for h in handles:
+            h.remove()
+    return pairs
+
+
+# --------------------------------------------------------------------------------------------------
+# the entry point
+# --------------------------------------------------------------------------------------------------
+def compress_weights(
+    model: nn.Module,
+    mode: CompressWeightsMode = CompressWeightsMode.INT8_ASYM,
+    ratio: Optional[float] = None,
+    group_size: Optional[int] = None,
+    ignored_scope: Optional[Iterable[str]] = None,
+    all_layers: Optional[bool] = None,
+    dataset: Optional[Dataset] = None,
+    sensitivity_metric: Optional[SensitivityMetric] = None,
+    *,
+    subset_size: int = 128,
+    awq: Optional[bool] = None,
+    scale_estimation: Optional[bool] = None,
+    gptq: Optional[bool] = None,
+    lora_correction: Optional[bool] = None,
+    backup_mode: Optional[BackupMode] = None,
+    compression_format: CompressionFormat = CompressionFormat.DQ,
+    advanced_parameters: Optional[AdvancedCompressionParameters] = None,
+) -> nn.Module:
+    """Compress the weights of ``model`` (CUDA, modified in place and returned).  Same keyword API and
+    defaults as ``nncf.compress_weights``; ``ignored_scope`` is a collection of module names."""
+    mode = CompressWeightsMode(mode)
+    check_user_compression_configuration(mode, subset_size, dataset, ratio, group_size, all_layers, awq,
+                                         scale_estimation, gptq, lora_correction, sensitivity_metric, backup_mode,
+                                         compression_format, advanced_parameters)
+    cfg = get_weight_compression_configuration(mode, dataset, ratio, group_size, all_layers, awq, scale_estimation,
+                                               gptq, sensitivity_metric, backup_mode, advanced_parameters)
+    adv: AdvancedCompressionParameters = cfg["advanced_parameters"]
+    items = list(dataset.get_inference_data()) if dataset is not None else []
+    sample = items[0] if items else None
+    params = get_weight_compression_parameters(model, ignored_scope, sample)
+    if not params:
+        return model
+    if any(not p.weight.is_cuda for p in params):
+        msg = "nncf_b200.compress_weights needs the model on a CUDA device: there is no CPU fallback"
+        raise ValueError(msg)
+
+    primary = WeightCompressionConfig(mode, cfg["group_size"])
+    backup = _backup_config(cfg["backup_mode"])
+    ratio_defining = _ratio_defining(params, mode, cfg["all_layers"])
+    rd_names = {p.weight_name for p in ratio_defining}
+    for p in params:
+        p.compression_config = primary if p.weight_name in rd_names else backup
+
+    # group-size fallback / validation (algorithm.py:652-780)
+    if primary.group_size != -1:
+        failed = [p for p in ratio_defining if p.weight_shape[1] % primary.group_size != 0]
+        fb = adv.group_size_fallback_mode
+        for p in failed:
+            if fb == GroupSizeFallbackMode.IGNORE:
+                p.compression_config = None
+            elif fb == GroupSizeFallbackMode.ADJUST:
+                gs = primary.group_size
+                while gs >= adv.min_adjusted_group_size and p.weight_shape[1] % gs != 0:
+                    gs //= 2
+                p.compression_config = (WeightCompressionConfig(mode, gs) if gs >= adv.min_adjusted_group_size
+                                        and p.weight_shape[1] % gs == 0 else backup)
+        still = [p for p in ratio_defining if p.compression_config is not None and p.compression_config.group_size != -1
+                 and p.weight_shape[1] % p.compression_config.group_size != 0]
+        if still:
+            names = "\n\t".join(f'"{p.weight_name}" (channel size: {p.weight_shape[1]})' for p in still)
+            msg = (f"Failed to apply group-wise quantization with group size value {primary.group_size}.\n"
+                   "Ensure that the group size is divisible by the channel size, or consider setting "
+                   "`group_size_fallback_mode` to IGNORE or ADJUST. Failed nodes:\n\t" + names)
+            raise InvalidGroupSizeError(msg)
+        ratio_defining = [p for p in ratio_defining if p.compression_config is not None]
+
+    # statistics (one calibration pass, hooks on every Linear input)
+    need_stats = bool(items) and (cfg["awq"] or cfg["scale_estimation"] or
+                                  (cfg["ratio"] < 1 and cfg["sensitivity_metric"] != SensitivityMetric.WEIGHT_QUANTIZATION_ERROR))
+    stats: dict = {}
+    act = None
+    if need_stats:
+        metric = cfg["sensitivity_metric"] if cfg["ratio"] < 1 else None
+        act = _ActivationStats(params, subset_size, metric)
+        try:
+            with torch.no_grad():
+                for item in items[:subset_size]:
+                    _run(model, item)
+        finally:
+            act.remove()
+        stats = act.statistics()
+
+    # mixed precision (algorithm.py:622-650, mixed_precision.py:71-100)
+    if cfg["ratio"] < 1 and ratio_defining and mode not in INT8_MODES:
+        scores = []
+        metric = cfg["sensitivity_metric"]
+        for p in ratio_defining:
+            if metric == SensitivityMetric.HESSIAN_INPUT_ACTIVATION:
+                wscore = get_integer_quantization_error(p.weight, 1, WeightCompressionConfig(), "frobenius")
+            else:
+                err = get_integer_quantization_error(p.weight, 1, WeightCompressionConfig(), "max_mean")
+                wscore = 1 / (err + torch.finfo(p.weight.dtype).eps)
+            if metric == SensitivityMetric.WEIGHT_QUANTIZATION_ERROR:
+                scores.append(wscore)
+            elif p.is_embedding:
+                scores.append(0.0)
+            else:
+                scores.append(wscore * act.activation_score(p.weight_name))
+        total = sum(p.num_weights for p in ratio_defining)
+        n4 = 0
+        chosen = set()
+        for i in sorted(range(len(scores)), key=lambda k: scores[k]):
+            p = ratio_defining[i]
+            if (n4 + p.num_weights) / total >= cfg["ratio"]:
+                break
+            chosen.add(p.weight_name)
+            n4 += p.num_weights
+        for p in ratio_defining:
+            if p.weight_name not in chosen:
+                p.compression_config = backup
+
+    active = [p for p in params if p.compression_config is not None]
+    precomputed: dict[str, CompressedWeight] = {}
+
+    # AWQ (awq.py:124-241): Linear -> multiply -> Linear pairs, 4-bit targets only
+    if cfg["awq"] and sample is not None:
+        four_bit = {p.weight_name: p.module for p in active if p.compression_config.num_bits == 4 and not p.is_embedding}
+        pairs = find_mul_merge_pairs(model, sample, four_bit)
+        algo = AWQ(adv.awq_params.subset_size, adv.awq_params.percent_to_apply, adv.awq_params.alpha_min,
+                   adv.awq_params.alpha_max, adv.awq_params.steps, adv.awq_params.prefer_data_aware_scaling)
+        by_module = {id(p.module): p for p in params}
+        scales = {}
+        for p in active:
+            merge = pairs.get(p.weight_name)
+            if merge is None or p.weight_name not in stats:
+                continue
+            mp = by_module.get(id(merge))
+            scales[p.weight_name] = algo.apply_to_pair(p, p.module.weight, stats[p.weight_name], merge.weight,
+                                                       stats.get(mp.weight_name) if mp is not None else None)
+        algo.update_statistics(stats, scales)
+
+    # GPTQ (gptq.py:82-171) or ScaleEstimation (scale_estimation.py:97-158)
+    if cfg["gptq"]:
+        g = GPTQ(adv.gptq_params.damp_percent, adv.gptq_params.block_size, adv.gptq_params.subset_size)
+        for p in active:
+            if p.is_embedding or p.compression_config.mode in INT8_MODES:
+                continue
+            H = _layer_hessian(model, p.module, items[: adv.gptq_params.subset_size], g)
+            w = p.weight.data.float().contiguous()
+            q, sc, zp = g._quantize_weights(p, H, w)
+            p.module.weight.data = q.to(p.weight.dtype)
+            precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
+    elif cfg["scale_estimation"]:
+        se = adv.scale_estimation_params
+        algo = ScaleEstimation(se.subset_size, se.initial_steps, se.scale_steps, se.weight_penalty)
+        precomputed.update({k: v for k, v in algo.apply([p for p in active if not p.is_embedding], stats).items()
+                            if v.scale is not None})
+
+    _transform_model(active, precomputed)
+    return model
+
+
+def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ) -> torch.Tensor:
+    """Hessian of one Linear's input over the calibration items, with every previously processed layer already
+    holding its quantised weight (the semantics of the reference's layer-wise engine,
+    src/nncf/quantization/algorithms/layerwise/openvino_iterator.py:183-231).  Activations are consumed as
+    they appear; nothing is stored."""
+    C = module.in_features
+    H = torch.zeros(C, C, dtype=torch.float32, device=module.weight.device)
+    state = {"n": 0}
+
+    class _Stop(Exception):
+        pass
+
+    def hook(mod, args):
+        x = args[0]
+        batch = x.shape[0] if x.ndim == 3 else 1
+        state["n"] = g.accumulate_hessian(H, x, state["n"], batch)
+        raise _Stop
+
+    h = module.register_forward_pre_hook(hook)
+    try:
+        with torch.no_grad():
+            for item in items:
+                try:
+                    _run(model, item)
+                except _Stop:
+                    pass
+    finally:
+        h.remove()
+    return H
+
+
+def _make_decompressor(p: WeightCompressionParameters, item) -> nn.Module:
+    cfg = p.compression_config
+    w = p.weight
+    out_ch, in_ch = w.shape
+    gs = cfg.group_size if cfg.group_size != -1 else in_ch
+    G = in_ch // gs
+    if cfg.num_bits == 8:
+        pshape = (out_ch, 1)
+        if cfg.mode == _M.INT8_ASYM:
+            return INT8AsymmetricWeightsDecompressor(item.scale.reshape(pshape), item.zero_point.reshape(pshape), w.dtype)
+        return INT8SymmetricWeightsDecompressor(item.scale.reshape(pshape), w.dtype)
+    grouped = (out_ch, G, gs) if cfg.group_size != -1 else (out_ch, in_ch)
+    pshape = (out_ch, G, 1) if cfg.group_size != -1 else (out_ch, 1)
+    if cfg.mode == _M.INT4_SYM:
+        return INT4SymmetricWeightsDecompressor(item.scale.reshape(pshape), grouped, tuple(w.shape), w.dtype)
+    if cfg.mode == _M.INT4_ASYM:
+        return INT4AsymmetricWeightsDecompressor(item.scale.reshape(pshape), item.zero_point.reshape(pshape), grouped,
+                                                 tuple(w.shape), w.dtype)
+    scale = item.scale_e8m0.reshape(pshape) if cfg.mode == _M.MXFP4 else item.scale.reshape(pshape)
+    return FloatCodebookWeightsDecompressor(cfg.mode, scale, grouped, tuple(w.shape), w.dtype)
+
+
+def _transform_model(active: list, precomputed: dict) -> None:
+    """torch_backend.py:424-485: compress every weight and install its decompressor.  Weights without
+    precomputed parameters go through one batched launch; the others through compress_weight."""
+    from .weight_lowering import compress_weight
+
+    plain = [p for p in active if p.weight_name not in precomputed]
+    results = {}
+    if plain:
+        plan = CompressionPlan([(p.weight_name, p.weight.data.contiguous(), p.compression_config) for p in plain])
+        plan.run(use_graph=False)
+        for p, it in zip(plain, plan.items):
+            results[p.weight_name] = it
+    for p in active:
+        if p.weight_name in precomputed:
+            cw = compress_weight(p.weight.data, p.reduction_axes, p.compression_config, precomputed[p.weight_name], pack=True)
+
+            class _It:
+                pass
+
+            it = _It()
+            it.packed, it.scale, it.zero_point, it.scale_e8m0 = cw.packed, cw.scale, cw.zero_point, cw.scale_e8m0
+            results[p.weight_name] = it
+    for p in active:
+        it = results[p.weight_name]
+        dec = _make_decompressor(p, it)
+        four = p.compression_config.num_bits == 4
+        packed = it.packed.reshape(-1, 1) if four else it.packed.reshape(p.weight.shape)
+        mod = p.module
+        mod.weight.requires_grad_(False)
+        mod.weight.data = packed
+        parametrize.register_parametrization(mod, "weight", dec, unsafe=True)

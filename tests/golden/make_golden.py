@@ -375,6 +375,7 @@ def gen_gptq(out: dict):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference/src", help="path to the reference's src/ directory")
+    ap.add_argument("groups", nargs="*", help="fixture groups to regenerate (default: all)")
     args = ap.parse_args()
     _setup(args.reference)
     groups = {
@@ -384,7 +385,11 @@ def main():
         "scale_estimation": gen_scale_estimation,
         "awq": gen_awq,
         "gptq": gen_gptq,
+        "api": gen_api,
     }
+    only = [a for a in sys.argv[1:] if a in groups]
+    if only:
+        groups = {k: v for k, v in groups.items() if k in only}
     for fname, fn in groups.items():
         data: dict = {}
         fn(data)
@@ -392,6 +397,40 @@ def main():
         np.savez_compressed(path, **{k.replace("/", "|"): v for k, v in data.items()})
         print(f"{path.name}: {len(data)} arrays, {path.stat().st_size / 1024:.0f} KiB")
 
+
+
+def gen_api(out: dict):
+    """nncf.compress_weights end to end on a toy Llama-like torch model (CPU): packed weights and
+    decompressor buffers per layer."""
+    import torch
+
+    import nncf
+    from models import API_CASES, TinyGatedLM, calibration_ids
+
+    names = []
+    for name, kwargs, use_ds in API_CASES:
+        model = TinyGatedLM()
+        ids = calibration_ids()
+        kw = dict(kwargs)
+        kw["mode"] = nncf.CompressWeightsMode(kw["mode"])
+        if "sensitivity_metric" in kw:
+            kw["sensitivity_metric"] = nncf.SensitivityMetric(kw["sensitivity_metric"])
+        if kw.get("awq"):
+            kw["advanced_parameters"] = nncf.AdvancedCompressionParameters(
+                awq_params=nncf.AdvancedAWQParameters(percent_to_apply=0.05))
+        ds = nncf.Dataset(ids)
+        # the torch backend traces the model with a dataset item even when the algorithm is data-free
+        cm = nncf.compress_weights(model, dataset=ds if use_ds else None, **kw) if use_ds else \
+            nncf.compress_weights(nncf.torch.wrap_model(model, example_input=ids[0], trace_parameters=True), **kw)
+        sd = cm.state_dict()
+        key = f"api/{name}"
+        names.append(key)
+        for k, v in sd.items():
+            out[f"{key}/{k}"] = _np(v)
+        out[key + "/keys"] = np.array(list(sd.keys()))
+        with torch.no_grad():
+            out[key + "/logits"] = _np(cm(ids[0]))
+    out["api/index"] = np.array(names)
 
 if __name__ == "__main__":
     main()

@@ -1,0 +1,161 @@
+"""``nncf_b200.compress_weights`` on a toy Llama-like torch model against the state dict that the
+reference's ``nncf.compress_weights`` produced for the same seeded model (tests/golden/api.npz).
+
+Data-free cases must match bit for bit (packed weights, fp16 scales, packed zero points, which layers got
+which precision).  Data-aware cases take their statistics from a forward pass on the GPU whose fp32
+matmuls differ from the reference's CPU pass in the last bits, so scales are compared with a tolerance and
+the model outputs against the reference's outputs."""
+
+import numpy as np
+import pytest
+import torch
+from conftest import golden
+from models import API_CASES, TinyGatedLM, calibration_ids
+
+pytestmark = pytest.mark.gpu
+
+LAYERS = ["embed", "blocks.0.q", "blocks.0.gate", "blocks.0.up", "blocks.0.down", "blocks.1.q", "blocks.1.gate",
+          "blocks.1.up", "blocks.1.down", "head"]
+
+
+def _compress(kwargs, use_ds):
+    import nncf_b200 as nb
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    model = TinyGatedLM().cuda()
+    ids = [i.cuda() for i in calibration_ids()]
+    kw = dict(kwargs)
+    kw["mode"] = nb.CompressWeightsMode(kw["mode"])
+    if "sensitivity_metric" in kw:
+        kw["sensitivity_metric"] = nb.SensitivityMetric(kw["sensitivity_metric"])
+    if kw.get("awq"):
+        kw["advanced_parameters"] = nb.AdvancedCompressionParameters(awq_params=nb.AdvancedAWQParameters(percent_to_apply=0.05))
+    # the reference needs a dataset item for tracing in every case; here it only fixes the layer order
+    return nb.compress_weights(model, dataset=nb.Dataset(ids) if use_ds else None, **kw), ids
+
+
+def _ref(g, key, layer, what):
+    k = f"{key}/__nncf_hooks.post_hooks.{layer.replace('.', ':')}:weight__0.0.{what}"
+    return g[k] if k in g else None
+
+
+@pytest.mark.parametrize("case", API_CASES, ids=[c[0] for c in API_CASES])
+def test_compress_weights_matches_reference_state_dict(case):
+    name, kwargs, use_ds = case
+    g = golden("api")
+    key = f"api/{name}"
+    model, ids = _compress(kwargs, use_ds)
+    sd = model.state_dict()
+    exact = not (kwargs.get("awq") or kwargs.get("scale_estimation") or "sensitivity_metric" in kwargs)
+    mism, total = 0, 0
+    for layer in LAYERS:
+        ref_w = g[f"{key}/{layer}.weight"]
+        got_w = sd[f"{layer}.parametrizations.weight.original"].cpu().numpy()
+        assert got_w.shape == ref_w.shape and got_w.dtype == ref_w.dtype, f"{layer}: precision assignment differs"
+        ref_s = _ref(g, key, layer, "_scale")
+        got_s = sd[f"{layer}.parametrizations.weight.0._scale"].cpu().numpy()
+        assert got_s.shape == ref_s.shape and got_s.dtype == np.float16
+        ref_z = _ref(g, key, layer, "_zero_point")
+        got_z = sd.get(f"{layer}.parametrizations.weight.0._zero_point")
+        assert (ref_z is None) == (got_z is None)
+        if exact:
+            np.testing.assert_array_equal(got_w, ref_w, err_msg=layer)
+            np.testing.assert_array_equal(got_s, ref_s, err_msg=layer)
+            if ref_z is not None:
+                np.testing.assert_array_equal(got_z.cpu().numpy(), ref_z, err_msg=layer)
+        else:
+            np.testing.assert_allclose(got_s.astype(np.float32), ref_s.astype(np.float32), rtol=2e-2, atol=1e-4)
+            mism += int(np.sum(got_w != ref_w))
+            total += got_w.size
+    if not exact:
+        assert mism / total < 0.05, f"{mism}/{total} packed bytes differ"
+    with torch.no_grad():
+        out = model(ids[0]).float().cpu().numpy()
+    ref_out = g[key + "/logits"]
+    tol = 1e-5 if exact else 3e-2
+    assert np.linalg.norm(out - ref_out) / np.linalg.norm(ref_out) < tol
+
+
+def test_nf4_and_mxfp4_models_run_and_stay_close_to_the_original():
+    """Modes the reference's torch backend rejects: the compressed model must run and approximate the original."""
+    import nncf_b200 as nb
+
+    ids = [i.cuda() for i in calibration_ids()]
+    with torch.no_grad():
+        base = TinyGatedLM().cuda()(ids[0])
+    for mode, gs in (("nf4", 16), ("mxfp4", 32), ("fp4", 16)):
+        model = nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode(mode), group_size=gs)
+        with torch.no_grad():
+            out = model(ids[0])
+        rel = float((out - base).norm() / base.norm())
+        assert rel < 0.25, (mode, rel)
+        assert model.blocks[0].q.parametrizations.weight.original.dtype == torch.uint8
+
+
+def test_invalid_options_raise_like_the_reference():
+    import nncf_b200 as nb
+
+    m = TinyGatedLM().cuda()
+    with pytest.raises(nb.ParameterNotSupportedError):
+        nb.compress_weights(m, mode=nb.CompressWeightsMode.INT8_ASYM, group_size=64)
+    with pytest.raises(nb.ParameterNotSupportedError):
+        nb.compress_weights(m, mode=nb.CompressWeightsMode.INT8_SYM, awq=True)
+    with pytest.raises(nb.ValidationError):
+        nb.compress_weights(m, mode=nb.CompressWeightsMode.INT4_SYM, ratio=1.5)
+    with pytest.raises(nb.ValidationError):
+        nb.compress_weights(m, mode=nb.CompressWeightsMode.MXFP4, group_size=64)
+    with pytest.raises(nb.InvalidGroupSizeError):
+        nb.compress_weights(m, mode=nb.CompressWeightsMode.INT4_SYM, group_size=24)
+    with pytest.raises(nb.ParameterNotSupportedError):
+        nb.compress_weights(m, mode=nb.CompressWeightsMode.INT4_SYM, lora_correction=True)
+
+
+def test_gptq_model_level_reduces_output_error():
+    """GPTQ through the model API: output error on the calibration data must not exceed plain rounding's."""
+    import nncf_b200 as nb
+
+    ids = [i.cuda() for i in calibration_ids(n=8, seq=32)]
+    with torch.no_grad():
+        base = torch.cat([TinyGatedLM().cuda()(i) for i in ids])
+    errs = {}
+    for use_gptq in (False, True):
+        model = nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode.INT4_SYM, group_size=16,
+                                    dataset=nb.Dataset(ids), gptq=use_gptq or None,
+                                    advanced_parameters=nb.AdvancedCompressionParameters(
+                                        gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.1, subset_size=8)))
+        with torch.no_grad():
+            out = torch.cat([model(i) for i in ids])
+        errs[use_gptq] = float((out - base).norm() / base.norm())
+    assert errs[True] < errs[False] * 1.05, errs
+
+
+@pytest.mark.parametrize("mode,gs", [("int4_sym", 128), ("int4_asym", 64), ("int8_asym", -1), ("int8_sym", -1),
+                                     ("nf4", 128), ("mxfp4", 32)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_decompress_kernel_matches_oracle(mode, gs, dtype):
+    """nncfb_decompress against the reference's fp16 decompression arithmetic restated by the oracle."""
+    from oracle import wc_oracle as O
+
+    import nncf_b200 as nb
+    from nncf_b200 import weight_lowering as wl
+    from nncf_b200.compress_api import _make_decompressor
+    from nncf_b200.config import WeightCompressionParameters
+
+    gen = torch.Generator().manual_seed(9)
+    lin = torch.nn.Linear(512, 96, bias=False)
+    lin.weight.data = (torch.randn(96, 512, generator=gen) * 0.05)
+    lin = lin.cuda().to(dtype)
+    cfg = nb.WeightCompressionConfig(nb.CompressWeightsMode(mode), gs)
+    p = WeightCompressionParameters("l", lin, "weight", (1,), cfg)
+    cw = wl.compress_weight(lin.weight.data, 1, cfg, pack=True)
+    dec = _make_decompressor(p, cw)
+    got = dec(cw.packed).float().cpu().numpy()
+    w_np = lin.weight.data.float().cpu().numpy()
+    ref = O.compress_weight(w_np if dtype != torch.float16 else lin.weight.data.cpu().numpy(), 1, mode, gs)
+    if O.is_integer(mode):
+        s16 = ref.scale.astype(np.float16)
+        dq = O.decompress_asymmetric(ref.tensor, s16, ref.zero_point) if O.is_asym(mode) else O.decompress_symmetric(ref.tensor, s16)
+        exp = torch.from_numpy(dq.astype(np.float32)).to(dtype).float().numpy().reshape(96, 512)
+    else:
+        exp = torch.from_numpy((ref.tensor * ref.scale).astype(np.float32)).to(dtype).float().numpy().reshape(96, 512)
+    np.testing.assert_array_equal(got, exp)
