@@ -248,6 +248,55 @@ def run_gptq_workload(args, device):
     print(json.dumps(out), flush=True)
 
 
+def run_data_aware_workload(args, device):
+    """ScaleEstimation and AWQ at Llama-3-8B layer shapes (config: INT4_ASYM g128, AWQ subset 32 / 100 alpha
+    steps, ScaleEstimation subset 64 / 5 + 5 steps, statistics synthetic with 1 % outlier channels x20),
+    extrapolated to the 32 layers of the model."""
+    from nncf_b200 import CompressWeightsMode, WCTensorStatistic, WeightCompressionConfig
+    from nncf_b200.awq import AWQ, make_wp
+    from nncf_b200.scale_estimation import ScaleEstimation
+
+    cfg = WeightCompressionConfig(CompressWeightsMode.INT4_ASYM, 128)
+    gen = torch.Generator(device=device).manual_seed(2)
+
+    def stats(hidden, n=128):
+        outl = 1 + 19 * (torch.rand(hidden, device=device, generator=gen) < 0.01)
+        means = [(torch.randn(hidden, device=device, generator=gen) * outl).to(torch.bfloat16) for _ in range(n)]
+        return WCTensorStatistic(means, [(1, 512, hidden)] * n)
+
+    def timed(fn, reps=3):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps * 1e3
+
+    shapes = {"q_proj": (4096, 4096), "k_proj": (1024, 4096), "gate_proj": (14336, 4096), "down_proj": (4096, 14336)}
+    if args.profile_case:
+        shapes = {"k_proj": (1024, 4096)}
+    se_ms, st = {}, {4096: stats(4096), 14336: stats(14336)}
+    for name, (o, i) in shapes.items():
+        w = (torch.randn(o, i, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        se_ms[name] = round(timed(lambda: ScaleEstimation.calculate_quantization_params(st[i], w, (1,), cfg, -1, 64, 5, 5)), 3)
+    out = {"metric": "data_aware_seconds_per_8b_model", "unit": "s", "higher_is_better": False, "n_gpus": 1,
+           "data": "synthetic", "dtype": "f32",
+           "config": {"workload": "INT4_ASYM g128 ScaleEstimation (64 samples, 5+5 steps) on all 7 matrices per layer and "
+                                  "AWQ (32 samples, 100 alpha steps) on down_proj, Llama-3-8B shapes, x32 layers"},
+           "scale_estimation_ms": se_ms}
+    if not args.profile_case:
+        wd = (torch.randn(4096, 14336, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        wu = (torch.randn(14336, 4096, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        algo = AWQ()
+        out["awq_down_proj_ms"] = round(timed(lambda: algo._data_aware_step(make_wp(cfg), wd, st[14336], -1, wu, st[4096])), 3)
+        per_layer = 2 * se_ms["q_proj"] + 2 * se_ms["k_proj"] + 2 * se_ms["gate_proj"] + se_ms["down_proj"] + out["awq_down_proj_ms"]
+        out["value"] = round(32 * per_layer / 1e3, 3)
+        n_w = 32 * (2 * 4096 * 4096 + 2 * 1024 * 4096 + 3 * 14336 * 4096)
+        out["source_GBps"] = round(n_w * 2 / (32 * per_layer * 1e-3) / 1e9, 1)
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -258,7 +307,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a graph")
-    ap.add_argument("--workload", default="compress", choices=["compress", "gptq"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "data_aware"],
                     help="compress: the headline metric (default); gptq: the secondary GPTQ metric")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profilers: one decoder layer, no e2e / cpu arm, 1 warm-up, 1 step")
@@ -277,9 +326,9 @@ def main():
     torch.cuda.set_device(device)
     import torch.distributed as dist
 
-    if args.workload == "gptq":
+    if args.workload in ("gptq", "data_aware"):
         if rank == 0:
-            run_gptq_workload(args, device)
+            (run_gptq_workload if args.workload == "gptq" else run_data_aware_workload)(args, device)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
