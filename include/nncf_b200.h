@@ -227,7 +227,7 @@ int nncfb_channel_stats(const void* x, int32_t dtype, int64_t tokens, int64_t ch
  *   integer modes: scale = fp16 [n_groups] (the decompressor's `_scale` buffer); zero_point = uint8 per group
  *                  (INT8_ASYM) or nibble-packed in flat group order (INT4_ASYM), NULL for symmetric modes;
  *                  arithmetic in fp16 exactly as the reference: (x.f16 - zp.f16) * scale.f16, then the cast;
- *   NF4 / FP4:     scale = fp32 [n_groups];   MXFP4: scale = E8M0 bytes [n_groups].
+ *   NF4 / FP4 / FP8_E4M3: scale = fp32 [n_groups];   MXFP4 / MXFP8_E4M3: scale = E8M0 bytes [n_groups].
  * Replaces src/nncf/torch/quantization/layers.py:1334-1338,1364-1368,1406-1416,1453-1460 (the forward of the
  * INT8/INT4 weight decompressors) and src/nncf/torch/quantization/quantize_functions.py:389-414,436-473.
  */

@@ -127,7 +127,12 @@ def get_weight_compression_configuration(mode, dataset, ratio, group_size, all_l
     if group_size is None:
         group_size = -1 if mode in INT8_MODES else (32 if mode == _M.MXFP4 else 128)
     if backup_mode is None:
-        backup_mode = BackupMode.INT8_ASYM  # MXFP8 / FP8 backups are served by the INT8 default here
+        if mode == _M.MXFP4:
+            backup_mode = BackupMode.MXFP8_E4M3
+        elif mode == _M.FP4:
+            backup_mode = BackupMode.FP8_E4M3
+        else:
+            backup_mode = BackupMode.INT8_ASYM
     if sensitivity_metric is None:
         sensitivity_metric = (SensitivityMetric.WEIGHT_QUANTIZATION_ERROR if dataset is None
                               else SensitivityMetric.MAX_ACTIVATION_VARIANCE)
@@ -137,10 +142,14 @@ def get_weight_compression_configuration(mode, dataset, ratio, group_size, all_l
             "advanced_parameters": advanced_parameters or AdvancedCompressionParameters()}
 
 
-def _backup_config(backup_mode: BackupMode) -> Optional[WeightCompressionConfig]:
+def _backup_config(backup_mode: BackupMode, group_size: int = -1) -> Optional[WeightCompressionConfig]:
     """algorithm.py:577-603."""
     if backup_mode == BackupMode.NONE:
         return None
+    if backup_mode == BackupMode.FP8_E4M3:
+        return WeightCompressionConfig(_M.FP8_E4M3, group_size)
+    if backup_mode == BackupMode.MXFP8_E4M3:
+        return WeightCompressionConfig(_M.MXFP8_E4M3, 32)
     if backup_mode == BackupMode.INT8_SYM:
         return WeightCompressionConfig(_M.INT8_SYM, -1)
     return WeightCompressionConfig(_M.INT8_ASYM, -1)
@@ -351,7 +360,7 @@ def compress_weights(
         raise ValueError(msg)
 
     primary = WeightCompressionConfig(mode, cfg["group_size"])
-    backup = _backup_config(cfg["backup_mode"])
+    backup = _backup_config(cfg["backup_mode"], cfg["group_size"])
     ratio_defining = _ratio_defining(params, mode, cfg["all_layers"])
     rd_names = {p.weight_name for p in ratio_defining}
     for p in params:
@@ -448,14 +457,21 @@ def compress_weights(
     # GPTQ (gptq.py:82-171) or ScaleEstimation (scale_estimation.py:97-158)
     if cfg["gptq"]:
         g = GPTQ(adv.gptq_params.damp_percent, adv.gptq_params.block_size, adv.gptq_params.subset_size)
-        for p in active:
-            if p.is_embedding or p.compression_config.mode in INT8_MODES:
-                continue
-            H = _layer_hessian(model, p.module, items[: adv.gptq_params.subset_size], g)
-            w = p.weight.data.float().contiguous()
-            q, sc, zp = g._quantize_weights(p, H, w)
-            p.module.weight.data = q.to(p.weight.dtype)
-            precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
+        targets = [p for p in active if not p.is_embedding and p.compression_config.mode not in INT8_MODES]
+        # layers fed by the very same tensor (q/k/v, gate/up) share one Hessian and one factorisation
+        for group in _same_input_groups(model, sample, targets):
+            H = _layer_hessian(model, group[0].module, items[: adv.gptq_params.subset_size], g)
+            hinv = None
+            for p in group:
+                w = p.weight.data.float().contiguous()
+                if hinv is None:
+                    hinv = g.prepare_hessian_inverse(H, w)
+                q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv)
+                precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
+                p._gptq_weight = q
+            for p in group:  # weights are replaced only after the whole group saw the same inputs
+                p.module.weight.data = p._gptq_weight.to(p.weight.dtype)
+                del p._gptq_weight
     elif cfg["scale_estimation"]:
         se = adv.scale_estimation_params
         algo = ScaleEstimation(se.subset_size, se.initial_steps, se.scale_steps, se.weight_penalty)
@@ -464,6 +480,37 @@ def compress_weights(
 
     _transform_model(active, precomputed)
     return model
+
+
+def _same_input_groups(model: nn.Module, sample: Any, targets: list) -> list:
+    """Consecutive target layers whose forward receives the identical input tensor."""
+    seen: dict = {}
+    keep = []
+    handles = []
+
+    def make(name):
+        def hook(mod, args):
+            seen.setdefault(name, id(args[0]))
+            keep.append(args[0])
+        return hook
+
+    for p in targets:
+        handles.append(p.module.register_forward_pre_hook(make(p.weight_name)))
+    try:
+        with torch.no_grad():
+            _run(model, sample)
+    finally:
+        for h in handles:
+            h.remove()
+    groups: list = []
+    for p in targets:
+        key = seen.get(p.weight_name)
+        if groups and key is not None and seen.get(groups[-1][0].weight_name) == key and \
+                groups[-1][0].weight_shape[1] == p.weight_shape[1]:
+            groups[-1].append(p)
+        else:
+            groups.append([p])
+    return groups
 
 
 def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ) -> torch.Tensor:
@@ -503,6 +550,11 @@ def _make_decompressor(p: WeightCompressionParameters, item) -> nn.Module:
     out_ch, in_ch = w.shape
     gs = cfg.group_size if cfg.group_size != -1 else in_ch
     G = in_ch // gs
+    if cfg.mode in (_M.FP8_E4M3, _M.MXFP8_E4M3):
+        grouped = (out_ch, G, gs) if cfg.group_size != -1 else (out_ch, in_ch)
+        pshape = (out_ch, G, 1) if cfg.group_size != -1 else (out_ch, 1)
+        scale = item.scale_e8m0.reshape(pshape) if cfg.mode == _M.MXFP8_E4M3 else item.scale.reshape(pshape)
+        return FloatCodebookWeightsDecompressor(cfg.mode, scale, grouped, tuple(w.shape), w.dtype)
     if cfg.num_bits == 8:
         pshape = (out_ch, 1)
         if cfg.mode == _M.INT8_ASYM:

@@ -7,8 +7,8 @@
 //
 // Integer modes reproduce the reference bit for bit: the arithmetic is done in fp16 like
 // decompress_asymmetric / decompress_symmetric (src/nncf/torch/quantization/quantize_functions.py:389-414:
-// (x.f16 - zp.f16) * scale.f16), then cast to the result dtype.  NF4 / E2M1 have no torch decompressor in
-// the reference; they decode the code book value and multiply by the fp32 (or E8M0) scale in fp32.
+// (x.f16 - zp.f16) * scale.f16), then cast to the result dtype.  NF4 / E2M1 / E4M3 have no torch decompressor in
+// the reference; they decode the format's value and multiply by the fp32 (or E8M0) scale in fp32.
 #include <algorithm>
 
 #include "nncfb_common.cuh"
@@ -76,13 +76,15 @@ __global__ void __launch_bounds__(256) decompress_kernel(const DecompressArgs a)
       }
     } else {
       float s;
-      if constexpr (MODE == NNCFB_MXFP4) s = exp2_int(static_cast<int>(reinterpret_cast<const uint8_t*>(a.scale)[g]) - 127);
+      if constexpr (mode_is_mx(MODE)) s = exp2_int(static_cast<int>(reinterpret_cast<const uint8_t*>(a.scale)[g]) - 127);
       else s = reinterpret_cast<const float*>(a.scale)[g];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float u;
         if constexpr (MODE == NNCFB_NF4) {
           u = kNf4Levels[code[i]];
+        } else if constexpr (mode_bits(MODE) == 8) {
+          u = e4m3_value(code[i]);
         } else {
           const float mag = e2m1_magnitude(static_cast<int>(code[i] & 7u));
           u = (code[i] & 8u) ? -mag : mag;
@@ -116,6 +118,8 @@ int launch_decompress(const DecompressArgs& a, cudaStream_t st) {
     case NNCFB_NF4: NNCFB_DQ(NNCFB_NF4);
     case NNCFB_FP4: NNCFB_DQ(NNCFB_FP4);
     case NNCFB_MXFP4: NNCFB_DQ(NNCFB_MXFP4);
+    case NNCFB_FP8_E4M3: NNCFB_DQ(NNCFB_FP8_E4M3);
+    case NNCFB_MXFP8_E4M3: NNCFB_DQ(NNCFB_MXFP8_E4M3);
     default:
       set_error("nncfb_decompress: mode %d is not supported", a.mode);
       return NNCFB_E_UNSUPPORTED;

@@ -22,7 +22,7 @@
 namespace nncfb {
 
 constexpr int kGptqMaxBlock = 128;
-constexpr int kSweepRows = 64;
+constexpr int kSweepRows = 32;
 constexpr int kSweepLd = kSweepRows + 1;
 
 struct GptqArgs {
@@ -37,21 +37,26 @@ struct GptqArgs {
   int i1, count;       // current block: columns [i1, i1 + count)
 };
 
+// One warp per 32 output rows (a thread owns a row).  The 128-column block is swept in four sub-blocks of
+// 32 columns: the sub-block lives in registers and its triangular update is fully unrolled; the error columns
+// of a finished sub-block are then applied to the rest of the block, column by column in ascending error
+// order, so every weight sees exactly the sequence of rounded multiply / subtract steps that the reference's
+// column loop applies to it (WC/gptq.py:337-358).
 template <int MODE>
 __global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a) {
   extern __shared__ __align__(16) float smem[];
   float* hs = smem;                                   // [128][128] Hinv block (row i, col j >= i used)
-  float* ws = hs + kGptqMaxBlock * kGptqMaxBlock;     // [128][65]  weights, column-major per thread
-  float* es = ws + kGptqMaxBlock * kSweepLd;          // [128][65]  error columns
+  float* ws = hs + kGptqMaxBlock * kGptqMaxBlock;     // [128][33]  weights, column-major per thread
+  float* es = ws + kGptqMaxBlock * kSweepLd;          // [128][33]  error columns
   const int t = threadIdx.x;
   const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kSweepRows;
   const int64_t row = row0 + t;
   const bool valid = row < a.rows;
   const int count = a.count, i1 = a.i1;
 
-  for (int idx = t; idx < count * count; idx += kSweepRows) {
-    const int i = idx / count, j = idx - i * count;
-    hs[i * kGptqMaxBlock + j] = a.hinv[static_cast<int64_t>(i1 + i) * a.cols + (i1 + j)];
+  for (int idx = t; idx < kGptqMaxBlock * kGptqMaxBlock; idx += kSweepRows) {
+    const int i = idx / kGptqMaxBlock, j = idx - i * kGptqMaxBlock;
+    hs[idx] = (i < count && j < count) ? a.hinv[static_cast<int64_t>(i1 + i) * a.cols + (i1 + j)] : 0.0f;
   }
   // weight tile: rows are read along their columns (coalesced), stored column-major per thread
   for (int r = 0; r < kSweepRows; ++r) {
@@ -59,7 +64,7 @@ __global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a
     if (rr >= a.rows) break;
     for (int j = t; j < count; j += kSweepRows) ws[j * kSweepLd + r] = a.w[rr * a.cols + i1 + j];
   }
-  __syncthreads();
+  __syncwarp();
 
   Codec<MODE> c;
   c.from_given(1.0f, 0.0f);
@@ -68,37 +73,67 @@ __global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a
     const int64_t g = i1 / a.gs;
     c.from_given(a.scale[row * a.G + g], a.zp ? static_cast<float>(a.zp[row * a.G + g]) : 0.0f);
   }
-  for (int i = 0; i < count; ++i) {
-    const int64_t col = i1 + i;
-    if (col % a.gs == 0 && valid) {
-      // parameters from the tensor-level weight of this group (WC/gptq.py:312-335)
-      const int64_t end = min(col + a.gs, a.cols);
-      const float* wr = a.w + row * a.cols;
-      float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
-      for (int64_t k = col; k < end; ++k) {
-        const float v = wr[k];
-        mn = fminf(mn, v);
-        mx = fmaxf(mx, v);
-      }
-      c.from_stats(mn, mx);
-      const int64_t g = col / a.gs;
-      a.scale[row * a.G + g] = c.scale;
-      if (a.zp) a.zp[row * a.G + g] = static_cast<int32_t>(c.zp);
+  constexpr int SB = 32;
+  for (int sb0 = 0; sb0 < count; sb0 += SB) {
+    const int cb = min(SB, count - sb0);
+    float w[SB], e[SB];
+#pragma unroll
+    for (int k = 0; k < SB; ++k) {
+      w[k] = (k < cb) ? ws[(sb0 + k) * kSweepLd + t] : 0.0f;
+      e[k] = 0.0f;
     }
-    const float d = hs[i * kGptqMaxBlock + i];
-    const float w = ws[i * kSweepLd + t];
-    float u = 0.0f;
-    if (valid) c.encode(w, u);
-    const float dq = __fmul_rn(u, c.scale);
-    const float e = __fdiv_rn(__fsub_rn(w, dq), d);
-    ws[i * kSweepLd + t] = dq;  // the slot of a finished column carries its result
-    es[i * kSweepLd + t] = e;
-    const float* hrow = hs + i * kGptqMaxBlock;
-    for (int j = i + 1; j < count; ++j) {
-      ws[j * kSweepLd + t] = __fsub_rn(ws[j * kSweepLd + t], __fmul_rn(e, hrow[j]));
+#pragma unroll
+    for (int k = 0; k < SB; ++k) {
+      if (k < cb) {
+        const int i = sb0 + k;
+        const int64_t col = i1 + i;
+        if (col % a.gs == 0 && valid) {
+          // parameters from the tensor-level weight of this group (WC/gptq.py:312-335)
+          const int64_t end = min(col + a.gs, a.cols);
+          const float* wr = a.w + row * a.cols;
+          float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
+          for (int64_t kk = col; kk < end; ++kk) {
+            const float v = wr[kk];
+            mn = fminf(mn, v);
+            mx = fmaxf(mx, v);
+          }
+          c.from_stats(mn, mx);
+          const int64_t g = col / a.gs;
+          a.scale[row * a.G + g] = c.scale;
+          if (a.zp) a.zp[row * a.G + g] = static_cast<int32_t>(c.zp);
+        }
+        const float* hrow = hs + i * kGptqMaxBlock + sb0;
+        const float d = hrow[k];
+        float u = 0.0f;
+        if (valid) c.encode(w[k], u);
+        const float dq = __fmul_rn(u, c.scale);
+        e[k] = __fdiv_rn(__fsub_rn(w[k], dq), d);
+        ws[i * kSweepLd + t] = dq;  // the slot of a finished column carries its result
+        es[i * kSweepLd + t] = e[k];
+#pragma unroll
+        for (int k2 = k + 1; k2 < SB; ++k2) w[k2] = __fsub_rn(w[k2], __fmul_rn(e[k], hrow[k2]));
+      }
+    }
+    // the finished sub-block's errors applied to the remaining columns of the block, four columns at a time
+    for (int j = sb0 + SB; j < count; j += 4) {
+      float wj[4];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) wj[q4] = ws[(j + q4) * kSweepLd + t];   // rows beyond `count` are unused padding
+#pragma unroll
+      for (int k = 0; k < SB; ++k) {
+        const float4 h = *reinterpret_cast<const float4*>(hs + (sb0 + k) * kGptqMaxBlock + j);
+        wj[0] = __fsub_rn(wj[0], __fmul_rn(e[k], h.x));
+        wj[1] = __fsub_rn(wj[1], __fmul_rn(e[k], h.y));
+        wj[2] = __fsub_rn(wj[2], __fmul_rn(e[k], h.z));
+        wj[3] = __fsub_rn(wj[3], __fmul_rn(e[k], h.w));
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        if (j + q4 < count) ws[(j + q4) * kSweepLd + t] = wj[q4];
+      }
     }
   }
-  __syncthreads();
+  __syncwarp();
   for (int r = 0; r < kSweepRows; ++r) {
     const int64_t rr = row0 + r;
     if (rr >= a.rows) break;

@@ -78,18 +78,26 @@ class GPTQ:
         torch.diagonal(hessian).add_(damp)
         L = torch.linalg.cholesky(hessian)
         Hinv = torch.cholesky_inverse(L)
-        return torch.linalg.cholesky(Hinv, upper=True).contiguous()
+        U = torch.linalg.cholesky(Hinv, upper=True).contiguous()
+        U._dead_columns = dead if bool(dead.any()) else None  # reused when several weights share this factor
+        return U
 
     def _quantize_weights(self, wc_params, hessian: torch.Tensor, weight_tensor: torch.Tensor,
-                          inputs: Optional[Sequence[torch.Tensor]] = None):
+                          inputs: Optional[Sequence[torch.Tensor]] = None, hinv: Optional[torch.Tensor] = None):
         """gptq.py:244-379.  ``weight_tensor`` [out, C] fp32 is modified in place (trailing updates) like the
-        reference's; returns (dequantised weight [out, C] fp32, scales [out, G, 1], zero points or None)."""
+        reference's; returns (dequantised weight [out, C] fp32, scales [out, G, 1], zero points or None).
+        ``hinv``: the factor returned by ``prepare_hessian_inverse`` for this Hessian, when several weights
+        share one input (q/k/v, gate/up) and the factorisation was already done; dead columns of the weight
+        are then zeroed from ``hessian``'s diagonal as usual."""
         config: WeightCompressionConfig = wc_params.compression_config
         assert hessian.ndim == 2, "Hessian should be 2D"
         if weight_tensor.dtype != torch.float32 or not weight_tensor.is_contiguous():
             msg = "weight_tensor must be a contiguous fp32 tensor (the sweep updates it in place)"
             raise ValueError(msg)
-        hinv = self.prepare_hessian_inverse(hessian, weight_tensor)
+        if hinv is None:
+            hinv = self.prepare_hessian_inverse(hessian, weight_tensor)
+        elif getattr(hinv, "_dead_columns", None) is not None:
+            weight_tensor[:, hinv._dead_columns] = 0
         rows, cols = weight_tensor.shape
         gs = config.group_size if config.group_size != -1 else cols
         dev = weight_tensor.device

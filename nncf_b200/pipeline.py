@@ -116,7 +116,7 @@ class CompressionPlan:
         if four_bit and not nibble_ok:
             msg = f"{item.name}: shape {tuple(w.shape)} cannot be nibble-packed in one pass"
             raise ValueError(msg)
-        signed8 = cfg.is_integer and not cfg.is_asym_mode and not four_bit
+        signed8 = cfg.is_integer and not cfg.is_asym_mode and not four_bit  # FP8 bit patterns are unsigned bytes
         item.packed = torch.empty(n // 2 if four_bit else n, dtype=torch.int8 if signed8 else torch.uint8, device=dev)
         item.scale = torch.empty(n_groups, dtype=torch.float32, device=dev)
         a = _lib.QuantizeArgs()

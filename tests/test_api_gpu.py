@@ -90,6 +90,9 @@ def test_nf4_and_mxfp4_models_run_and_stay_close_to_the_original():
         rel = float((out - base).norm() / base.norm())
         assert rel < 0.25, (mode, rel)
         assert model.blocks[0].q.parametrizations.weight.original.dtype == torch.uint8
+        # the default backup of the embedding / last layer: MXFP8 for MXFP4, FP8 for FP4, INT8_ASYM otherwise
+        expect = {"nf4": "int8_asym", "mxfp4": "mxfp8_e4m3", "fp4": "fp8_e4m3"}[mode]
+        assert model.head.parametrizations.weight[0].mode.value == expect
 
 
 def test_invalid_options_raise_like_the_reference():
@@ -130,7 +133,7 @@ def test_gptq_model_level_reduces_output_error():
 
 
 @pytest.mark.parametrize("mode,gs", [("int4_sym", 128), ("int4_asym", 64), ("int8_asym", -1), ("int8_sym", -1),
-                                     ("nf4", 128), ("mxfp4", 32)])
+                                     ("nf4", 128), ("mxfp4", 32), ("fp8_e4m3", 128), ("mxfp8_e4m3", 32)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_decompress_kernel_matches_oracle(mode, gs, dtype):
     """nncfb_decompress against the reference's fp16 decompression arithmetic restated by the oracle."""
