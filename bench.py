@@ -482,7 +482,7 @@ def main():
     peak, peak_src = _peaks()
     achieved = alg4 / (ms4 * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "quant_rows_batch_kernel<bf16, INT4_SYM, 8 lanes x 2 vectors per group, 2 groups in flight> (one launch for all 224 tensors)",
+        "bound": "hbm", "kernel": "quant_rows_batch_kernel<bf16, INT4_SYM, 8 lanes x 2 vectors per group, 4 groups in flight> (one launch for all 224 tensors)",
         "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
         "peak_source": peak_src, "launches_per_step": 1, "tensors_per_launch": n4, "avg_launch_us": round(ms4 * 1e3, 2),
         "algorithmic_bytes_per_step": alg4, "traffic": None,

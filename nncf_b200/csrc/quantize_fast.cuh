@@ -23,6 +23,14 @@ namespace nncfb {
 
 constexpr int kMaxBatchTensors = 256;
 
+// Tuning knobs of the row-group kernel (the defaults are the measured best on B200).
+#ifndef NNCFB_ROWS_U
+#define NNCFB_ROWS_U 4          // groups in flight per sub-warp
+#endif
+#ifndef NNCFB_ROWS_MINBLOCKS
+#define NNCFB_ROWS_MINBLOCKS 4  // resident 256-thread blocks per SM that the register budget must allow
+#endif
+
 struct FastTensor {
   const void* weight;
   uint8_t* codes;
@@ -329,7 +337,7 @@ __device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s,
 // owns vectors j, j+L, ... of its group so that every warp load and store is fully coalesced).
 // =====================================================================================================
 template <typename SrcT, int MODE, int L, int VPL, int U>
-__global__ void __launch_bounds__(256, 4) quant_rows_batch_kernel(const __grid_constant__ FastBatch b) {
+__global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_kernel(const __grid_constant__ FastBatch b) {
   constexpr int GPW = 32 / L;
   constexpr int GS = 8 * L * VPL;
   const int lane = threadIdx.x & 31;

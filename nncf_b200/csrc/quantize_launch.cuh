@@ -122,9 +122,9 @@ int launch_fast_mode(const FastBatch& b, FastClass cls, cudaStream_t stream) {
     }
   }
   if (cls.kind == 1) {
-    constexpr int U = 2;
+    constexpr int U = NNCFB_ROWS_U;
     const int grid = static_cast<int>(std::max<int64_t>(
-        1, std::min<int64_t>((b.iter_start[b.n_tensors] + 7) / 8, static_cast<int64_t>(sms) * 4)));
+        1, std::min<int64_t>((b.iter_start[b.n_tensors] + 7) / 8, static_cast<int64_t>(sms) * NNCFB_ROWS_MINBLOCKS)));
     if (cls.group == 128) {
       quant_rows_batch_kernel<SrcT, MODE, 8, 2, U><<<grid, 256, 0, stream>>>(b);
     } else if (cls.group == 64) {
@@ -169,7 +169,7 @@ int launch_fast_t(const FastBatch& b, int mode, FastClass cls, cudaStream_t stre
 inline int64_t fast_iterations(const FastClass& cls, int64_t n_groups, size_t elem_size) {
   if (cls.kind == 1) {
     const int L = cls.group == 128 ? 8 : 4;
-    const int64_t per_iter = (32 / L) * 2;  // GPW * U
+    const int64_t per_iter = (32 / L) * NNCFB_ROWS_U;  // GPW * U
     return (n_groups + per_iter - 1) / per_iter;
   }
   const int K = elem_size == 4 ? 4 : 8;
