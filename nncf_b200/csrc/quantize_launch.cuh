@@ -130,7 +130,7 @@ int launch_fast_mode(const FastBatch& b, FastClass cls, cudaStream_t stream) {
     } else if (cls.group == 64) {
       quant_rows_batch_kernel<SrcT, MODE, 4, 2, U><<<grid, 256, 0, stream>>>(b);
     } else {
-      quant_rows_batch_kernel<SrcT, MODE, 4, 1, U><<<grid, 256, 0, stream>>>(b);
+      quant_rows_batch_kernel<SrcT, MODE, 2, 2, U><<<grid, 256, 0, stream>>>(b);
     }
   } else if constexpr (!mode_is_fast_float(MODE)) {
     const int grid = static_cast<int>(std::max<int64_t>(
@@ -168,7 +168,7 @@ int launch_fast_t(const FastBatch& b, int mode, FastClass cls, cudaStream_t stre
 // iterations one tensor contributes to a batch of class `cls`
 inline int64_t fast_iterations(const FastClass& cls, int64_t n_groups, size_t elem_size) {
   if (cls.kind == 1) {
-    const int L = cls.group == 128 ? 8 : 4;
+    const int L = cls.group == 128 ? 8 : (cls.group == 64 ? 4 : 2);
     const int64_t per_iter = (32 / L) * NNCFB_ROWS_U;  // GPW * U
     return (n_groups + per_iter - 1) / per_iter;
   }
