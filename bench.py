@@ -259,6 +259,62 @@ def run_gptq_workload(args, device):
     print(json.dumps(out), flush=True)
 
 
+def run_moe_workload(args, device, rank, world, dist):
+    """BASELINE.json config 5: NF4 (g128) or MXFP4 (E2M1 values, E8M0 scale per 32) data-free compression of a
+    Mixtral-8x7B-shaped expert stack (per layer 8 experts x (w1, w3: 14336 x 4096; w2: 4096 x 14336), bf16
+    N(0, 0.02^2), seed 4), experts sharded over the ranks by bytes.  `--layers` sets how many of the 32 layers
+    are generated (90 GB for all 32)."""
+    from nncf_b200 import CompressWeightsMode, WeightCompressionConfig
+    from nncf_b200.pipeline import CompressionPlan, partition_by_bytes
+
+    mode = CompressWeightsMode(args.mode)
+    cfg = WeightCompressionConfig(mode, 32 if mode == CompressWeightsMode.MXFP4 else 128)
+    names, shapes = [], []
+    for layer in range(args.layers):
+        for e in range(8):
+            for w, shp in (("w1", (14336, 4096)), ("w3", (14336, 4096)), ("w2", (4096, 14336))):
+                names.append(f"layers.{layer}.experts.{e}.{w}")
+                shapes.append(shp)
+    mine = partition_by_bytes([a * b * 2 for a, b in shapes], world)[rank]
+    gen = torch.Generator(device=device).manual_seed(4 + rank)
+    items = []
+    for i in mine:
+        w = torch.empty(shapes[i], dtype=torch.bfloat16, device=device)
+        w.normal_(0.0, 0.02, generator=gen)
+        items.append((names[i], w, cfg))
+    plan = CompressionPlan(items, device)
+    steps = 1 if args.profile_case else args.steps
+    for _ in range(1 if args.profile_case else max(args.warmup, 3)):
+        plan.run(use_graph=False)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        plan.run(use_graph=False)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=device)
+    tot = torch.tensor([float(plan.source_bytes), float(plan.algorithmic_bytes)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    if rank != 0:
+        return
+    ms = float(t.item())
+    peak, peak_src = _peaks()
+    alg_rank = plan.algorithmic_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": f"source_weight_GBps_compressed_{mode.value}", "value": round(float(tot[0]) / (ms * 1e-3) / 1e9, 1),
+        "unit": UNIT, "n_gpus": world, "steps": steps, "ms_per_step": round(ms, 3), "higher_is_better": True,
+        "scaling": "strong", "data": "synthetic", "dtype": "f32",
+        "config": {"workload": f"Mixtral-8x7B-shaped expert stack, {args.layers} of 32 layers ({len(names)} tensors, "
+                               f"{float(tot[0]) / 1e9:.1f} GB bf16), {mode.value} group {cfg.group_size}, experts sharded by bytes"},
+        "roofline": {"bound": "hbm", "kernel": f"quant_rows_batch_kernel<bf16, {mode.value}>", "achieved": round(alg_rank, 1),
+                     "peak": peak, "unit": "GB/s", "frac": round(alg_rank / peak, 4), "peak_source": peak_src}}), flush=True)
+
+
 def run_data_aware_workload(args, device):
     """ScaleEstimation and AWQ at Llama-3-8B layer shapes (config: INT4_ASYM g128, AWQ subset 32 / 100 alpha
     steps, ScaleEstimation subset 64 / 5 + 5 steps, statistics synthetic with 1 % outlier channels x20),
@@ -318,8 +374,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a graph")
-    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "data_aware"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "data_aware", "moe"],
                     help="compress: the headline metric (default); gptq: the secondary GPTQ metric")
+    ap.add_argument("--mode", default="nf4", choices=["nf4", "mxfp4", "fp4"], help="mode of the moe workload")
+    ap.add_argument("--layers", type=int, default=4, help="layers of the moe workload (32 = the full 90 GB stack)")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profilers: one decoder layer, no e2e / cpu arm, 1 warm-up, 1 step")
     args = ap.parse_args()
@@ -337,6 +395,15 @@ def main():
     torch.cuda.set_device(device)
     import torch.distributed as dist
 
+    if args.workload == "moe":
+        if world > 1:
+            dist.init_process_group("nccl", device_id=device)
+        if args.profile_case:
+            args.layers = 1
+        run_moe_workload(args, device, rank, world, dist)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload in ("gptq", "data_aware"):
         if rank == 0:
             (run_gptq_workload if args.workload == "gptq" else run_data_aware_workload)(args, device)
