@@ -585,14 +585,9 @@ def _transform_model(active: list, precomputed: dict) -> None:
             results[p.weight_name] = it
     for p in active:
         if p.weight_name in precomputed:
-            cw = compress_weight(p.weight.data, p.reduction_axes, p.compression_config, precomputed[p.weight_name], pack=True)
-
-            class _It:
-                pass
-
-            it = _It()
-            it.packed, it.scale, it.zero_point, it.scale_e8m0 = cw.packed, cw.scale, cw.zero_point, cw.scale_e8m0
-            results[p.weight_name] = it
+            # a CompressedWeight carries the same fields a plan item does (packed, scale, zero_point, scale_e8m0)
+            results[p.weight_name] = compress_weight(p.weight.data, p.reduction_axes, p.compression_config,
+                                                     precomputed[p.weight_name], pack=True)
     for p in active:
         it = results[p.weight_name]
         dec = _make_decompressor(p, it)

@@ -60,40 +60,6 @@ __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(
 template <>
 __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// 8 consecutive elements, 16-byte aligned, widened to fp32 (exact for f16 / bf16).
-// Streaming loads: the weight is read exactly once.
-template <typename T>
-__device__ __forceinline__ void load8(const T* __restrict__ p, float (&v)[8]);
-
-template <>
-__device__ __forceinline__ void load8<float>(const float* __restrict__ p, float (&v)[8]) {
-  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* __restrict__ p, float (&v)[8]) {
-  const uint4 r = __ldcs(reinterpret_cast<const uint4*>(p));
-  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-template <>
-__device__ __forceinline__ void load8<__half>(const __half* __restrict__ p, float (&v)[8]) {
-  const uint4 r = __ldcs(reinterpret_cast<const uint4*>(p));
-  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    v[2 * i] = f.x;
-    v[2 * i + 1] = f.y;
-  }
-}
-
 // ---- exact fp32 division by a per-group constant -----------------------------------------
 // The reference divides every weight by its group's scale with a true IEEE division
 // (WC/weight_lowering.py:678, :626).  One division per element is the most expensive step

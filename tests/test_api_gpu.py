@@ -162,3 +162,38 @@ def test_decompress_kernel_matches_oracle(mode, gs, dtype):
     else:
         exp = torch.from_numpy((ref.tensor * ref.scale).astype(np.float32)).to(dtype).float().numpy().reshape(96, 512)
     np.testing.assert_array_equal(got, exp)
+
+
+def test_hf_llama_model_awq_scale_estimation_end_to_end():
+    """A randomly initialised Hugging Face Llama decoder (2 layers, hidden 64): INT4_ASYM g32 with AWQ and
+    ScaleEstimation must find the up_proj -> multiply -> down_proj pairs, keep the embedding and lm_head in the
+    INT8_ASYM backup, and stay close to the original model's logits."""
+    transformers = pytest.importorskip("transformers")
+    import nncf_b200 as nb
+    from nncf_b200.compress_api import find_mul_merge_pairs
+
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, vocab_size=256, max_position_embeddings=64,
+                                   tie_word_embeddings=False)
+    model = transformers.LlamaForCausalLM(cfg).cuda().eval()
+    gen = torch.Generator().manual_seed(2)
+    items = [{"input_ids": torch.randint(0, 256, (1, 24), generator=gen).cuda()} for _ in range(8)]
+    with torch.no_grad():
+        base = model(**items[0]).logits.float()
+    targets = {n: m for n, m in model.named_modules() if isinstance(m, torch.nn.Linear)}
+    pairs = find_mul_merge_pairs(model, items[0], targets)
+    assert {n.split(".")[-1] for n in pairs} == {"down_proj"}
+    assert all(m is model.get_submodule(n.replace("down_proj", "up_proj")) for n, m in pairs.items())
+    cm = nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_ASYM, group_size=32, dataset=nb.Dataset(items),
+                             awq=True, scale_estimation=True,
+                             advanced_parameters=nb.AdvancedCompressionParameters(
+                                 awq_params=nb.AdvancedAWQParameters(percent_to_apply=0.05)))
+    with torch.no_grad():
+        out = cm(**items[0]).logits.float()
+    rel = float((out - base).norm() / base.norm())
+    assert rel < 0.2, rel
+    sd = cm.state_dict()
+    assert sd["lm_head.parametrizations.weight.original"].shape == (256, 64)           # INT8 backup, unpacked bytes
+    assert sd["model.embed_tokens.parametrizations.weight.original"].shape == (256, 64)
+    assert sd["model.layers.0.mlp.down_proj.parametrizations.weight.original"].shape == (64 * 128 // 2, 1)

@@ -337,3 +337,51 @@ def test_float_codes_at_and_next_to_every_decision_boundary(mode):
     plan.run(use_graph=False)
     codes = O.nibble_code_nf4(ref.tensor) if mode == "nf4" else O.nibble_code_e2m1(ref.tensor)
     _eq(plan.items[0].packed, O.pack_uint4(codes).reshape(-1), "packed")
+
+
+def test_random_shapes_modes_and_dtypes_match_oracle():
+    """Seeded fuzz over shapes (ragged rows, group sizes that hit every kernel variant, odd sizes), modes,
+    dtypes and value distributions: reference-shaped outputs and the stored (packed) form against the oracle."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import weight_lowering as wl
+
+    rng = np.random.default_rng(2024)
+    group_sizes = [8, 16, 24, 32, 40, 64, 128, 256, 384, 512, 1024, -1]
+    for case in range(160):
+        mode = MODES[rng.integers(len(MODES))]
+        dtype = ["f32", "f16", "bf16"][rng.integers(3)]
+        gs = group_sizes[rng.integers(len(group_sizes))]
+        rows = int(rng.integers(1, 70))
+        groups = int(rng.integers(1, 6)) if gs != -1 else 1
+        cols = gs * groups if gs != -1 else int(rng.integers(1, 300)) * 8 + (int(rng.integers(0, 8)) if rng.random() < 0.3 else 0)
+        kind = rng.integers(4)
+        if kind == 0:
+            w = rng.normal(0, 0.02, (rows, cols))
+        elif kind == 1:
+            w = rng.uniform(-3, 3, (rows, cols))
+        elif kind == 2:
+            w = rng.normal(0, 1, (rows, cols)) * (rng.random((rows, 1)) < 0.7)   # some all-zero rows
+        else:
+            w = np.abs(rng.normal(0, 5e-3, (rows, cols))) + 1e-3                 # one-signed
+        wt = torch.from_numpy(w.astype(np.float32)).to(TORCH_DTYPE[dtype])
+        w_np = wt.numpy() if dtype == "f16" else wt.float().numpy()
+        ref = O.compress_weight(w_np, 1, mode, gs)
+        cfg = _cfg(mode, gs)
+        tag = f"case {case}: {mode} {dtype} {rows}x{cols} g{gs}"
+        cw = wl.compress_weight(wt.cuda(), 1, cfg)
+        _eq(cw.scale, ref.scale, tag + " scale")
+        got_t, ref_t = cw.tensor.cpu().numpy(), ref.tensor
+        assert np.array_equal(got_t, ref_t, equal_nan=True), tag + " tensor"
+        if cfg.is_asym_mode:
+            _eq(cw.zero_point, ref.zero_point, tag + " zp")
+        if (rows * cols) % 2 == 0 or cfg.num_bits == 8:
+            st = wl.compress_weight(wt.cuda(), 1, cfg, pack=True)
+            if cfg.is_integer and cfg.num_bits == 4:
+                exp = O.pack_int4(ref.tensor) if mode == "int4_sym" else O.pack_uint4(ref.tensor)
+                _eq(st.packed, exp, tag + " packed")
+            elif cfg.is_integer:
+                _eq(st.packed, ref.tensor, tag + " codes")
+            elif cfg.num_bits == 4:
+                codes = O.nibble_code_nf4(ref.tensor) if mode == "nf4" else O.nibble_code_e2m1(ref.tensor)
+                _eq(st.packed, O.pack_uint4(codes), tag + " packed float codes")
