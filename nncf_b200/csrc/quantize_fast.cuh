@@ -247,30 +247,23 @@ __device__ __forceinline__ void int_params(float mn, float mx, float& s, float& 
 }
 
 // ---- float (code-book) modes ---------------------------------------------------------------------------
-// NF4 and E2M1 indices without a search: the quotient q is bucketed by one FMA (bucket width smaller than
-// the smallest gap between decision boundaries, so a bucket holds at most one boundary) and a 32-entry
-// table spread over the lanes of the warp - fetched with two shuffles - gives the number of boundaries
-// below the bucket and the one boundary inside it:  index = base[k] + (q > bound[k]).
-// NF4: k = rint(q * 15.49 + 16) in [1, 31] for q in [-1, 1]; bounds are the reference's 15 literals
-// (WC/constants.py:84-103), '>' reproduces searchsorted(side='left').
-// E2M1: k = rint(4 |q|) in [0, 24]; the seven thresholds sit at bucket centres; a '>=' threshold (ties that
-// go up to an even mantissa) is stored as the float just below it, so one '>' serves both kinds.
+// NF4 index = number of the reference's 15 decision boundaries (WC/constants.py:84-103) strictly below the
+// quotient q in [-1, 1] (searchsorted side='left', WC/weight_lowering.py:574), without a search:
+//   k = rint(7 + q * (c1 + q * (c2 + q * c3)))   -- a cubic through the boundaries, three packed FMAs, the
+//       last one adding 1.5 * 2^23 + 7 so that k lands in the low mantissa bits;
+//   index = k + (q > bound[k])                   -- bound[] is spread over the lanes of the warp, one shuffle.
+// The cubic keeps k in {index - 1, index} for every real q in [-1, 1] with 0.034 to spare (fp32 evaluation
+// error is below 1e-5), so comparing against the single boundary bound[k] decides the index exactly; k = -1
+// reads lane 31, which holds -inf.  tests/test_kernel_constants.py re-derives that margin from these constants.
+constexpr float kNf4PolyC1 = 11.72690251f, kNf4PolyC2 = -0.51709913f, kNf4PolyC3 = -4.67530535f;
 constexpr float kLutNone = 3.0e38f;
 __device__ __constant__ const float kNf4LutBound[32] = {
-    kLutNone, kLutNone, kLutNone, -0.8480964303016663f, kLutNone, kLutNone, kLutNone, -0.6106328964233398f,
-    kLutNone, -0.4599952697753906f, kLutNone, -0.33967941999435425f, -0.23460739850997925f, kLutNone,
-    -0.13791173696517944f, -0.045525018125772476f, kLutNone, 0.03979014977812767f, 0.1202552542090416f,
-    0.2035212516784668f, kLutNone, 0.2920137643814087f, 0.3893125355243683f, kLutNone, 0.5016633868217468f,
-    kLutNone, 0.6427869200706482f, kLutNone, kLutNone, 0.8614783883094788f, kLutNone, kLutNone};
-__device__ __constant__ const int kNf4LutBase[32] = {0, 0, 0, 0, 1, 1, 1, 1, 2, 2, 3, 3, 4, 5, 5, 6,
-                                                     7, 7, 8, 9, 10, 10, 11, 12, 12, 13, 13, 14, 14, 14, 15, 15};
-__device__ __constant__ const float kE2m1LutBound[32] = {
-    kLutNone, 0.25f, kLutNone, 0.7499999403953552f, kLutNone, 1.25f, kLutNone, 1.7499998807907104f,
-    kLutNone, kLutNone, 2.5f, kLutNone, kLutNone, kLutNone, 3.499999761581421f, kLutNone,
-    kLutNone, kLutNone, kLutNone, kLutNone, 5.0f, kLutNone, kLutNone, kLutNone,
-    kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone};
-__device__ __constant__ const int kE2m1LutBase[32] = {0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 4, 5, 5, 5, 5, 6,
-                                                      6, 6, 6, 6, 6, 7, 7, 7, 7, 7, 7, 7, 7, 7, 7, 7};
+    -0.8480964303016663f, -0.6106328964233398f, -0.4599952697753906f, -0.33967941999435425f,
+    -0.23460739850997925f, -0.13791173696517944f, -0.045525018125772476f, 0.03979014977812767f,
+    0.1202552542090416f, 0.2035212516784668f, 0.2920137643814087f, 0.3893125355243683f,
+    0.5016633868217468f, 0.6427869200706482f, 0.8614783883094788f, kLutNone,
+    kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone,
+    kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, -kLutNone};
 
 __host__ __device__ constexpr bool mode_is_fast_float(int m) { return m == NNCFB_NF4 || m == NNCFB_FP4 || m == NNCFB_MXFP4; }
 
@@ -292,44 +285,67 @@ __device__ __forceinline__ void float_params(float mn, float mx, float& s, float
   }
 }
 
+// Value of `v` held by lane (index & 31).  Written as PTX so that the index, which keeps the 1.5 * 2^23
+// pattern in its high bits and is used again as a Horner digit, carries no lane-range assumption.
+__device__ __forceinline__ float shfl_low5(float v, uint32_t index) {
+  float r;
+  asm volatile("shfl.sync.idx.b32 %0, %1, %2, 0x1f, 0xffffffff;" : "=f"(r) : "f"(v), "r"(index));
+  return r;
+}
+
 // Nibble codes of 8 elements: NF4 table index, or E2M1 bit pattern sign|index (zero is stored as +0).
+// E2M1 uses the hardware conversion cvt.rn.satfinite.e2m1x2.f32: round to nearest, ties to the even
+// mantissa, saturation at 6 - the rule WC/weight_lowering.py:577-583 implements on its 15-entry table.
 template <int MODE>
-__device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s, float r, float lut_bound, int lut_base) {
+__device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s, float r, float lut_bound) {
   const float2 r2 = f2(r, r), ns2 = f2(-s, -s);
-  uint32_t acc = 0;
+  float2 q[4];
 #pragma unroll
-  for (int i = 3; i >= 0; --i) {
-    const float2 q0 = __fmul2_rn(v[i], r2);
-    const float2 e = __ffma2_rn(ns2, q0, v[i]);
-    const float2 q = __ffma2_rn(e, r2, q0);
-    uint32_t d[2];
-    if constexpr (MODE == NNCFB_NF4) {
-      const float2 t = __ffma2_rn(q, f2(15.49f, 15.49f), f2(12582928.0f, 12582928.0f));
-      const float qq[2] = {q.x, q.y};
-      const uint32_t kk[2] = {__float_as_uint(t.x), __float_as_uint(t.y)};
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float b = __shfl_sync(0xffffffffu, lut_bound, kk[h]);
-        const int base = __shfl_sync(0xffffffffu, lut_base, kk[h]);
-        d[h] = static_cast<uint32_t>(base + (qq[h] > b ? 1 : 0));
-      }
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (MODE == NNCFB_MXFP4) {
+      q[i] = __fmul2_rn(v[i], r2);  // the scale is a power of two: one multiply is the exact quotient
     } else {
-      const float2 a = f2(fabsf(q.x), fabsf(q.y));
-      const float2 t = __ffma2_rn(a, f2(4.0f, 4.0f), f2(12582912.0f, 12582912.0f));
-      const float aa[2] = {a.x, a.y}, qq[2] = {q.x, q.y};
-      const uint32_t kk[2] = {__float_as_uint(t.x), __float_as_uint(t.y)};
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float b = __shfl_sync(0xffffffffu, lut_bound, kk[h]);
-        const int base = __shfl_sync(0xffffffffu, lut_base, kk[h]);
-        const uint32_t idx = static_cast<uint32_t>(base + (aa[h] > b ? 1 : 0));
-        const uint32_t s8 = (__float_as_uint(qq[h]) >> 28) & 8u;
-        d[h] = idx | (s8 & (idx + 7u));  // sign bit only for non-zero magnitudes
-      }
+      const float2 q0 = __fmul2_rn(v[i], r2);
+      const float2 e = __ffma2_rn(ns2, q0, v[i]);
+      q[i] = __ffma2_rn(e, r2, q0);
     }
-    acc = (acc * 16u + d[1]) * 16u + d[0];
   }
-  return acc;
+  if constexpr (MODE == NNCFB_NF4) {
+    const float2 c1 = f2(kNf4PolyC1, kNf4PolyC1), c2 = f2(kNf4PolyC2, kNf4PolyC2), c3 = f2(kNf4PolyC3, kNf4PolyC3);
+    const float2 m7 = f2(12582919.0f, 12582919.0f);
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 3; i >= 0; --i) {
+      float2 h = __ffma2_rn(q[i], c3, c2);
+      h = __ffma2_rn(h, q[i], c1);
+      const float2 t = __ffma2_rn(h, q[i], m7);
+      uint32_t kx = __float_as_uint(t.x), ky = __float_as_uint(t.y);
+      // Opaque to the optimiser from here on: when it can see that kx and ky are the halves of one packed
+      // result it was observed (nvcc 12.9, sm_100a) to place digits of the sum below in the wrong nibble.
+      asm("" : "+r"(kx), "+r"(ky));
+      const float bx = shfl_low5(lut_bound, kx);
+      const float by = shfl_low5(lut_bound, ky);
+      acc = acc * 16u + ky;
+      if (q[i].y > by) acc += 1u;
+      acc = acc * 16u + kx;
+      if (q[i].x > bx) acc += 1u;
+    }
+    return acc - kMagicBits * 0x11111111u;
+  } else {
+    uint32_t w;
+    asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+        "mov.b32 %0, {t0, t1, t2, t3};\n\t}"
+        : "=r"(w)
+        : "f"(q[0].x), "f"(q[0].y), "f"(q[1].x), "f"(q[1].y), "f"(q[2].x), "f"(q[2].y), "f"(q[3].x), "f"(q[3].y));
+    // a negative value that rounds to zero is stored as +0: drop the sign of nibbles with zero magnitude
+    const uint32_t m = w & 0x77777777u;
+    const uint32_t nz = (m | (m >> 1) | (m >> 2)) & 0x11111111u;
+    return w & (0x77777777u | (nz * 8u));
+  }
 }
 
 // =====================================================================================================
@@ -348,14 +364,7 @@ __global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_ke
   const int64_t total_iters = b.iter_start[b.n_tensors];
   int lo = 0;  // tensor of the current iteration; iterations only move forward
   float lut_bound = 0.0f;
-  int lut_base = 0;
-  if constexpr (MODE == NNCFB_NF4) {
-    lut_bound = kNf4LutBound[lane];
-    lut_base = kNf4LutBase[lane];
-  } else if constexpr (mode_is_fast_float(MODE)) {
-    lut_bound = kE2m1LutBound[lane];
-    lut_base = kE2m1LutBase[lane];
-  }
+  if constexpr (MODE == NNCFB_NF4) lut_bound = kNf4LutBound[lane];
 
   for (int64_t it = warp; it < total_iters; it += n_warps) {
     while (b.iter_start[lo + 1] <= it) ++lo;
@@ -390,7 +399,7 @@ __global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_ke
         for (int v = 0; v < VPL; ++v) {
           float2 x[4];
           unpack8_pairs(raw[p][v], x);
-          const uint32_t w = encode8_float<MODE>(x, s, r, lut_bound, lut_base);  // shuffles inside: all lanes
+          const uint32_t w = encode8_float<MODE>(x, s, r, lut_bound);  // shuffles inside: all lanes
           if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
         }
         if (valid && lig == 0) {
