@@ -352,65 +352,56 @@ __device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s,
 // Batched row-group kernel: group_size = 8 * L * VPL (L lanes, VPL 16-byte vectors per lane; lane j
 // owns vectors j, j+L, ... of its group so that every warp load and store is fully coalesced).
 // =====================================================================================================
-template <typename SrcT, int MODE, int L, int VPL, int U>
-__global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_kernel(const __grid_constant__ FastBatch b) {
+// One warp iteration: U * (32 / L) consecutive groups of one tensor.  FULL: every group exists (all but
+// the last iteration of a tensor), so the loads, the code stores and the zero fill need no predicates.
+template <typename SrcT, int MODE, int L, int VPL, int U, bool FULL>
+__device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_t g0, const int lig, const float lut_bound) {
   constexpr int GPW = 32 / L;
   constexpr int GS = 8 * L * VPL;
-  const int lane = threadIdx.x & 31;
-  const int sub = lane / L;
-  const int lig = lane % L;
-  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int64_t total_iters = b.iter_start[b.n_tensors];
-  int lo = 0;  // tensor of the current iteration; iterations only move forward
-  float lut_bound = 0.0f;
-  if constexpr (MODE == NNCFB_NF4) lut_bound = kNf4LutBound[lane];
+  const SrcT* __restrict__ src = reinterpret_cast<const SrcT*>(T.weight);
+  const int64_t n_groups = T.n_groups;
 
-  for (int64_t it = warp; it < total_iters; it += n_warps) {
-    while (b.iter_start[lo + 1] <= it) ++lo;
-    const FastTensor& T = b.t[lo];
-    const SrcT* __restrict__ src = reinterpret_cast<const SrcT*>(T.weight);
-    const int64_t n_groups = T.n_groups;
-    const int64_t g0 = (it - b.iter_start[lo]) * (GPW * U) + sub;
-
-    Raw8<SrcT> raw[U][VPL];
+  Raw8<SrcT> raw[U][VPL];
 #pragma unroll
-    for (int p = 0; p < U; ++p) {
-      const int64_t g = g0 + p * GPW;
+  for (int p = 0; p < U; ++p) {
+    const int64_t g = g0 + p * GPW;
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) {
+    for (int v = 0; v < VPL; ++v) {
+      if constexpr (FULL) {
+        raw[p][v] = load_raw8<SrcT>(src + g * GS + (lig + v * L) * 8);
+      } else {
         raw[p][v] = g < n_groups ? load_raw8<SrcT>(src + g * GS + (lig + v * L) * 8) : zero_raw8<SrcT>();
       }
     }
+  }
 #pragma unroll
-    for (int p = 0; p < U; ++p) {
-      const int64_t g = g0 + p * GPW;
-      const bool valid = g < n_groups;
-      MinNegMax m = min_negmax<SrcT, VPL>(raw[p]);
+  for (int p = 0; p < U; ++p) {
+    const int64_t g = g0 + p * GPW;
+    const bool valid = FULL || g < n_groups;
+    MinNegMax m = min_negmax<SrcT, VPL>(raw[p]);
 #pragma unroll
-      for (int o = L / 2; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
-      float mn, mx, s, r, zp;
-      bool need_clamp;
-      finish_minmax<SrcT>(m, mn, mx);
-      if constexpr (mode_is_fast_float(MODE)) {
-        int e8;
-        float_params<MODE>(mn, mx, s, r, e8);
+    for (int o = L / 2; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
+    float mn, mx, s, r, zp;
+    bool need_clamp;
+    finish_minmax<SrcT>(m, mn, mx);
+    if constexpr (mode_is_fast_float(MODE)) {
+      int e8;
+      float_params<MODE>(mn, mx, s, r, e8);
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) {
-          float2 x[4];
-          unpack8_pairs(raw[p][v], x);
-          const uint32_t w = encode8_float<MODE>(x, s, r, lut_bound);  // shuffles inside: all lanes
-          if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
-        }
-        if (valid && lig == 0) {
-          if (T.scale) T.scale[g] = s;
-          if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
-          if constexpr (MODE == NNCFB_MXFP4) {
-            if (T.e8m0) T.e8m0[g] = static_cast<uint8_t>(e8 + 127);
-          }
-        }
-        continue;
+      for (int v = 0; v < VPL; ++v) {
+        float2 x[4];
+        unpack8_pairs(raw[p][v], x);
+        const uint32_t w = encode8_float<MODE>(x, s, r, lut_bound);  // shuffles inside: all lanes
+        if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
       }
+      if (valid && lig == 0) {
+        if (T.scale) T.scale[g] = s;
+        if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
+        if constexpr (MODE == NNCFB_MXFP4) {
+          if (T.e8m0) T.e8m0[g] = static_cast<uint8_t>(e8 + 127);
+        }
+      }
+    } else {
       int_params<MODE>(mn, mx, s, r, zp, need_clamp);
       bool clamp = false;
       if constexpr (mode_is_asym(MODE)) clamp = __any_sync(0xffffffffu, need_clamp);
@@ -438,6 +429,31 @@ __global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_ke
         if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
         if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
       }
+    }
+  }
+}
+
+template <typename SrcT, int MODE, int L, int VPL, int U>
+__global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_kernel(const __grid_constant__ FastBatch b) {
+  constexpr int GPW = 32 / L;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / L;
+  const int lig = lane % L;
+  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t total_iters = b.iter_start[b.n_tensors];
+  int lo = 0;  // tensor of the current iteration; iterations only move forward
+  float lut_bound = 0.0f;
+  if constexpr (MODE == NNCFB_NF4) lut_bound = kNf4LutBound[lane];
+
+  for (int64_t it = warp; it < total_iters; it += n_warps) {
+    while (b.iter_start[lo + 1] <= it) ++lo;
+    const FastTensor& T = b.t[lo];
+    const int64_t first = (it - b.iter_start[lo]) * (GPW * U);  // warp-uniform
+    if (first + GPW * U <= T.n_groups) {
+      rows_iteration<SrcT, MODE, L, VPL, U, true>(T, first + sub, lig, lut_bound);
+    } else {
+      rows_iteration<SrcT, MODE, L, VPL, U, false>(T, first + sub, lig, lut_bound);
     }
   }
 }
