@@ -462,119 +462,103 @@ __global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_ke
 // Batched per-channel kernel (one group per row, row length % 8 == 0): TPR threads per row keep the
 // row in registers (K vectors each); rows longer than TPR*K*8 re-read the tail from L2.
 // =====================================================================================================
-template <typename SrcT, int MODE, int TPR>
-__global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __grid_constant__ FastBatch b,
-                                                                     const int64_t row_len) {
+// One block iteration of the per-channel kernel: 256 / TPR rows.  FULL: every row exists and the row is
+// exactly the TPR * K vectors the threads hold, so nothing is predicated and there is no tail loop.
+template <typename SrcT, int MODE, int TPR, bool FULL>
+__device__ __forceinline__ void channel_iteration(const FastTensor& T, const int64_t g, const int64_t row_len,
+                                                  uint32_t* red16, float* red_mn, float* red_nmx) {
   constexpr int K = WideCache<SrcT>::K;
-  constexpr int RPB = 256 / TPR;  // rows per block
   constexpr int WPR = TPR / 32;   // warps per row
-  __shared__ uint32_t red16[8];
-  __shared__ float red_mn[8], red_nmx[8];
   const int tir = threadIdx.x % TPR;
-  const int rib = threadIdx.x / TPR;
   const int warp_in_block = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int first_warp = rib * WPR;
+  const int first_warp = (threadIdx.x / TPR) * WPR;
   const int64_t nvec = row_len >> 3;
-  const int64_t total_iters = b.iter_start[b.n_tensors];  // iterations of RPB rows
+  const bool valid = FULL || g < T.n_groups;
+  const SrcT* __restrict__ row = reinterpret_cast<const SrcT*>(T.weight) + (valid ? g : 0) * row_len;
 
-  int lo = 0;
-  for (int64_t it = blockIdx.x; it < total_iters; it += gridDim.x) {
-    while (b.iter_start[lo + 1] <= it) ++lo;
-    const FastTensor& T = b.t[lo];
-    const int64_t g = (it - b.iter_start[lo]) * RPB + rib;
-    const bool valid = g < T.n_groups;
-    const SrcT* __restrict__ row = reinterpret_cast<const SrcT*>(T.weight) + (valid ? g : 0) * row_len;
-
-    Raw8<SrcT> cache[K];
-    bool have[K];
+  Raw8<SrcT> cache[K];
+  bool have[K];
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int64_t j = tir + static_cast<int64_t>(k) * TPR;
-      have[k] = valid && j < nvec;
-      cache[k] = have[k] ? load_raw8<SrcT>(row + j * 8) : zero_raw8<SrcT>();
+  for (int k = 0; k < K; ++k) {
+    const int64_t j = tir + static_cast<int64_t>(k) * TPR;
+    have[k] = FULL || (valid && j < nvec);
+    if constexpr (FULL) cache[k] = load_raw8<SrcT>(row + j * 8);
+    else cache[k] = have[k] ? load_raw8<SrcT>(row + j * 8) : zero_raw8<SrcT>();
+  }
+  // thread-local (min, -max), starting from the neutral element (+inf, +inf) so that vectors which
+  // do not exist contribute nothing
+  MinNegMax m;
+  if constexpr (std::is_same<SrcT, __nv_bfloat16>::value) m.packed = 0x7f807f80u;
+  else if constexpr (std::is_same<SrcT, __half>::value) m.packed = 0x7c007c00u;
+  else m.packed = 0u;
+  m.mn = __uint_as_float(0x7f800000u);
+  m.nmx = __uint_as_float(0x7f800000u);
+  auto fold = [&m](const Raw8<SrcT>& vec) {
+    Raw8<SrcT> one[1] = {vec};
+    const MinNegMax x = min_negmax<SrcT, 1>(one);
+    if constexpr (sizeof(SrcT) == 2) {
+      using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
+      const V2 y = __hmin2(*reinterpret_cast<const V2*>(&m.packed), *reinterpret_cast<const V2*>(&x.packed));
+      m.packed = *reinterpret_cast<const uint32_t*>(&y);
+    } else {
+      m.mn = fminf(m.mn, x.mn);
+      m.nmx = fminf(m.nmx, x.nmx);
     }
-    // thread-local (min, -max), starting from the neutral element (+inf, +inf) so that vectors which
-    // do not exist contribute nothing
-    MinNegMax m;
-    if constexpr (std::is_same<SrcT, __nv_bfloat16>::value) m.packed = 0x7f807f80u;
-    else if constexpr (std::is_same<SrcT, __half>::value) m.packed = 0x7c007c00u;
-    else m.packed = 0u;
-    m.mn = __uint_as_float(0x7f800000u);
-    m.nmx = __uint_as_float(0x7f800000u);
-    auto fold = [&m](const Raw8<SrcT>& vec) {
-      Raw8<SrcT> one[1] = {vec};
-      const MinNegMax x = min_negmax<SrcT, 1>(one);
-      if constexpr (sizeof(SrcT) == 2) {
-        using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
-        const V2 y = __hmin2(*reinterpret_cast<const V2*>(&m.packed), *reinterpret_cast<const V2*>(&x.packed));
-        m.packed = *reinterpret_cast<const uint32_t*>(&y);
-      } else {
-        m.mn = fminf(m.mn, x.mn);
-        m.nmx = fminf(m.nmx, x.nmx);
-      }
-    };
+  };
+  if constexpr (FULL) {
+    m = min_negmax<SrcT, K>(cache);  // all K vectors at once: the (min, -max) packing is paid once
+  } else {
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       if (have[k]) fold(cache[k]);
     }
     for (int64_t j = tir + static_cast<int64_t>(K) * TPR; valid && j < nvec; j += TPR) fold(load_raw8<SrcT>(row + j * 8));
+  }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
-    if (lane == 0) {
-      red16[warp_in_block] = m.packed;
-      red_mn[warp_in_block] = m.mn;
-      red_nmx[warp_in_block] = m.nmx;
-    }
-    __syncthreads();
-    float mn, mx;
-    {
-      MinNegMax t;
-      t.packed = red16[first_warp];
-      t.mn = red_mn[first_warp];
-      t.nmx = red_nmx[first_warp];
+  for (int o = 16; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
+  if (lane == 0) {
+    red16[warp_in_block] = m.packed;
+    red_mn[warp_in_block] = m.mn;
+    red_nmx[warp_in_block] = m.nmx;
+  }
+  __syncthreads();
+  float mn, mx;
+  {
+    MinNegMax t;
+    t.packed = red16[first_warp];
+    t.mn = red_mn[first_warp];
+    t.nmx = red_nmx[first_warp];
 #pragma unroll
-      for (int w = 1; w < WPR; ++w) {
-        if constexpr (sizeof(SrcT) == 2) {
-          using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
-          const uint32_t o = red16[first_warp + w];
-          const V2 y = __hmin2(*reinterpret_cast<const V2*>(&t.packed), *reinterpret_cast<const V2*>(&o));
-          t.packed = *reinterpret_cast<const uint32_t*>(&y);
-        } else {
-          t.mn = fminf(t.mn, red_mn[first_warp + w]);
-          t.nmx = fminf(t.nmx, red_nmx[first_warp + w]);
-        }
-      }
-      finish_minmax<SrcT>(t, mn, mx);
-    }
-    float s, r, zp;
-    bool clamp;  // uniform over the row, hence over the warp (TPR >= 32)
-    int_params<MODE>(mn, mx, s, r, zp, clamp);
-    auto encode = [&](const float2 (&x)[4]) -> uint2 {
-      if constexpr (mode_is_asym(MODE)) {
-        return clamp ? encode8_int<MODE, 2>(x, s, r, zp) : encode8_int<MODE, 0>(x, s, r, zp);
+    for (int w = 1; w < WPR; ++w) {
+      if constexpr (sizeof(SrcT) == 2) {
+        using V2 = typename std::conditional<std::is_same<SrcT, __half>::value, __half2, __nv_bfloat162>::type;
+        const uint32_t o = red16[first_warp + w];
+        const V2 y = __hmin2(*reinterpret_cast<const V2*>(&t.packed), *reinterpret_cast<const V2*>(&o));
+        t.packed = *reinterpret_cast<const uint32_t*>(&y);
       } else {
-        return encode8_int<MODE, 1>(x, s, r, zp);
-      }
-    };
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      if (have[k]) {
-        const int64_t j = tir + static_cast<int64_t>(k) * TPR;
-        float2 x[4];
-        unpack8_pairs(cache[k], x);
-        const uint2 w = encode(x);
-        const int64_t e0 = g * row_len + j * 8;
-        if constexpr (mode_bits(MODE) == 4) {
-          __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
-        } else {
-          __stcs(reinterpret_cast<uint2*>(T.codes + e0), w);
-        }
+        t.mn = fminf(t.mn, red_mn[first_warp + w]);
+        t.nmx = fminf(t.nmx, red_nmx[first_warp + w]);
       }
     }
-    for (int64_t j = tir + static_cast<int64_t>(K) * TPR; valid && j < nvec; j += TPR) {
+    finish_minmax<SrcT>(t, mn, mx);
+  }
+  float s, r, zp;
+  bool clamp;  // uniform over the row, hence over the warp (TPR >= 32)
+  int_params<MODE>(mn, mx, s, r, zp, clamp);
+  auto encode = [&](const float2 (&x)[4]) -> uint2 {
+    if constexpr (mode_is_asym(MODE)) {
+      return clamp ? encode8_int<MODE, 2>(x, s, r, zp) : encode8_int<MODE, 0>(x, s, r, zp);
+    } else {
+      return encode8_int<MODE, 1>(x, s, r, zp);
+    }
+  };
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    if (have[k]) {
+      const int64_t j = tir + static_cast<int64_t>(k) * TPR;
       float2 x[4];
-      unpack8_pairs(load_raw8<SrcT>(row + j * 8), x);
+      unpack8_pairs(cache[k], x);
       const uint2 w = encode(x);
       const int64_t e0 = g * row_len + j * 8;
       if constexpr (mode_bits(MODE) == 4) {
@@ -583,10 +567,45 @@ __global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __gri
         __stcs(reinterpret_cast<uint2*>(T.codes + e0), w);
       }
     }
-    if (valid && tir == 0) {
-      T.scale[g] = s;
-      if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
-      if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+  }
+  for (int64_t j = tir + static_cast<int64_t>(K) * TPR; !FULL && valid && j < nvec; j += TPR) {
+    float2 x[4];
+    unpack8_pairs(load_raw8<SrcT>(row + j * 8), x);
+    const uint2 w = encode(x);
+    const int64_t e0 = g * row_len + j * 8;
+    if constexpr (mode_bits(MODE) == 4) {
+      __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
+    } else {
+      __stcs(reinterpret_cast<uint2*>(T.codes + e0), w);
+    }
+  }
+  if (valid && tir == 0) {
+    T.scale[g] = s;
+    if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
+    if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+  }
+}
+
+template <typename SrcT, int MODE, int TPR>
+__global__ void __launch_bounds__(256, 3) quant_channel_batch_kernel(const __grid_constant__ FastBatch b,
+                                                                     const int64_t row_len) {
+  constexpr int K = WideCache<SrcT>::K;
+  constexpr int RPB = 256 / TPR;  // rows per block
+  __shared__ uint32_t red16[8];
+  __shared__ float red_mn[8], red_nmx[8];
+  const int rib = threadIdx.x / TPR;
+  const bool whole_row = (row_len >> 3) == static_cast<int64_t>(K) * TPR;
+  const int64_t total_iters = b.iter_start[b.n_tensors];  // iterations of RPB rows
+
+  int lo = 0;
+  for (int64_t it = blockIdx.x; it < total_iters; it += gridDim.x) {
+    while (b.iter_start[lo + 1] <= it) ++lo;
+    const FastTensor& T = b.t[lo];
+    const int64_t first = (it - b.iter_start[lo]) * RPB;  // block-uniform
+    if (whole_row && first + RPB <= T.n_groups) {
+      channel_iteration<SrcT, MODE, TPR, true>(T, first + rib, row_len, red16, red_mn, red_nmx);
+    } else {
+      channel_iteration<SrcT, MODE, TPR, false>(T, first + rib, row_len, red16, red_mn, red_nmx);
     }
     __syncthreads();  // red* reused by the next iteration
   }
