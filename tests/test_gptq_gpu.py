@@ -71,8 +71,43 @@ def test_tensor_core_hessian_matches_fp64(dtype, C, tokens):
     assert (H2 - ref2).abs().max().item() <= 2 * tol
 
 
+def test_inverse_factor_routes_agree():
+    """U with H^-1 = U^T U from the reversed-order Cholesky route against the reference's three calls
+    (gptq.py:293-295) and against an fp64 evaluation; dead columns and damping included."""
+    from nncf_b200.gptq import GPTQ
+
+    gen = torch.Generator().manual_seed(11)
+    C = 768
+    x = torch.randn(2048, C, generator=gen)
+    x[:, 5] = 0.0      # dead columns
+    x[:, 700] = 0.0
+    x[:, :8] *= 10.0
+    H = (2.0 / 16) * (x.double().T @ x.double()).float()
+    w = torch.randn(64, C, generator=gen)
+    out = {}
+    for route in ("reversed", "reference"):
+        Hc, wc = H.clone().cuda(), w.clone().cuda()
+        out[route] = GPTQ(0.01, inverse_factor=route).prepare_hessian_inverse(Hc, wc)
+        assert torch.all(wc[:, 5] == 0) and torch.all(wc[:, 700] == 0)
+        assert torch.all(Hc.cpu().diagonal()[[5, 700]] > 1.0)  # dead diagonal = 1 + damping
+        assert torch.equal(out[route], torch.triu(out[route]))
+    H64 = H.double()
+    d = torch.diagonal(H64)
+    d[d == 0] = 1
+    d += 0.01 * d.mean()
+    U64 = torch.linalg.cholesky(torch.linalg.inv(H64), upper=True)
+    err = {k: ((v.cpu().double() - U64).norm() / U64.norm()).item() for k, v in out.items()}
+    rel = ((out["reversed"] - out["reference"]).norm() / out["reference"].norm()).item()
+    print(f"inverse factor: reversed vs reference {rel:.2e}; vs fp64: {err}")
+    assert rel < 2e-5
+    assert err["reversed"] < 2e-5 and err["reversed"] <= 2.0 * err["reference"]
+    with pytest.raises(ValueError):
+        GPTQ(inverse_factor="lu")
+
+
+@pytest.mark.parametrize("route", ["reversed", "reference"])
 @pytest.mark.parametrize("case", GPTQ_CASES, ids=[c[0] for c in GPTQ_CASES])
-def test_gptq_sweep_matches_reference_golden(case):
+def test_gptq_sweep_matches_reference_golden(case, route):
     from nncf_b200.gptq import GPTQ
 
     name, o, C, gs, block, mode, damp, n_in, tokens, xdt = case
@@ -80,7 +115,7 @@ def test_gptq_sweep_matches_reference_golden(case):
     key = f"gptq/{name}"
     H = torch.from_numpy(g[key + "/H"].copy()).cuda()
     w = torch.from_numpy(g[key + "/w"].copy()).cuda()
-    q, s, z = GPTQ(damp, block, n_in)._quantize_weights(_wp(mode, gs), H, w)
+    q, s, z = GPTQ(damp, block, n_in, inverse_factor=route)._quantize_weights(_wp(mode, gs), H, w)
     qref, sref = g[key + "/q"], g[key + "/scale"]
     assert tuple(q.shape) == qref.shape and tuple(s.shape) == sref.shape
     got = q.cpu().numpy()
