@@ -37,34 +37,75 @@ struct GptqArgs {
   int i1, count;       // current block: columns [i1, i1 + count)
 };
 
-// One warp per 32 output rows (a thread owns a row).  The 128-column block is swept in four sub-blocks of
-// 32 columns: the sub-block lives in registers and its triangular update is fully unrolled; the error columns
-// of a finished sub-block are then applied to the rest of the block, column by column in ascending error
-// order, so every weight sees exactly the sequence of rounded multiply / subtract steps that the reference's
-// column loop applies to it (WC/gptq.py:337-358).
+// A warp owns 32 output rows (a thread owns a row); kSweepWarps warps share one copy of the block of Hinv.
+// The 128-column block is swept in four sub-blocks of 32 columns: the sub-block lives in registers and its
+// triangular update is fully unrolled; the error columns of a finished sub-block are then applied to the rest
+// of the block, column by column in ascending error order, so every weight sees exactly the sequence of
+// rounded multiply / subtract steps that the reference's column loop applies to it (WC/gptq.py:337-358).
+// The kernel is a chain of dependent steps, so what matters is the latency of its prologue: Hinv and the
+// weight tile are fetched with wide independent loads by all warps, and the parameters of every group that
+// starts inside the block are computed from the tile before the sweep (the tensor-level weight the reference
+// reads at a group start is this tile as loaded: it is only updated at block ends).
+constexpr int kSweepWarps = 4;
+constexpr int kSweepMaxGroups = 16;  // groups starting inside one block whose parameters are kept in shared memory
+
+struct SweepSmem {
+  static constexpr size_t hs_floats = static_cast<size_t>(kGptqMaxBlock) * kGptqMaxBlock;
+  static constexpr size_t per_warp_floats = 2 * static_cast<size_t>(kGptqMaxBlock) * kSweepLd + 2 * kSweepMaxGroups * kSweepRows;
+  static constexpr size_t bytes = (hs_floats + kSweepWarps * per_warp_floats) * sizeof(float);
+};
+
 template <int MODE>
-__global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a) {
+__global__ void __launch_bounds__(kSweepWarps * kSweepRows) gptq_sweep_kernel(const GptqArgs a) {
   extern __shared__ __align__(16) float smem[];
-  float* hs = smem;                                   // [128][128] Hinv block (row i, col j >= i used)
-  float* ws = hs + kGptqMaxBlock * kGptqMaxBlock;     // [128][33]  weights, column-major per thread
-  float* es = ws + kGptqMaxBlock * kSweepLd;          // [128][33]  error columns
-  const int t = threadIdx.x;
-  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kSweepRows;
+  const int warp = threadIdx.x >> 5, t = threadIdx.x & 31;
+  float* hs = smem;                                                    // [128][128] Hinv block (row i, col j >= i used)
+  float* ws = hs + SweepSmem::hs_floats + warp * SweepSmem::per_warp_floats;  // [128][33] weights, column-major per thread
+  float* es = ws + kGptqMaxBlock * kSweepLd;                           // [128][33] error columns
+  float* ps = es + kGptqMaxBlock * kSweepLd;                           // [16][32] scale of the groups starting here
+  float* pz = ps + kSweepMaxGroups * kSweepRows;                       // [16][32] zero point
+  const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * kSweepWarps + warp) * kSweepRows;
   const int64_t row = row0 + t;
   const bool valid = row < a.rows;
   const int count = a.count, i1 = a.i1;
+  // 16-byte loads need whole, aligned quads of columns
+  const bool vec = count == kGptqMaxBlock && (a.cols & 3) == 0 && (i1 & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(a.hinv) | reinterpret_cast<uintptr_t>(a.w) |
+                     reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.err)) & 15u) == 0;
 
-  for (int idx = t; idx < kGptqMaxBlock * kGptqMaxBlock; idx += kSweepRows) {
-    const int i = idx / kGptqMaxBlock, j = idx - i * kGptqMaxBlock;
-    hs[idx] = (i < count && j < count) ? a.hinv[static_cast<int64_t>(i1 + i) * a.cols + (i1 + j)] : 0.0f;
+  if (vec) {
+    // quads that touch the upper triangle (j + 3 >= i); the rest of hs is never read
+#pragma unroll 8
+    for (int idx = threadIdx.x; idx < kGptqMaxBlock * (kGptqMaxBlock / 4); idx += kSweepWarps * kSweepRows) {
+      const int i = idx >> 5, j = (idx & 31) << 2;
+      if (j + 3 >= i) {
+        *reinterpret_cast<float4*>(hs + i * kGptqMaxBlock + j) =
+            *reinterpret_cast<const float4*>(a.hinv + static_cast<int64_t>(i1 + i) * a.cols + (i1 + j));
+      }
+    }
+#pragma unroll 8
+    for (int r = 0; r < kSweepRows; ++r) {
+      const int64_t rr = row0 + r;
+      if (rr < a.rows) {
+        const float4 v = *reinterpret_cast<const float4*>(a.w + rr * a.cols + i1 + 4 * t);
+        ws[(4 * t + 0) * kSweepLd + r] = v.x;
+        ws[(4 * t + 1) * kSweepLd + r] = v.y;
+        ws[(4 * t + 2) * kSweepLd + r] = v.z;
+        ws[(4 * t + 3) * kSweepLd + r] = v.w;
+      }
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < kGptqMaxBlock * kGptqMaxBlock; idx += kSweepWarps * kSweepRows) {
+      const int i = idx / kGptqMaxBlock, j = idx - i * kGptqMaxBlock;
+      hs[idx] = (i < count && j < count) ? a.hinv[static_cast<int64_t>(i1 + i) * a.cols + (i1 + j)] : 0.0f;
+    }
+    for (int r = 0; r < kSweepRows; ++r) {
+      const int64_t rr = row0 + r;
+      if (rr >= a.rows) break;
+      for (int j = t; j < count; j += kSweepRows) ws[j * kSweepLd + r] = a.w[rr * a.cols + i1 + j];
+    }
   }
-  // weight tile: rows are read along their columns (coalesced), stored column-major per thread
-  for (int r = 0; r < kSweepRows; ++r) {
-    const int64_t rr = row0 + r;
-    if (rr >= a.rows) break;
-    for (int j = t; j < count; j += kSweepRows) ws[j * kSweepLd + r] = a.w[rr * a.cols + i1 + j];
-  }
-  __syncwarp();
+  __syncthreads();
 
   Codec<MODE> c;
   c.from_given(1.0f, 0.0f);
@@ -73,6 +114,41 @@ __global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a
     const int64_t g = i1 / a.gs;
     c.from_given(a.scale[row * a.G + g], a.zp ? static_cast<float>(a.zp[row * a.G + g]) : 0.0f);
   }
+  // parameters of the groups that start inside this block, from the tensor-level weight (WC/gptq.py:312-335):
+  // the columns inside the block are the tile as loaded, later ones are read from global memory
+  const int64_t first_start = ((static_cast<int64_t>(i1) + a.gs - 1) / a.gs) * a.gs;
+  if (valid) {
+    int gl = 0;
+    for (int64_t col = first_start; col < i1 + count; col += a.gs, ++gl) {
+      const int64_t end = min(col + a.gs, a.cols);
+      const int64_t in_block_end = min(end, static_cast<int64_t>(i1 + count));
+      float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
+      for (int64_t kk = col; kk < in_block_end; ++kk) {
+        const float v = ws[(kk - i1) * kSweepLd + t];
+        mn = fminf(mn, v);
+        mx = fmaxf(mx, v);
+      }
+      const float* wr = a.w + row * a.cols;
+      for (int64_t kk = in_block_end; kk < end; ++kk) {
+        const float v = wr[kk];
+        mn = fminf(mn, v);
+        mx = fmaxf(mx, v);
+      }
+      Codec<MODE> cg;
+      cg.from_stats(mn, mx);
+      const int64_t g = col / a.gs;
+      a.scale[row * a.G + g] = cg.scale;
+      if (a.zp) a.zp[row * a.G + g] = static_cast<int32_t>(cg.zp);
+      if (gl < kSweepMaxGroups) {
+        ps[gl * kSweepRows + t] = cg.scale;
+        pz[gl * kSweepRows + t] = cg.zp;
+      }
+    }
+  }
+  // block-relative column of the next group start, advanced in 32-bit arithmetic (no 64-bit modulo per column)
+  int next_start = static_cast<int>(min(first_start - i1, static_cast<int64_t>(kGptqMaxBlock)));
+  const int gs_step = static_cast<int>(min(a.gs, static_cast<int64_t>(kGptqMaxBlock)));
+  int gl_next = 0;
   constexpr int SB = 32;
   for (int sb0 = 0; sb0 < count; sb0 += SB) {
     const int cb = min(SB, count - sb0);
@@ -86,21 +162,17 @@ __global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a
     for (int k = 0; k < SB; ++k) {
       if (k < cb) {
         const int i = sb0 + k;
-        const int64_t col = i1 + i;
-        if (col % a.gs == 0 && valid) {
-          // parameters from the tensor-level weight of this group (WC/gptq.py:312-335)
-          const int64_t end = min(col + a.gs, a.cols);
-          const float* wr = a.w + row * a.cols;
-          float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
-          for (int64_t kk = col; kk < end; ++kk) {
-            const float v = wr[kk];
-            mn = fminf(mn, v);
-            mx = fmaxf(mx, v);
+        if (i == next_start) {  // a group starts at this column
+          if (valid) {
+            if (gl_next < kSweepMaxGroups) {
+              c.from_given(ps[gl_next * kSweepRows + t], pz[gl_next * kSweepRows + t]);
+            } else {
+              const int64_t g = (static_cast<int64_t>(i1) + i) / a.gs;  // written above by this thread
+              c.from_given(a.scale[row * a.G + g], a.zp ? static_cast<float>(a.zp[row * a.G + g]) : 0.0f);
+            }
           }
-          c.from_stats(mn, mx);
-          const int64_t g = col / a.gs;
-          a.scale[row * a.G + g] = c.scale;
-          if (a.zp) a.zp[row * a.G + g] = static_cast<int32_t>(c.zp);
+          next_start += gs_step;
+          ++gl_next;
         }
         const float* hrow = hs + i * kGptqMaxBlock + sb0;
         const float d = hrow[k];
@@ -134,12 +206,28 @@ __global__ void __launch_bounds__(kSweepRows) gptq_sweep_kernel(const GptqArgs a
     }
   }
   __syncwarp();
-  for (int r = 0; r < kSweepRows; ++r) {
-    const int64_t rr = row0 + r;
-    if (rr >= a.rows) break;
-    for (int j = t; j < count; j += kSweepRows) {
-      a.q[rr * a.cols + i1 + j] = ws[j * kSweepLd + r];
-      a.err[rr * kGptqMaxBlock + j] = es[j * kSweepLd + r];
+  if (vec) {
+#pragma unroll 4
+    for (int r = 0; r < kSweepRows; ++r) {
+      const int64_t rr = row0 + r;
+      if (rr < a.rows) {
+        float4 qv, ev;
+        qv.x = ws[(4 * t + 0) * kSweepLd + r]; ev.x = es[(4 * t + 0) * kSweepLd + r];
+        qv.y = ws[(4 * t + 1) * kSweepLd + r]; ev.y = es[(4 * t + 1) * kSweepLd + r];
+        qv.z = ws[(4 * t + 2) * kSweepLd + r]; ev.z = es[(4 * t + 2) * kSweepLd + r];
+        qv.w = ws[(4 * t + 3) * kSweepLd + r]; ev.w = es[(4 * t + 3) * kSweepLd + r];
+        *reinterpret_cast<float4*>(a.q + rr * a.cols + i1 + 4 * t) = qv;
+        *reinterpret_cast<float4*>(a.err + rr * kGptqMaxBlock + 4 * t) = ev;
+      }
+    }
+  } else {
+    for (int r = 0; r < kSweepRows; ++r) {
+      const int64_t rr = row0 + r;
+      if (rr >= a.rows) break;
+      for (int j = t; j < count; j += kSweepRows) {
+        a.q[rr * a.cols + i1 + j] = ws[j * kSweepLd + r];
+        a.err[rr * kGptqMaxBlock + j] = es[j * kSweepLd + r];
+      }
     }
   }
 }
@@ -193,14 +281,14 @@ __global__ void __launch_bounds__(256) gptq_trailing_kernel(const GptqArgs a, co
 
 template <int MODE>
 int run_gptq(GptqArgs a, int block, cudaStream_t st) {
-  const size_t smem = (static_cast<size_t>(kGptqMaxBlock) * kGptqMaxBlock + 2 * kGptqMaxBlock * kSweepLd) * sizeof(float);
+  const size_t smem = SweepSmem::bytes;
   NNCFB_CUDA(cudaFuncSetAttribute(gptq_sweep_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
-  const unsigned row_blocks = static_cast<unsigned>((a.rows + kSweepRows - 1) / kSweepRows);
+  const unsigned row_blocks = static_cast<unsigned>((a.rows + kSweepWarps * kSweepRows - 1) / (kSweepWarps * kSweepRows));
   for (int64_t i1 = 0; i1 < a.cols; i1 += block) {
     a.i1 = static_cast<int>(i1);
     a.count = static_cast<int>(std::min<int64_t>(block, a.cols - i1));
-    gptq_sweep_kernel<MODE><<<row_blocks, kSweepRows, smem, st>>>(a);
+    gptq_sweep_kernel<MODE><<<row_blocks, kSweepWarps * kSweepRows, smem, st>>>(a);
     const int64_t c0 = i1 + a.count;
     if (c0 < a.cols) {
       const dim3 grid(static_cast<unsigned>((a.cols - c0 + 63) / 64), static_cast<unsigned>((a.rows + 63) / 64));
