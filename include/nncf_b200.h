@@ -164,8 +164,9 @@ int nncfb_awq_search(const void* weight, int32_t weight_dtype, int64_t rows, int
  * beta = 2/(n+b) per call.  With allow_tensor_cores != 0 and a 16-bit activation whose channel count is a
  * multiple of 64 (>= 256) the contraction runs on tcgen05 tensor cores (exact 16-bit products, fp32
  * accumulation in tensor memory, operands by TMA); otherwise an fp32 CUDA-core kernel runs.  The
- * tensor-core kernel bounds every wait; nncfb_hessian_status() (synchronises the stream) returns
- * NNCFB_E_TIMEOUT if one gave up.  workspace is reserved (may be NULL).
+ * tensor-core kernels (this one and the GPTQ trailing update) bound every wait; nncfb_hessian_status()
+ * (synchronises the stream) returns NNCFB_E_TIMEOUT if one gave up since the flag was last cleared (every
+ * Hessian launch and every nncfb_gptq_quantize call clears it first).  workspace is reserved (may be NULL).
  * Replaces WC/gptq.py:200-242 (GPTQ._calculate_hessian).
  */
 int nncfb_hessian_accumulate(float* hessian, int64_t channels, const void* x, int32_t dtype, int64_t tokens,
@@ -180,10 +181,16 @@ int nncfb_hessian_status(void* stream);
  * at each group start from the tensor-level weight, quantise-dequantise column by column with error feedback
  * inside the block, then weight[:, i2:] -= Err @ hinv[i1:i2, i2:].  Outputs: q_out [rows, cols] fp32
  * dequantised weight, scale_out [rows, G] fp32, zp_out [rows, G] int32 (asymmetric modes).
- * workspace: caller-provided scratch of nncfb_gptq_workspace_bytes(rows) bytes.
+ * workspace: caller-provided scratch.  nncfb_gptq_workspace_bytes(rows) is the minimum; the trailing update is
+ * then an fp32 CUDA-core contraction.  With nncfb_gptq_workspace_bytes_tensor_cores(rows, cols) bytes, and
+ * block_size = 128, rows % 8 == 0, cols % 4 == 0, it runs on the tcgen05 tensor cores instead: both fp32
+ * operands are split into three bf16 planes and six plane products are accumulated in fp32 in tensor memory
+ * (agrees with the fp32 contraction to ~1e-7 relative).  That kernel bounds every wait like the Hessian kernel;
+ * nncfb_hessian_status() reports a wait that gave up.
  * Replaces WC/gptq.py:297-379 (the loop of GPTQ._quantize_weights).
  */
 size_t nncfb_gptq_workspace_bytes(int64_t rows);
+size_t nncfb_gptq_workspace_bytes_tensor_cores(int64_t rows, int64_t cols);
 int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode, int64_t group_size,
                         int32_t block_size, float* q_out, float* scale_out, int32_t* zp_out, void* workspace,
                         size_t workspace_bytes, void* stream);

@@ -66,6 +66,7 @@ def _load() -> C.CDLL:
         "nncfb_hessian_accumulate": ([vp, i64, vp, i32, i64, C.c_float, C.c_float, i32, vp, C.c_size_t, vp], C.c_int),
         "nncfb_hessian_status": ([vp], C.c_int),
         "nncfb_gptq_workspace_bytes": ([i64], C.c_size_t),
+        "nncfb_gptq_workspace_bytes_tensor_cores": ([i64, i64], C.c_size_t),
         "nncfb_gptq_quantize": ([vp, i64, i64, vp, i32, i64, i32, vp, vp, vp, vp, C.c_size_t, vp], C.c_int),
         "nncfb_gptq_quantize_noalloc": ([vp, i64, i64, vp, i32, i64, i32, vp, vp, vp, vp], C.c_int),
         "nncfb_decompress": ([vp, i32, i64, i64, vp, vp, vp, i32, vp], C.c_int),
@@ -83,7 +84,8 @@ def _load() -> C.CDLL:
 lib = _load()
 EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_quantize_batch",
             "nncfb_scale_estimation", "nncfb_awq_workspace_bytes", "nncfb_awq_search", "nncfb_channel_stats",
-            "nncfb_hessian_accumulate", "nncfb_hessian_status", "nncfb_gptq_workspace_bytes", "nncfb_gptq_quantize",
+            "nncfb_hessian_accumulate", "nncfb_hessian_status", "nncfb_gptq_workspace_bytes",
+            "nncfb_gptq_workspace_bytes_tensor_cores", "nncfb_gptq_quantize",
             "nncfb_gptq_quantize_noalloc", "nncfb_decompress",
             "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
             "nncfb_selftest_division"]

@@ -30,6 +30,8 @@ struct GptqArgs {
   const float* hinv;   // [cols, cols] upper Cholesky factor of H^-1
   float* q;            // [rows, cols] dequantised result
   float* err;          // [rows, kGptqMaxBlock] scratch: error columns of the current block
+  __nv_bfloat16* err_planes;  // optional [3 * 128, err_ld]: the same errors as three bf16 planes, transposed
+  int64_t err_ld;
   float* scale;        // [rows, G]
   int32_t* zp;         // [rows, G] or null
   int64_t rows, cols;
@@ -206,6 +208,17 @@ __global__ void __launch_bounds__(kSweepWarps * kSweepRows) gptq_sweep_kernel(co
     }
   }
   __syncwarp();
+  if (a.err_planes != nullptr && valid) {
+    // operand of the tensor-core trailing update: plane p, row k, column = this thread's output row
+#pragma unroll 4
+    for (int j = 0; j < count; ++j) {
+      __nv_bfloat16 h, m, l;
+      split_bf16x3(es[j * kSweepLd + t], h, m, l);
+      a.err_planes[(0 * kGptqMaxBlock + j) * a.err_ld + row] = h;
+      a.err_planes[(1 * kGptqMaxBlock + j) * a.err_ld + row] = m;
+      a.err_planes[(2 * kGptqMaxBlock + j) * a.err_ld + row] = l;
+    }
+  }
   if (vec) {
 #pragma unroll 4
     for (int r = 0; r < kSweepRows; ++r) {
@@ -279,20 +292,43 @@ __global__ void __launch_bounds__(256) gptq_trailing_kernel(const GptqArgs a, co
   }
 }
 
+// tensor-core trailing update and its helpers (hessian_tc.cu)
+bool gptq_trailing_tc_available();
+int tc_status_reset(cudaStream_t st);
+int gptq_trailing_tc(float* w_c0, int64_t ld, int64_t rows, int64_t n, const float* hinv, int64_t cols, int i1, int64_t c0,
+                     const __nv_bfloat16* err_planes, int64_t err_ld, __nv_bfloat16* slab_planes, int64_t slab_ld,
+                     cudaStream_t st);
+
+struct GptqTcScratch {
+  __nv_bfloat16* slab_planes = nullptr;  // [3 * 128, slab_ld]
+  int64_t slab_ld = 0;
+};
+
 template <int MODE>
-int run_gptq(GptqArgs a, int block, cudaStream_t st) {
+int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, cudaStream_t st) {
   const size_t smem = SweepSmem::bytes;
   NNCFB_CUDA(cudaFuncSetAttribute(gptq_sweep_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
   const unsigned row_blocks = static_cast<unsigned>((a.rows + kSweepWarps * kSweepRows - 1) / (kSweepWarps * kSweepRows));
+  const bool use_tc = tc.slab_planes != nullptr;
+  if (use_tc) {
+    const int rc = tc_status_reset(st);
+    if (rc != NNCFB_OK) return rc;
+  }
   for (int64_t i1 = 0; i1 < a.cols; i1 += block) {
     a.i1 = static_cast<int>(i1);
     a.count = static_cast<int>(std::min<int64_t>(block, a.cols - i1));
     gptq_sweep_kernel<MODE><<<row_blocks, kSweepWarps * kSweepRows, smem, st>>>(a);
     const int64_t c0 = i1 + a.count;
     if (c0 < a.cols) {
-      const dim3 grid(static_cast<unsigned>((a.cols - c0 + 63) / 64), static_cast<unsigned>((a.rows + 63) / 64));
-      gptq_trailing_kernel<<<grid, 256, 0, st>>>(a, c0);
+      if (use_tc) {
+        const int rc = gptq_trailing_tc(a.w + c0, a.cols, a.rows, a.cols - c0, a.hinv, a.cols, a.i1, c0, a.err_planes,
+                                        a.err_ld, tc.slab_planes, tc.slab_ld, st);
+        if (rc != NNCFB_OK) return rc;
+      } else {
+        const dim3 grid(static_cast<unsigned>((a.cols - c0 + 63) / 64), static_cast<unsigned>((a.rows + 63) / 64));
+        gptq_trailing_kernel<<<grid, 256, 0, st>>>(a, c0);
+      }
     }
   }
   NNCFB_CUDA(cudaGetLastError());
@@ -366,8 +402,20 @@ __global__ void __launch_bounds__(256) mirror_upper_kernel(float* __restrict__ H
 
 using namespace nncfb;
 
+namespace {
+constexpr size_t align1k(size_t v) { return (v + 1023) & ~static_cast<size_t>(1023); }
+size_t err_bytes(int64_t rows) { return align1k(static_cast<size_t>(rows) * kGptqMaxBlock * sizeof(float)); }
+int64_t round8(int64_t v) { return (v + 7) & ~static_cast<int64_t>(7); }
+size_t planes_bytes(int64_t extent) { return align1k(static_cast<size_t>(3) * kGptqMaxBlock * round8(extent) * 2); }
+}  // namespace
+
 extern "C" size_t nncfb_gptq_workspace_bytes(int64_t rows) {
   return rows > 0 ? static_cast<size_t>(rows) * kGptqMaxBlock * sizeof(float) : 0;
+}
+
+extern "C" size_t nncfb_gptq_workspace_bytes_tensor_cores(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return err_bytes(rows) + planes_bytes(rows) + planes_bytes(cols);
 }
 
 extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
@@ -388,6 +436,8 @@ extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, co
   a.hinv = hinv;
   a.q = q_out;
   a.err = static_cast<float*>(workspace);
+  a.err_planes = nullptr;
+  a.err_ld = 0;
   a.scale = scale_out;
   a.zp = mode_is_asym(mode) ? zp_out : nullptr;
   a.rows = rows;
@@ -396,15 +446,28 @@ extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, co
   a.G = cols / group_size;
   a.i1 = 0;
   a.count = 0;
+  // The trailing update runs on the tensor cores when the caller's workspace has room for the operand planes
+  // (nncfb_gptq_workspace_bytes_tensor_cores) and the shapes allow 16-byte rows: full 128-column blocks, more
+  // than one block, rows % 8 == 0, cols % 4 == 0, 16-byte aligned weight.  Otherwise the fp32 CUDA-core kernel.
+  GptqTcScratch tc;
+  if (workspace_bytes >= nncfb_gptq_workspace_bytes_tensor_cores(rows, cols) && block_size == kGptqMaxBlock &&
+      cols > kGptqMaxBlock && rows % 8 == 0 && cols % 4 == 0 && aligned16(weight) && aligned16(workspace) &&
+      gptq_trailing_tc_available()) {
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    a.err_planes = reinterpret_cast<__nv_bfloat16*>(base + err_bytes(rows));
+    a.err_ld = round8(rows);
+    tc.slab_planes = reinterpret_cast<__nv_bfloat16*>(base + err_bytes(rows) + planes_bytes(rows));
+    tc.slab_ld = round8(cols);
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (mode) {
-    case NNCFB_INT4_SYM: return run_gptq<NNCFB_INT4_SYM>(a, block_size, st);
-    case NNCFB_INT4_ASYM: return run_gptq<NNCFB_INT4_ASYM>(a, block_size, st);
-    case NNCFB_INT8_SYM: return run_gptq<NNCFB_INT8_SYM>(a, block_size, st);
-    case NNCFB_INT8_ASYM: return run_gptq<NNCFB_INT8_ASYM>(a, block_size, st);
-    case NNCFB_NF4: return run_gptq<NNCFB_NF4>(a, block_size, st);
-    case NNCFB_FP4: return run_gptq<NNCFB_FP4>(a, block_size, st);
-    case NNCFB_MXFP4: return run_gptq<NNCFB_MXFP4>(a, block_size, st);
+    case NNCFB_INT4_SYM: return run_gptq<NNCFB_INT4_SYM>(a, block_size, tc, st);
+    case NNCFB_INT4_ASYM: return run_gptq<NNCFB_INT4_ASYM>(a, block_size, tc, st);
+    case NNCFB_INT8_SYM: return run_gptq<NNCFB_INT8_SYM>(a, block_size, tc, st);
+    case NNCFB_INT8_ASYM: return run_gptq<NNCFB_INT8_ASYM>(a, block_size, tc, st);
+    case NNCFB_NF4: return run_gptq<NNCFB_NF4>(a, block_size, tc, st);
+    case NNCFB_FP4: return run_gptq<NNCFB_FP4>(a, block_size, tc, st);
+    case NNCFB_MXFP4: return run_gptq<NNCFB_MXFP4>(a, block_size, tc, st);
     default: break;
   }
   set_error("nncfb_gptq_quantize: mode %d is not supported", mode);

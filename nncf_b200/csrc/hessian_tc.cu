@@ -16,6 +16,12 @@
 //   warp 0        TMA producer (one elected lane), 4-stage ring, mbarrier expect-tx
 //   warp 1        tensor-memory allocation, MMA issue (one elected lane), tcgen05.commit
 //   warps 2..5    epilogue: tcgen05.ld of the fp32 accumulators, H = alpha*H + beta*acc
+// The same kernel, with two tensor maps and twelve K segments, is the lazy-batch trailing update of the
+// GPTQ sweep, W[:, i2:] -= Err_blk @ Hinv[i1:i2, i2:] (WC/gptq.py:361-363): both fp32 operands are split into
+// three bf16 planes (hi + mid + lo = the fp32 value to 2^-27), stored with the block's 128 rows of K as the
+// slow axis, and six plane products (everything down to 2^-24 relative) are accumulated in fp32 in tensor
+// memory, smallest terms first.  That update is bound by the read-modify-write of W, so its variant keeps
+// two stages per CTA and two CTAs per SM: one CTA's epilogue overlaps the other's loads and MMAs.
 // Every wait is bounded: after kSpinLimit polls a role records an error code in a global flag
 // and leaves; the other roles then time out the same way, tensor memory is released and the
 // kernel returns (the host reports NNCFB_E_TIMEOUT).  No multicast, no cluster, no peer memory.
@@ -31,7 +37,9 @@ constexpr int kTileM = 128;
 constexpr int kTileN = 256;
 constexpr int kBoxC = 64;    // channels per TMA box (128 bytes of bf16)
 constexpr int kBlockK = 64;  // tokens per pipeline stage
-constexpr int kStages = 4;
+constexpr int kStagesHessian = 4;
+constexpr int kStagesTrailing = 2;
+constexpr int kMaxStages = 4;
 constexpr int kBoxBytes = kBoxC * kBlockK * 2;                           // 8192
 constexpr int kStageBytes = (kTileM / kBoxC + kTileN / kBoxC) * kBoxBytes;  // 49152
 constexpr int kTmemCols = 256;
@@ -112,33 +120,45 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 struct __align__(8) Control {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_ready;
   uint32_t tmem_base;
   uint32_t pad;
 };
 
-__global__ void __launch_bounds__(192, 1)
-hessian_tc_kernel(const __grid_constant__ CUtensorMap xmap, float* __restrict__ H, int64_t C, int64_t tokens,
-                  float alpha, float beta, uint32_t idesc, int n_tiles_n, int* __restrict__ status) {
+// TRAILING = false: D = H [C, C], upper-triangle tiles, K = tokens, both operands from `amap`.
+// TRAILING = true:  D = W + c0 [rows, n_bound] with leading dimension ld, all tiles, twelve K segments of 64:
+//                   plane pair (pa, pb) x two halves of the 128-row block; A planes in `amap`, B planes in `bmap`,
+//                   each a 2-D tensor [3 * 128, extent] with plane p at rows [128 p, 128 p + 128).
+template <int kStages, bool TRAILING>
+__global__ void __launch_bounds__(192, TRAILING ? 2 : 1)
+tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, float* __restrict__ H,
+             int64_t ld, int64_t m_bound, int64_t n_bound, int64_t tokens, float alpha, float beta, uint32_t idesc,
+             int n_tiles_n, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte aligned operand ring (swizzle-128B atoms must start on 1 KiB), control block behind it
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Control* ctl = reinterpret_cast<Control*>(ring + kStages * kStageBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // tile -> (mi, nj) with nj >= mi / 2 (tiles that touch the upper triangle)
-  int mi = 0, rem = blockIdx.x;
-  for (;;) {
-    const int row_tiles = n_tiles_n - mi / 2;
-    if (rem < row_tiles) break;
-    rem -= row_tiles;
-    ++mi;
+  int mi = 0, nj = 0;
+  if constexpr (TRAILING) {
+    mi = blockIdx.x / n_tiles_n;
+    nj = blockIdx.x - mi * n_tiles_n;
+  } else {
+    // tile -> (mi, nj) with nj >= mi / 2 (tiles that touch the upper triangle)
+    int rem = blockIdx.x;
+    for (;;) {
+      const int row_tiles = n_tiles_n - mi / 2;
+      if (rem < row_tiles) break;
+      rem -= row_tiles;
+      ++mi;
+    }
+    nj = mi / 2 + rem;
   }
-  const int nj = mi / 2 + rem;
   const int m0 = mi * kTileM, n0 = nj * kTileN;
-  const int k_iters = static_cast<int>((tokens + kBlockK - 1) / kBlockK);
+  const int k_iters = TRAILING ? 12 : static_cast<int>((tokens + kBlockK - 1) / kBlockK);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -174,12 +194,18 @@ hessian_tc_kernel(const __grid_constant__ CUtensorMap xmap, float* __restrict__ 
         }
         uint8_t* stage = ring + s * kStageBytes;
         mbar_expect_tx(&ctl->full[s], kStageBytes);
-        const int tok = it * kBlockK;
+        int ka = it * kBlockK, kb = ka;
+        if constexpr (TRAILING) {
+          // plane pairs, smallest products first: (lo,hi) (hi,lo) (mid,mid) (mid,hi) (hi,mid) (hi,hi); hi = plane 0
+          const int combo = it >> 1, half = it & 1;
+          ka = static_cast<int>((0x001102u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
+          kb = static_cast<int>((0x010120u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
+        }
 #pragma unroll
-        for (int b = 0; b < kTileM / kBoxC; ++b) tma_load_2d(stage + b * kBoxBytes, &xmap, m0 + b * kBoxC, tok, &ctl->full[s]);
+        for (int b = 0; b < kTileM / kBoxC; ++b) tma_load_2d(stage + b * kBoxBytes, &amap, m0 + b * kBoxC, ka, &ctl->full[s]);
 #pragma unroll
         for (int b = 0; b < kTileN / kBoxC; ++b)
-          tma_load_2d(stage + (kTileM / kBoxC + b) * kBoxBytes, &xmap, n0 + b * kBoxC, tok, &ctl->full[s]);
+          tma_load_2d(stage + (kTileM / kBoxC + b) * kBoxBytes, &bmap, n0 + b * kBoxC, kb, &ctl->full[s]);
         ++issued;
       }
       // do not leave while a copy into this CTA's shared memory may still be in flight: wait (bounded)
@@ -219,32 +245,45 @@ hessian_tc_kernel(const __grid_constant__ CUtensorMap xmap, float* __restrict__ 
     }
   } else {
     // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ------------------------------
+    const int q = warp & 3;
+    const int64_t r = static_cast<int64_t>(m0) + q * 32 + lane;
+    // While the MMAs run, pull this thread's row of the D tile (eight 128-byte lines) into L2: the
+    // read-modify-write below would otherwise wait for DRAM once per step.
+    if (r < m_bound) {
+      const float* drow = H + r * ld + n0;
+#pragma unroll
+      for (int c = 0; c < kTileN; c += 32) {
+        if (n0 + c < n_bound) asm volatile("prefetch.global.L2 [%0];" ::"l"(drow + c));
+      }
+    }
     const bool ok = mbar_wait(&ctl->acc_ready, 0);
     if (!ok && lane == 0) atomicExch(status, 3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool good = ok && (*reinterpret_cast<volatile int*>(status) == 0);
     if (good) {
-      const int q = warp & 3;
-      const int64_t r = static_cast<int64_t>(m0) + q * 32 + lane;
+      // tcgen05.ld hands each lane one accumulator row, 32 columns (one 128-byte line of D) per step.  The
+      // eight 16-byte loads of a step are issued together, before the first store, so that they overlap.
 #pragma unroll 1
       for (int c = 0; c < kTileN; c += 32) {
         uint32_t acc[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c), acc);
-        if (r < C) {
-          float* hrow = H + r * C + n0 + c;
+        if (r < m_bound) {
+          float* hrow = H + r * ld + n0 + c;
+          if (n0 + c + 31 < n_bound) {
+            float4 h[8];
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            if (n0 + c + j + 3 < C) {
-              float4 h = *reinterpret_cast<float4*>(hrow + j);
-              h.x = __fmaf_rn(beta, __uint_as_float(acc[j]), __fmul_rn(alpha, h.x));
-              h.y = __fmaf_rn(beta, __uint_as_float(acc[j + 1]), __fmul_rn(alpha, h.y));
-              h.z = __fmaf_rn(beta, __uint_as_float(acc[j + 2]), __fmul_rn(alpha, h.z));
-              h.w = __fmaf_rn(beta, __uint_as_float(acc[j + 3]), __fmul_rn(alpha, h.w));
-              *reinterpret_cast<float4*>(hrow + j) = h;
-            } else {
-              for (int jj = j; jj < j + 4; ++jj) {
-                if (n0 + c + jj < C) hrow[jj] = __fmaf_rn(beta, __uint_as_float(acc[jj]), __fmul_rn(alpha, hrow[jj]));
-              }
+            for (int j = 0; j < 8; ++j) h[j] = *reinterpret_cast<const float4*>(hrow + 4 * j);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              h[j].x = __fmaf_rn(beta, __uint_as_float(acc[4 * j]), __fmul_rn(alpha, h[j].x));
+              h[j].y = __fmaf_rn(beta, __uint_as_float(acc[4 * j + 1]), __fmul_rn(alpha, h[j].y));
+              h[j].z = __fmaf_rn(beta, __uint_as_float(acc[4 * j + 2]), __fmul_rn(alpha, h[j].z));
+              h[j].w = __fmaf_rn(beta, __uint_as_float(acc[4 * j + 3]), __fmul_rn(alpha, h[j].w));
+              *reinterpret_cast<float4*>(hrow + 4 * j) = h[j];
+            }
+          } else {
+            for (int jj = 0; jj < 32; ++jj) {
+              if (n0 + c + jj < n_bound) hrow[jj] = __fmaf_rn(beta, __uint_as_float(acc[jj]), __fmul_rn(alpha, hrow[jj]));
             }
           }
         }
@@ -299,43 +338,121 @@ EncodeTiledFn encode_tiled_fn() {
 // Per-device error flag of the tensor-core kernel (static device memory: nothing is allocated).
 __device__ int g_hessian_status;
 
-int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t tokens, float alpha, float beta,
-                          void* /*workspace*/, size_t /*workspace_bytes*/, cudaStream_t st) {
-  if (C % 64 != 0 || C < 256 || !aligned16(x) || !aligned16(H) || tokens <= 0 || tokens > 0x7fffffff ||
-      C > 0x7fffffff / 2)
-    return NNCFB_E_UNSUPPORTED;
+namespace {
+
+int status_address(int** status) {
+  NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(status), g_hessian_status));
+  return NNCFB_OK;
+}
+
+// instruction descriptor: fp32 accumulate, A/B format, both operands MN-major, N >> 3, M >> 4
+uint32_t instr_desc(bool bf16) {
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+         (static_cast<uint32_t>(kTileM >> 4) << 24);
+}
+
+// 2-D map over a row-major 16-bit matrix [k_rows, extent] with `ld` elements between rows; boxes of
+// 64 (extent) x 64 (k) with the 128-byte swizzle the operand descriptors expect.
+int encode_map(CUtensorMap* map, const void* base, bool bf16, int64_t extent, int64_t k_rows, int64_t ld) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return NNCFB_E_UNSUPPORTED;
-  CUtensorMap map;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(tokens)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(C) * 2};
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(extent), static_cast<cuuint64_t>(k_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
   const cuuint32_t box[2] = {kBoxC, kBlockK};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult cr = encode(&map, dtype == NNCFB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                             2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const CUresult cr = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with code %d", static_cast<int>(cr));
     return NNCFB_E_CUDA;
   }
+  return NNCFB_OK;
+}
+
+template <int kStages>
+constexpr size_t tc_smem_bytes() { return static_cast<size_t>(kStages) * kStageBytes + sizeof(Control) + 1024; }
+
+}  // namespace
+
+int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t tokens, float alpha, float beta,
+                          void* /*workspace*/, size_t /*workspace_bytes*/, cudaStream_t st) {
+  if (C % 64 != 0 || C < 256 || !aligned16(x) || !aligned16(H) || tokens <= 0 || tokens > 0x7fffffff ||
+      C > 0x7fffffff / 2)
+    return NNCFB_E_UNSUPPORTED;
+  CUtensorMap map;
+  const int rc = encode_map(&map, x, dtype == NNCFB_BF16, C, tokens, C);
+  if (rc != NNCFB_OK) return rc;
   const int tiles_m = static_cast<int>((C + kTileM - 1) / kTileM);
   const int tiles_n = static_cast<int>((C + kTileN - 1) / kTileN);
   int n_tiles = 0;
   for (int mi = 0; mi < tiles_m; ++mi) n_tiles += tiles_n - mi / 2;
-  // instruction descriptor: fp32 accumulate, A/B format, both operands MN-major, N >> 3, M >> 4
-  const uint32_t fmt = dtype == NNCFB_BF16 ? 1u : 0u;
-  const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) |
-                         (static_cast<uint32_t>(kTileN >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
-  const size_t smem = static_cast<size_t>(kStages) * kStageBytes + sizeof(Control) + 1024;
-  NNCFB_CUDA(cudaFuncSetAttribute(hessian_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  constexpr size_t smem = tc_smem_bytes<kStagesHessian>();
+  auto kernel = tc_tn_kernel<kStagesHessian, false>;
+  NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   int* status = nullptr;
-  NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_hessian_status));
+  if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
   NNCFB_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
-  hessian_tc_kernel<<<n_tiles, 192, smem, st>>>(map, H, C, tokens, alpha, beta, idesc, tiles_n, status);
+  kernel<<<n_tiles, 192, smem, st>>>(map, map, H, C, C, C, tokens, alpha, beta, instr_desc(dtype == NNCFB_BF16), tiles_n,
+                                     status);
   NNCFB_CUDA(cudaGetLastError());
   const dim3 mgrid(static_cast<unsigned>((C + 31) / 32), static_cast<unsigned>((C + 31) / 32));
   mirror_upper_tc_kernel<<<mgrid, 256, 0, st>>>(H, C);
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+// ---- GPTQ trailing update on the tensor cores -------------------------------------------------------
+// Three bf16 planes of one 128-row slab of the upper factor: planes[p][k][j] ~ Hinv[i1 + k][c0 + j].
+__global__ void __launch_bounds__(256) gptq_split_slab_kernel(const float* __restrict__ hinv, int64_t cols, int i1,
+                                                              int64_t c0, int64_t n, int64_t ld,
+                                                              __nv_bfloat16* __restrict__ planes) {
+  const int k = blockIdx.y;
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (j >= n) return;
+  __nv_bfloat16 h, m, l;
+  split_bf16x3(hinv[static_cast<int64_t>(i1 + k) * cols + c0 + j], h, m, l);
+  planes[(0 * 128 + k) * ld + j] = h;
+  planes[(1 * 128 + k) * ld + j] = m;
+  planes[(2 * 128 + k) * ld + j] = l;
+}
+
+bool gptq_trailing_tc_available() { return encode_tiled_fn() != nullptr; }
+
+// Clears the sticky error flag the tensor-core kernels share (read back with nncfb_hessian_status).
+int tc_status_reset(cudaStream_t st) {
+  int* status = nullptr;
+  if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
+  NNCFB_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  return NNCFB_OK;
+}
+
+// W[:, c0 : c0 + n] -= Err @ Hinv[i1 : i1 + 128, c0 : c0 + n].
+//   w_c0      = W + c0 (row stride ld floats; W 16-byte aligned, ld and c0 multiples of 4)
+//   err_planes: bf16 [3 * 128, err_ld], plane p row k column r = plane p of Err[r][k]  (written by the sweep kernel)
+//   slab_planes: bf16 [3 * 128, slab_ld] scratch, filled here from hinv
+int gptq_trailing_tc(float* w_c0, int64_t ld, int64_t rows, int64_t n, const float* hinv, int64_t cols, int i1, int64_t c0,
+                     const __nv_bfloat16* err_planes, int64_t err_ld, __nv_bfloat16* slab_planes, int64_t slab_ld,
+                     cudaStream_t st) {
+  const dim3 sgrid(static_cast<unsigned>((n + 255) / 256), 128);
+  gptq_split_slab_kernel<<<sgrid, 256, 0, st>>>(hinv, cols, i1, c0, n, slab_ld, slab_planes);
+  NNCFB_CUDA(cudaGetLastError());
+  CUtensorMap amap, bmap;
+  int rc = encode_map(&amap, err_planes, true, rows, 3 * 128, err_ld);
+  if (rc != NNCFB_OK) return rc;
+  rc = encode_map(&bmap, slab_planes, true, n, 3 * 128, slab_ld);
+  if (rc != NNCFB_OK) return rc;
+  const int tiles_m = static_cast<int>((rows + kTileM - 1) / kTileM);
+  const int tiles_n = static_cast<int>((n + kTileN - 1) / kTileN);
+  constexpr size_t smem = tc_smem_bytes<kStagesTrailing>();
+  auto kernel = tc_tn_kernel<kStagesTrailing, true>;
+  NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  int* status = nullptr;
+  if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
+  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, w_c0, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
+                                               status);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
 }

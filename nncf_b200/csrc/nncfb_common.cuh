@@ -60,6 +60,16 @@ __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(
 template <>
 __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// fp32 value as the sum of three bf16 numbers (round to nearest at each step; the two remainders are exact
+// in fp32): |v - (hi + mid + lo)| <= 2^-27 |v| for values whose low planes stay clear of the subnormals.
+__device__ __forceinline__ void split_bf16x3(float v, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
+  hi = __float2bfloat16_rn(v);
+  const float r1 = __fsub_rn(v, __bfloat162float(hi));
+  mid = __float2bfloat16_rn(r1);
+  const float r2 = __fsub_rn(r1, __bfloat162float(mid));
+  lo = __float2bfloat16_rn(r2);
+}
+
 // ---- exact fp32 division by a per-group constant -----------------------------------------
 // The reference divides every weight by its group's scale with a true IEEE division
 // (WC/weight_lowering.py:678, :626).  One division per element is the most expensive step

@@ -1,8 +1,9 @@
 """GPTQ: host mirror of src/nncf/quantization/algorithms/weight_compression/gptq.py
 (``_calculate_hessian`` :200-242 and ``_quantize_weights`` :244-379, same argument meaning and
 result shapes).  The Hessian contraction runs on the tcgen05 tensor cores (``nncfb_hessian_accumulate``),
-the blocked column sweep and its trailing updates in ``nncfb_gptq_quantize``; dead-column fix-up, damping
-and the three Cholesky steps are small library calls (torch.linalg / cuSOLVER) like in the reference."""
+the blocked column sweep in ``nncfb_gptq_quantize`` with its trailing updates on the tensor cores too (bf16x3
+operand planes, fp32 accumulate); dead-column fix-up, damping and the Cholesky steps are library calls
+(torch.linalg / cuSOLVER) like in the reference."""
 
 from __future__ import annotations
 
@@ -125,13 +126,17 @@ class GPTQ:
         q = torch.empty_like(weight_tensor)
         scale = torch.empty((rows, G), dtype=torch.float32, device=dev)
         zp = torch.empty((rows, G), dtype=torch.int32, device=dev) if config.is_asym_mode else None
-        ws_bytes = int(_lib.lib.nncfb_gptq_workspace_bytes(rows))
+        # room for the operand planes of the tensor-core trailing update when that path is wanted
+        ws_bytes = int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, cols) if self._tensor_cores
+                       else _lib.lib.nncfb_gptq_workspace_bytes(rows))
         workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib.nncfb_gptq_quantize(
                 _lib.ptr(weight_tensor), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[config.mode.value], gs,
                 self._block_size, _lib.ptr(q), _lib.ptr(scale), _lib.ptr(zp), _lib.ptr(workspace), ws_bytes,
                 _lib.stream_handle(dev)))
+            if self._tensor_cores:
+                _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(dev)))  # bounded waits of the TC kernels
         scales = scale.reshape(rows, G, 1)
         zero_points = zp.reshape(rows, G, 1) if zp is not None else None
         if config.group_size == -1:

@@ -150,3 +150,51 @@ def test_gptq_llama_slice_against_oracle():
     print(f"GPTQ 512x1024: relative Frobenius vs oracle {rel:.2e}, differing elements {flipped:.4f}")
     # bar of the task is 1e-3; the reference's own backends differ by 3.5e-3 on this problem size
     assert rel < 5e-3
+
+
+def test_trailing_update_on_tensor_cores_agrees_with_fp32_kernel():
+    """The bf16x3 tensor-core trailing update against the fp32 CUDA-core one on the same problem: the tensor-level
+    weight after the FIRST block (one trailing update, no error feedback through it yet) agrees to fp32
+    rounding, and the complete sweep differs only by the flips GPTQ makes out of last-bit differences."""
+    from nncf_b200 import _lib
+    from nncf_b200.gptq import GPTQ
+
+    gen = torch.Generator().manual_seed(5)
+    rows, C = 520, 1024      # rows % 128 != 0: partial M tile; four N tiles with a ragged last one after block 0
+    w = (torch.randn(rows, C, generator=gen) * 0.02).cuda()
+    x = torch.randn(4096, C, generator=gen)
+    x[:, :16] *= 8.0
+    H = ((2.0 / 8) * (x.double().T @ x.double()).float()).cuda()
+    hinv = GPTQ(0.01).prepare_hessian_inverse(H.clone(), w.clone())
+
+    def run(ws_bytes, cols):
+        wt = w.clone()[:, :cols].contiguous()
+        hv = hinv[:cols, :cols].contiguous()
+        q = torch.empty_like(wt)
+        sc = torch.empty(rows, cols // 128, device="cuda")
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        _lib.check(_lib.lib.nncfb_gptq_quantize(_lib.ptr(wt), rows, cols, _lib.ptr(hv), _lib.MODE_IDS["int4_sym"], 128, 128,
+                                                _lib.ptr(q), _lib.ptr(sc), None, _lib.ptr(ws), ws_bytes, None))
+        _lib.check(_lib.lib.nncfb_hessian_status(None))
+        return wt, q, sc
+
+    small = int(_lib.lib.nncfb_gptq_workspace_bytes(rows))
+    big = int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, C))
+    assert big > small
+    # two blocks only: the second block's input is the first block's trailing update, its output is not fed back
+    w_simt, q_simt, _ = run(small, 256)
+    w_tc, q_tc, _ = run(int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, 256)), 256)
+    assert torch.equal(q_simt[:, :128], q_tc[:, :128])
+    upd = (w[:, 128:256] - w_simt[:, 128:256]).abs().max().item()
+    diff = (w_simt[:, 128:256] - w_tc[:, 128:256]).abs().max().item()
+    print(f"trailing update: max |update| {upd:.3e}, tensor cores vs fp32 kernel max diff {diff:.3e}")
+    assert upd > 0 and diff <= 2e-6 * max(upd, 1e-3)
+    # whole sweep
+    _, q1, s1 = run(small, C)
+    _, q2, s2 = run(big, C)
+    flipped = ((q1 - q2).abs() > 1e-6).float().mean().item()   # a last-bit change of a scale is not a flip
+    rel = ((q1 - q2).norm() / q1.norm()).item()
+    print(f"whole sweep: tensor cores vs fp32 kernel differing elements {flipped:.5f}, relative Frobenius {rel:.2e}")
+    assert flipped < 5e-3
+    # a flipped code moves the later groups of its row; everything else agrees to the last bits
+    assert ((s1 - s2).abs() > 2e-3 * s1.abs()).float().mean().item() < 1e-2
