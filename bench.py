@@ -569,11 +569,11 @@ def main():
         "int8_kernel": {"kernel": "quant_channel_batch_kernel<bf16, INT8_ASYM, 64 threads/row>", "ms_per_step": round(ms8, 4)},
     }
     # DRAM traffic of the INT4 launch: dram__bytes_read + dram__bytes_write of one ncu capture of the same
-    # kernel on one decoder layer (profiles/quant_rows_batch_kernel_int4sym_g128_bf16_one_layer.md: 514.2 MB for
-    # 218.1 M elements = 2.358 B/element), scaled to this launch by its element count (traffic is proportional
+    # kernel on one decoder layer (profiles/quant_rows_batch_kernel_int4sym_g128_bf16_one_layer.md: 515.7 MB for
+    # 218.1 M elements = 2.364 B/element), scaled to this launch by its element count (traffic is proportional
     # to the elements processed: every weight is read once and every code written once)
     if not args.profile_case:
-        roofline["traffic"] = int(2.358 * alg4 / 2.53125)
+        roofline["traffic"] = int(2.364 * alg4 / 2.53125)
         roofline["traffic_source"] = "ncu capture of one decoder layer, scaled by elements"
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,

@@ -196,6 +196,18 @@ int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* 
                         size_t workspace_bytes, void* stream);
 
 /*
+ * nncfb_gptq_quantize with ScaleEstimation at every group start (GPTQ(scale_estimation=True), WC/gptq.py:319-327):
+ * the scale / zero point of a 4-bit integer group come from the candidate search of nncfb_scale_estimation, run on
+ * the tensor-level weight of that group as it stands when its block begins.  importance [cols] and x [cols, n_samples]
+ * are the layer's statistics after process_stats (WC/activation_stats.py:20-57), as for nncfb_scale_estimation;
+ * group_size <= 512.  Other modes ignore the statistics (the reference refines 4-bit integer groups only).
+ */
+int nncfb_gptq_quantize_se(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode, int64_t group_size,
+                           int32_t block_size, const float* importance, const float* x, int32_t n_samples,
+                           int32_t initial_steps, int32_t scale_steps, float weight_penalty, float* q_out,
+                           float* scale_out, int32_t* zp_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * nncfb_gptq_quantize for callers that cannot provide scratch memory.  It has no counterpart in the
  * reference.  Who needs it: a program that embeds the library but cannot allocate device memory itself -
  * its runtime handed all of HBM to a private arena at start-up and exposes no allocation hook, or it runs

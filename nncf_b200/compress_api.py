@@ -456,17 +456,21 @@ def compress_weights(
 
     # GPTQ (gptq.py:82-171) or ScaleEstimation (scale_estimation.py:97-158)
     if cfg["gptq"]:
-        g = GPTQ(adv.gptq_params.damp_percent, adv.gptq_params.block_size, adv.gptq_params.subset_size)
+        # with scale_estimation the reference gives the flag to GPTQ instead of running ScaleEstimation separately
+        # (WC/algorithm.py: the GPTQ branch excludes the ScaleEstimation branch)
+        g = GPTQ(adv.gptq_params.damp_percent, adv.gptq_params.block_size, adv.gptq_params.subset_size,
+                 scale_estimation=cfg["scale_estimation"])
         targets = [p for p in active if not p.is_embedding and p.compression_config.mode not in INT8_MODES]
         # layers fed by the very same tensor (q/k/v, gate/up) share one Hessian and one factorisation
         for group in _same_input_groups(model, sample, targets):
-            H = _layer_hessian(model, group[0].module, items[: adv.gptq_params.subset_size], g)
+            H, layer_stat = _layer_hessian(model, group[0].module, items[: adv.gptq_params.subset_size], g,
+                                           want_statistics=cfg["scale_estimation"])
             hinv = None
             for p in group:
                 w = p.weight.data.float().contiguous()
                 if hinv is None:
                     hinv = g.prepare_hessian_inverse(H, w)
-                q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv)
+                q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat)
                 precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
                 p._gptq_weight = q
             for p in group:  # weights are replaced only after the whole group saw the same inputs
@@ -513,12 +517,15 @@ def _same_input_groups(model: nn.Module, sample: Any, targets: list) -> list:
     return groups
 
 
-def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ) -> torch.Tensor:
+def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ, want_statistics: bool = False):
     """Hessian of one Linear's input over the calibration items, with every previously processed layer already
     holding its quantised weight (the semantics of the reference's layer-wise engine,
     src/nncf/quantization/algorithms/layerwise/openvino_iterator.py:183-231).  Activations are consumed as
-    they appear; nothing is stored."""
+    they appear; nothing is stored but, when the sweep refines its scales with ScaleEstimation, the per-sample
+    channel means and shapes (what GPTQ.activations_to_wc_statistics would reduce from stored inputs).
+    Returns (H, statistics or None)."""
     C = module.in_features
+    stat = WCTensorStatistic() if want_statistics else None
     H = torch.zeros(C, C, dtype=torch.float32, device=module.weight.device)
     state = {"n": 0}
 
@@ -529,6 +536,10 @@ def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ) ->
         x = args[0]
         batch = x.shape[0] if x.ndim == 3 else 1
         state["n"] = g.accumulate_hessian(H, x, state["n"], batch)
+        if stat is not None:
+            one = g.activations_to_wc_statistics([x])
+            stat.mean_values.append(one.mean_values[0])
+            stat.shape_values.append(one.shape_values[0])
         raise _Stop
 
     h = module.register_forward_pre_hook(hook)
@@ -541,7 +552,7 @@ def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ) ->
                     pass
     finally:
         h.remove()
-    return H
+    return H, stat
 
 
 def _make_decompressor(p: WeightCompressionParameters, item) -> nn.Module:

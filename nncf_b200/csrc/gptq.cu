@@ -37,6 +37,7 @@ struct GptqArgs {
   int64_t rows, cols;
   int64_t gs, G;
   int i1, count;       // current block: columns [i1, i1 + count)
+  int given;           // 1: scale / zp of the groups starting in this block are already in the tables
 };
 
 // A warp owns 32 output rows (a thread owns a row); kSweepWarps warps share one copy of the block of Hinv.
@@ -125,22 +126,27 @@ __global__ void __launch_bounds__(kSweepWarps * kSweepRows) gptq_sweep_kernel(co
       const int64_t end = min(col + a.gs, a.cols);
       const int64_t in_block_end = min(end, static_cast<int64_t>(i1 + count));
       float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
-      for (int64_t kk = col; kk < in_block_end; ++kk) {
+      for (int64_t kk = col; kk < in_block_end && !a.given; ++kk) {
         const float v = ws[(kk - i1) * kSweepLd + t];
         mn = fminf(mn, v);
         mx = fmaxf(mx, v);
       }
       const float* wr = a.w + row * a.cols;
-      for (int64_t kk = in_block_end; kk < end; ++kk) {
+      for (int64_t kk = in_block_end; kk < end && !a.given; ++kk) {
         const float v = wr[kk];
         mn = fminf(mn, v);
         mx = fmaxf(mx, v);
       }
       Codec<MODE> cg;
-      cg.from_stats(mn, mx);
       const int64_t g = col / a.gs;
-      a.scale[row * a.G + g] = cg.scale;
-      if (a.zp) a.zp[row * a.G + g] = static_cast<int32_t>(cg.zp);
+      if (a.given) {
+        // refined by ScaleEstimation for this block (WC/gptq.py:319-327)
+        cg.from_given(a.scale[row * a.G + g], a.zp ? static_cast<float>(a.zp[row * a.G + g]) : 0.0f);
+      } else {
+        cg.from_stats(mn, mx);
+        a.scale[row * a.G + g] = cg.scale;
+        if (a.zp) a.zp[row * a.G + g] = static_cast<int32_t>(cg.zp);
+      }
       if (gl < kSweepMaxGroups) {
         ps[gl * kSweepRows + t] = cg.scale;
         pz[gl * kSweepRows + t] = cg.zp;
@@ -304,8 +310,21 @@ struct GptqTcScratch {
   int64_t slab_ld = 0;
 };
 
+// ScaleEstimation inside the sweep (WC/gptq.py:319-327): statistics after process_stats
+struct GptqSe {
+  const float* importance = nullptr;  // [cols] s = max |X| over samples; null: plain min/max parameters
+  const float* x = nullptr;           // [cols, n]
+  int n = 0, initial_steps = 0, scale_steps = 0;
+  float weight_penalty = -1.0f;
+};
+
+int scale_estimation_launch(const void* weight, int32_t weight_dtype, int64_t rows, int64_t cols, int64_t ld,
+                            int64_t group_size, int32_t mode, const float* importance, const float* x, int32_t n_samples,
+                            int32_t initial_steps, int32_t scale_steps, float weight_penalty, float* scale_out,
+                            int32_t* zp_out, int64_t out_ld, cudaStream_t st);
+
 template <int MODE>
-int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, cudaStream_t st) {
+int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, const GptqSe& se, cudaStream_t st) {
   const size_t smem = SweepSmem::bytes;
   NNCFB_CUDA(cudaFuncSetAttribute(gptq_sweep_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
@@ -318,6 +337,22 @@ int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, cudaStream_t st) {
   for (int64_t i1 = 0; i1 < a.cols; i1 += block) {
     a.i1 = static_cast<int>(i1);
     a.count = static_cast<int>(std::min<int64_t>(block, a.cols - i1));
+    a.given = 0;
+    if (se.importance != nullptr) {
+      // The groups that start inside this block are refined now: the tensor-level weight they are computed
+      // from has received every earlier block's trailing update and is not touched again before the sweep.
+      // One call per block covers them all (groups are independent in ScaleEstimation).
+      const int64_t first = ((i1 + a.gs - 1) / a.gs) * a.gs;
+      if (first < i1 + a.count) {
+        const int64_t n_groups = (i1 + a.count - 1 - first) / a.gs + 1;
+        const int rc = scale_estimation_launch(a.w + first, NNCFB_F32, a.rows, n_groups * a.gs, a.cols, a.gs, MODE,
+                                               se.importance + first, se.x + first * se.n, se.n, se.initial_steps,
+                                               se.scale_steps, se.weight_penalty, a.scale + first / a.gs,
+                                               a.zp ? a.zp + first / a.gs : nullptr, a.G, st);
+        if (rc != NNCFB_OK) return rc;
+      }
+      a.given = 1;
+    }
     gptq_sweep_kernel<MODE><<<row_blocks, kSweepWarps * kSweepRows, smem, st>>>(a);
     const int64_t c0 = i1 + a.count;
     if (c0 < a.cols) {
@@ -418,9 +453,10 @@ extern "C" size_t nncfb_gptq_workspace_bytes_tensor_cores(int64_t rows, int64_t 
   return err_bytes(rows) + planes_bytes(rows) + planes_bytes(cols);
 }
 
-extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
-                                   int64_t group_size, int32_t block_size, float* q_out, float* scale_out,
-                                   int32_t* zp_out, void* workspace, size_t workspace_bytes, void* stream) {
+namespace nncfb {
+static int gptq_quantize_impl(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
+                              int64_t group_size, int32_t block_size, float* q_out, float* scale_out, int32_t* zp_out,
+                              void* workspace, size_t workspace_bytes, GptqSe se, void* stream) {
   NNCFB_CHECK_ARG(weight && hinv && q_out && scale_out && workspace, NNCFB_E_BAD_ARG, "nncfb_gptq_quantize: null pointer");
   NNCFB_CHECK_ARG(rows > 0 && cols > 0, NNCFB_E_BAD_ARG, "nncfb_gptq_quantize: bad shape");
   NNCFB_CHECK_ARG(group_size > 0 && cols % group_size == 0, NNCFB_E_GROUP_SIZE,
@@ -459,20 +495,52 @@ extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, co
     tc.slab_planes = reinterpret_cast<__nv_bfloat16*>(base + err_bytes(rows) + planes_bytes(rows));
     tc.slab_ld = round8(cols);
   }
+  a.given = 0;
+  // the reference refines 4-bit integer groups only (WC/gptq.py:319); other modes keep min/max parameters
+  if (mode != NNCFB_INT4_SYM && mode != NNCFB_INT4_ASYM) se = GptqSe();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (mode) {
-    case NNCFB_INT4_SYM: return run_gptq<NNCFB_INT4_SYM>(a, block_size, tc, st);
-    case NNCFB_INT4_ASYM: return run_gptq<NNCFB_INT4_ASYM>(a, block_size, tc, st);
-    case NNCFB_INT8_SYM: return run_gptq<NNCFB_INT8_SYM>(a, block_size, tc, st);
-    case NNCFB_INT8_ASYM: return run_gptq<NNCFB_INT8_ASYM>(a, block_size, tc, st);
-    case NNCFB_NF4: return run_gptq<NNCFB_NF4>(a, block_size, tc, st);
-    case NNCFB_FP4: return run_gptq<NNCFB_FP4>(a, block_size, tc, st);
-    case NNCFB_MXFP4: return run_gptq<NNCFB_MXFP4>(a, block_size, tc, st);
+    case NNCFB_INT4_SYM: return run_gptq<NNCFB_INT4_SYM>(a, block_size, tc, se, st);
+    case NNCFB_INT4_ASYM: return run_gptq<NNCFB_INT4_ASYM>(a, block_size, tc, se, st);
+    case NNCFB_INT8_SYM: return run_gptq<NNCFB_INT8_SYM>(a, block_size, tc, se, st);
+    case NNCFB_INT8_ASYM: return run_gptq<NNCFB_INT8_ASYM>(a, block_size, tc, se, st);
+    case NNCFB_NF4: return run_gptq<NNCFB_NF4>(a, block_size, tc, se, st);
+    case NNCFB_FP4: return run_gptq<NNCFB_FP4>(a, block_size, tc, se, st);
+    case NNCFB_MXFP4: return run_gptq<NNCFB_MXFP4>(a, block_size, tc, se, st);
     default: break;
   }
   set_error("nncfb_gptq_quantize: mode %d is not supported", mode);
   return NNCFB_E_UNSUPPORTED;
 }
+}  // namespace nncfb
+
+extern "C" int nncfb_gptq_quantize(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
+                                   int64_t group_size, int32_t block_size, float* q_out, float* scale_out,
+                                   int32_t* zp_out, void* workspace, size_t workspace_bytes, void* stream) {
+  return gptq_quantize_impl(weight, rows, cols, hinv, mode, group_size, block_size, q_out, scale_out, zp_out, workspace,
+                            workspace_bytes, GptqSe(), stream);
+}
+
+extern "C" int nncfb_gptq_quantize_se(float* weight, int64_t rows, int64_t cols, const float* hinv, int32_t mode,
+                                      int64_t group_size, int32_t block_size, const float* importance, const float* x,
+                                      int32_t n_samples, int32_t initial_steps, int32_t scale_steps, float weight_penalty,
+                                      float* q_out, float* scale_out, int32_t* zp_out, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  NNCFB_CHECK_ARG(importance && x && n_samples > 0, NNCFB_E_BAD_ARG, "nncfb_gptq_quantize_se: statistics are missing");
+  NNCFB_CHECK_ARG(group_size <= 512, NNCFB_E_TOO_LARGE,
+                  "nncfb_gptq_quantize_se: group size %lld exceeds the supported maximum of 512 of scale estimation",
+                  (long long)group_size);
+  GptqSe se;
+  se.importance = importance;
+  se.x = x;
+  se.n = n_samples;
+  se.initial_steps = initial_steps;
+  se.scale_steps = scale_steps;
+  se.weight_penalty = weight_penalty;
+  return gptq_quantize_impl(weight, rows, cols, hinv, mode, group_size, block_size, q_out, scale_out, zp_out, workspace,
+                            workspace_bytes, se, stream);
+}
+
 
 // ---- GPTQ sweep for callers that cannot hand over scratch memory -----------------------------------
 // Some programs that embed this library have no device allocator to offer: a runtime that gave every

@@ -26,6 +26,8 @@ struct SEArgs {
   float* scale_out;     // [rows, G]
   int32_t* zp_out;      // [rows, G] (asym) or null
   int64_t rows, cols;
+  int64_t ld;           // elements between weight rows (cols for a contiguous weight; larger for a column slice)
+  int64_t out_ld;       // groups per row of scale_out / zp_out (cols / gs unless writing into a wider table)
   int gs, n, np;        // group size, samples, samples padded to a multiple of 64
   int initial_steps, scale_steps;
   float weight_penalty;
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(256) scale_estimation_kernel(const SEArgs a) {
   for (int rr = 0; rr < kSeRowsPerWarp; ++rr) {
     const int64_t row = row0 + rr;
     if (row >= a.rows) break;  // warp-uniform
-    const SrcT* wrow = wsrc + row * a.cols + g * gs;
+    const SrcT* wrow = wsrc + row * a.ld + g * gs;
     float w[EPL], imp[EPL], tgt[EPL], zm[EPL];
     bool have[EPL];
     float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
@@ -223,8 +225,8 @@ __global__ void __launch_bounds__(256) scale_estimation_kernel(const SEArgs a) {
       }
     }
     if (lane == 0) {
-      a.scale_out[row * G + g] = result;
-      if (a.zp_out) a.zp_out[row * G + g] = static_cast<int32_t>(zp);
+      a.scale_out[row * a.out_ld + g] = result;
+      if (a.zp_out) a.zp_out[row * a.out_ld + g] = static_cast<int32_t>(zp);
     }
   }
 }
@@ -267,14 +269,15 @@ int launch_se_t(const SEArgs& a, int mode, cudaStream_t st) {
   return NNCFB_E_UNSUPPORTED;
 }
 
-}  // namespace nncfb
 
-using namespace nncfb;
 
-extern "C" int nncfb_scale_estimation(const void* weight, int32_t weight_dtype, int64_t rows, int64_t cols,
-                                      int64_t group_size, int32_t mode, const float* importance, const float* x,
-                                      int32_t n_samples, int32_t initial_steps, int32_t scale_steps,
-                                      float weight_penalty, float* scale_out, int32_t* zp_out, void* stream) {
+// Shared by the C entry point and the GPTQ sweep (which refines the groups of one column block at a time:
+// `weight` then points into a wider matrix with `ld` elements between rows, and the results go into the
+// full [rows, out_ld] tables at the block's first group).
+int scale_estimation_launch(const void* weight, int32_t weight_dtype, int64_t rows, int64_t cols, int64_t ld,
+                            int64_t group_size, int32_t mode, const float* importance, const float* x, int32_t n_samples,
+                            int32_t initial_steps, int32_t scale_steps, float weight_penalty, float* scale_out,
+                            int32_t* zp_out, int64_t out_ld, cudaStream_t st) {
   NNCFB_CHECK_ARG(weight && importance && x && scale_out, NNCFB_E_BAD_ARG, "nncfb_scale_estimation: null pointer");
   NNCFB_CHECK_ARG(rows > 0 && cols > 0 && n_samples > 0, NNCFB_E_BAD_ARG, "nncfb_scale_estimation: bad shape");
   NNCFB_CHECK_ARG(group_size > 0 && cols % group_size == 0, NNCFB_E_GROUP_SIZE,
@@ -300,13 +303,14 @@ extern "C" int nncfb_scale_estimation(const void* weight, int32_t weight_dtype, 
   a.zp_out = mode_is_asym(mode) ? zp_out : nullptr;
   a.rows = rows;
   a.cols = cols;
+  a.ld = ld;
+  a.out_ld = out_ld;
   a.gs = static_cast<int>(group_size);
   a.n = n_samples;
   a.np = np;
   a.initial_steps = initial_steps;
   a.scale_steps = scale_steps;
   a.weight_penalty = weight_penalty;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (weight_dtype) {
     case NNCFB_F32: return launch_se_t<float>(a, mode, st);
     case NNCFB_F16: return launch_se_t<__half>(a, mode, st);
@@ -315,4 +319,15 @@ extern "C" int nncfb_scale_estimation(const void* weight, int32_t weight_dtype, 
   }
   set_error("nncfb_scale_estimation: unsupported weight dtype %d", weight_dtype);
   return NNCFB_E_BAD_ARG;
+}
+
+}  // namespace nncfb
+
+extern "C" int nncfb_scale_estimation(const void* weight, int32_t weight_dtype, int64_t rows, int64_t cols,
+                                      int64_t group_size, int32_t mode, const float* importance, const float* x,
+                                      int32_t n_samples, int32_t initial_steps, int32_t scale_steps,
+                                      float weight_penalty, float* scale_out, int32_t* zp_out, void* stream) {
+  return nncfb::scale_estimation_launch(weight, weight_dtype, rows, cols, cols, group_size, mode, importance, x, n_samples,
+                                        initial_steps, scale_steps, weight_penalty, scale_out, zp_out,
+                                        group_size > 0 ? cols / group_size : 0, static_cast<cudaStream_t>(stream));
 }

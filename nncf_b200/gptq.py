@@ -12,7 +12,8 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from .config import WeightCompressionConfig
+from .activation_stats import channel_stats, process_stats
+from .config import WCTensorStatistic, WeightCompressionConfig
 from .parameters import CompressWeightsMode
 
 
@@ -22,9 +23,7 @@ class GPTQ:
         self._damp_percent = damp_percent
         self._block_size = block_size
         self._subset_size = subset_size
-        if scale_estimation:
-            msg = "scale estimation inside GPTQ is not supported"
-            raise NotImplementedError(msg)
+        self._scale_estimation = scale_estimation
         self._tensor_cores = tensor_cores
         if inverse_factor not in ("reversed", "reference"):
             msg = f"inverse_factor must be 'reversed' or 'reference', got {inverse_factor!r}"
@@ -103,13 +102,26 @@ class GPTQ:
         U._dead_columns = dead if bool(dead.any()) else None  # reused when several weights share this factor
         return U
 
+    @staticmethod
+    def activations_to_wc_statistics(activations: Sequence[torch.Tensor]) -> WCTensorStatistic:
+        """gptq.py:382-396: per input, the mean over every axis but the last (in the input's dtype) and its shape."""
+        stat = WCTensorStatistic()
+        for act in activations:
+            stat.shape_values.append(tuple(act.shape))
+            stat.mean_values.append(channel_stats(act, -1, ("mean",))["mean"])
+        return stat
+
     def _quantize_weights(self, wc_params, hessian: torch.Tensor, weight_tensor: torch.Tensor,
-                          inputs: Optional[Sequence[torch.Tensor]] = None, hinv: Optional[torch.Tensor] = None):
+                          inputs: Optional[Sequence[torch.Tensor]] = None, hinv: Optional[torch.Tensor] = None,
+                          statistics: Optional[WCTensorStatistic] = None):
         """gptq.py:244-379.  ``weight_tensor`` [out, C] fp32 is modified in place (trailing updates) like the
         reference's; returns (dequantised weight [out, C] fp32, scales [out, G, 1], zero points or None).
         ``hinv``: the factor returned by ``prepare_hessian_inverse`` for this Hessian, when several weights
         share one input (q/k/v, gate/up) and the factorisation was already done; dead columns of the weight
-        are then zeroed from ``hessian``'s diagonal as usual."""
+        are then zeroed from ``hessian``'s diagonal as usual.  With ``scale_estimation=True`` (4-bit integer
+        modes) every group's parameters come from ScaleEstimation on the group's current weight, as in
+        gptq.py:319-327; the layer statistics are taken from ``statistics`` (per-sample means and shapes, for
+        callers that do not keep the activations) or reduced from ``inputs``."""
         config: WeightCompressionConfig = wc_params.compression_config
         assert hessian.ndim == 2, "Hessian should be 2D"
         if weight_tensor.dtype != torch.float32 or not weight_tensor.is_contiguous():
@@ -130,11 +142,29 @@ class GPTQ:
         ws_bytes = int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, cols) if self._tensor_cores
                        else _lib.lib.nncfb_gptq_workspace_bytes(rows))
         workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        use_se = self._scale_estimation and config.is_integer and config.num_bits == 4
         with torch.cuda.device(dev):
-            _lib.check(_lib.lib.nncfb_gptq_quantize(
-                _lib.ptr(weight_tensor), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[config.mode.value], gs,
-                self._block_size, _lib.ptr(q), _lib.ptr(scale), _lib.ptr(zp), _lib.ptr(workspace), ws_bytes,
-                _lib.stream_handle(dev)))
+            if use_se:
+                if statistics is None:
+                    if not inputs:
+                        msg = "GPTQ with scale estimation needs the layer's inputs or their statistics"
+                        raise ValueError(msg)
+                    statistics = self.activations_to_wc_statistics(inputs)
+                # the reference calls ScaleEstimation.calculate_quantization_params with its defaults
+                # (subset 32, 5 + 10 steps, no weight penalty) on each group's slice of the statistics;
+                # slicing commutes with process_stats, so it is done once for the whole layer
+                s, X = process_stats(statistics, 32)
+                s = s.to(device=dev, dtype=torch.float32).contiguous()
+                X = X.to(device=dev, dtype=torch.float32).contiguous()
+                _lib.check(_lib.lib.nncfb_gptq_quantize_se(
+                    _lib.ptr(weight_tensor), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[config.mode.value], gs,
+                    self._block_size, _lib.ptr(s), _lib.ptr(X), X.shape[-1], 5, 10, -1.0, _lib.ptr(q), _lib.ptr(scale),
+                    _lib.ptr(zp), _lib.ptr(workspace), ws_bytes, _lib.stream_handle(dev)))
+            else:
+                _lib.check(_lib.lib.nncfb_gptq_quantize(
+                    _lib.ptr(weight_tensor), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[config.mode.value], gs,
+                    self._block_size, _lib.ptr(q), _lib.ptr(scale), _lib.ptr(zp), _lib.ptr(workspace), ws_bytes,
+                    _lib.stream_handle(dev)))
             if self._tensor_cores:
                 _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(dev)))  # bounded waits of the TC kernels
         scales = scale.reshape(rows, G, 1)

@@ -691,8 +691,15 @@ def gptq_hinv(H: np.ndarray, weight: np.ndarray, damp_percent: float):
     return U.astype(F32)
 
 
-def gptq_quantize(weight: np.ndarray, hinv: np.ndarray, mode: str, group_size: int, block_size: int = 128):
+def gptq_quantize(weight: np.ndarray, hinv: np.ndarray, mode: str, group_size: int, block_size: int = 128,
+                  se_stats=None):
     """Blocked column sweep with error feedback.  WC/gptq.py:297-379.
+
+    ``se_stats`` = (s [C], X [C, n]) after ``process_stats``: GPTQ(scale_estimation=True), i.e. 4-bit integer
+    groups take their parameters from ``scale_estimation`` on the group's slice of the statistics and of the
+    tensor-level weight (WC/gptq.py:319-327; the reference slices the raw activations, reduces them with
+    ``activations_to_wc_statistics`` :382-396 and lets calculate_quantization_params run process_stats with
+    its default subset of 32, which commutes with the slicing).
 
     ``weight`` [out, C] fp32 (mutated), ``hinv`` upper factor [C, C].  Scales are taken at
     each group start from the *tensor-level* weight (updated at block ends only), exactly as
@@ -713,7 +720,11 @@ def gptq_quantize(weight: np.ndarray, hinv: np.ndarray, mode: str, group_size: i
             d = Hb[i, i]
             if (i1 + i) % gs == 0:
                 grp = weight[:, i1 + i:i1 + i + gs]
-                if is_integer(mode):
+                if is_integer(mode) and se_stats is not None and num_bits(mode) == 4:
+                    c0 = i1 + i
+                    sc, zp = scale_estimation(se_stats[0][c0:c0 + gs], se_stats[1][c0:c0 + gs], grp, 1, mode, -1)
+                    zps.append(zp)
+                elif is_integer(mode):
                     sc, zp = integer_params(grp, 1, mode)
                     zps.append(zp)
                 else:

@@ -59,3 +59,11 @@ GPTQ_CASES = [
     ("int4_sym_row", 12, 64, -1, 32, "int4_sym", 0.1, 4, 64, "f32"),
     ("int4_sym_g128", 32, 256, 128, 128, "int4_sym", 0.01, 4, 160, "bf16"),
 ]
+
+# GPTQ(scale_estimation=True): same fields as GPTQ_CASES
+GPTQ_SE_CASES = [
+    ("se_int4_sym_g32_b64", 24, 128, 32, 64, "int4_sym", 0.01, 6, 96, "f32"),
+    ("se_int4_asym_g32_b32", 16, 128, 32, 32, "int4_asym", 0.01, 6, 96, "f32"),
+    ("se_int4_asym_g64_b128", 24, 256, 64, 128, "int4_asym", 0.05, 5, 64, "f32"),
+    ("se_int4_sym_g128", 32, 256, 128, 128, "int4_sym", 0.01, 4, 160, "bf16"),
+]

@@ -21,7 +21,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
-from cases import AWQ_CASES, DTYPES, GPTQ_CASES, MODES, QUANT_CASES, SE_CASES  # noqa: E402
+from cases import AWQ_CASES, DTYPES, GPTQ_CASES, GPTQ_SE_CASES, MODES, QUANT_CASES, SE_CASES  # noqa: E402
 
 
 def _setup(ref_src: str):
@@ -320,7 +320,12 @@ def gen_awq(out: dict):
 
 
 
-def gen_gptq(out: dict):
+def gen_gptq_se(out: dict):
+    """GPTQ with scale_estimation=True (the reference's _quantize_weights slices the inputs per group)."""
+    gen_gptq(out, cases=GPTQ_SE_CASES, prefix="gptq_se", scale_estimation=True)
+
+
+def gen_gptq(out: dict, cases=None, prefix="gptq", scale_estimation=False):
     import torch
 
     from nncf.parameters import CompressWeightsMode
@@ -338,7 +343,7 @@ def gen_gptq(out: dict):
     )
     rng = np.random.default_rng(0)
     names = []
-    for name, o, C, gs, block, mode, damp, n_in, tokens, xdt in GPTQ_CASES:
+    for name, o, C, gs, block, mode, damp, n_in, tokens, xdt in (cases if cases is not None else GPTQ_CASES):
         w = rng.normal(0, 0.05, size=(o, C)).astype(np.float32)
         base = rng.normal(0, 1.0, size=(C, C)) / np.sqrt(C)
         xs = []
@@ -348,7 +353,7 @@ def gen_gptq(out: dict):
         if name == "int4_sym_g32_b32":
             for x in xs:
                 x[..., 5] = 0.0  # dead column
-        g = GPTQ(damp_percent=damp, block_size=block, subset_size=n_in)
+        g = GPTQ(damp_percent=damp, block_size=block, subset_size=n_in, scale_estimation=scale_estimation)
         g._backend_entity = be
         inputs = [Tensor(_torch_weight(x, xdt)) for x in xs]
         H = g._calculate_hessian(node, inputs)
@@ -356,7 +361,7 @@ def gen_gptq(out: dict):
         wp = SimpleNamespace(node_with_weight=node, weight_port_id=1, compression_config=cfg, reduction_axes=(1,))
         Hc = Tensor(H.data[0].clone())
         q, s, z = g._quantize_weights(wp, Hc, Tensor(torch.from_numpy(w.copy())), inputs)
-        key = f"gptq/{name}"
+        key = f"{prefix}/{name}"
         names.append(key)
         out[key + "/w"] = w
         out[key + "/x"] = np.stack(xs)
@@ -369,7 +374,7 @@ def gen_gptq(out: dict):
         out[key + "/meta"] = np.array([gs, block], dtype=np.int64)
         out[key + "/damp"] = np.float64(damp)
         out[key + "/mode"] = np.array(mode)
-    out["gptq/index"] = np.array(names)
+    out[f"{prefix}/index"] = np.array(names)
 
 
 def main():
@@ -385,6 +390,7 @@ def main():
         "scale_estimation": gen_scale_estimation,
         "awq": gen_awq,
         "gptq": gen_gptq,
+        "gptq_se": gen_gptq_se,
         "api": gen_api,
     }
     only = [a for a in sys.argv[1:] if a in groups]

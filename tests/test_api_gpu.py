@@ -132,6 +132,29 @@ def test_gptq_model_level_reduces_output_error():
     assert errs[True] < errs[False] * 1.05, errs
 
 
+def test_gptq_with_scale_estimation_model_level():
+    """gptq=True together with scale_estimation=True hands the flag to GPTQ (every group's parameters come from
+    ScaleEstimation inside the sweep): it runs through the model API, changes the stored scales and keeps the
+    output error at the level of plain GPTQ."""
+    import nncf_b200 as nb
+
+    ids = [i.cuda() for i in calibration_ids(n=8, seq=32)]
+    with torch.no_grad():
+        base = torch.cat([TinyGatedLM().cuda()(i) for i in ids])
+    errs, scales = {}, {}
+    for se in (False, True):
+        model = nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode.INT4_ASYM, group_size=16,
+                                    dataset=nb.Dataset(ids), gptq=True, scale_estimation=se or None,
+                                    advanced_parameters=nb.AdvancedCompressionParameters(
+                                        gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.1, subset_size=8)))
+        with torch.no_grad():
+            out = torch.cat([model(i) for i in ids])
+        errs[se] = float((out - base).norm() / base.norm())
+        scales[se] = torch.cat([v.flatten().float() for k, v in model.state_dict().items() if k.endswith("_scale")])
+    assert (scales[True] != scales[False]).float().mean().item() > 0.3
+    assert errs[True] < errs[False] * 1.5, errs
+
+
 @pytest.mark.parametrize("mode,gs", [("int4_sym", 128), ("int4_asym", 64), ("int8_asym", -1), ("int8_sym", -1),
                                      ("nf4", 128), ("mxfp4", 32), ("fp8_e4m3", 128), ("mxfp8_e4m3", 32)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])

@@ -10,7 +10,7 @@ enough for that norm to be meaningful."""
 import numpy as np
 import pytest
 import torch
-from cases import GPTQ_CASES
+from cases import GPTQ_CASES, GPTQ_SE_CASES
 from conftest import golden
 
 pytestmark = pytest.mark.gpu
@@ -198,3 +198,31 @@ def test_trailing_update_on_tensor_cores_agrees_with_fp32_kernel():
     assert flipped < 5e-3
     # a flipped code moves the later groups of its row; everything else agrees to the last bits
     assert ((s1 - s2).abs() > 2e-3 * s1.abs()).float().mean().item() < 1e-2
+
+
+@pytest.mark.parametrize("case", GPTQ_SE_CASES, ids=[c[0] for c in GPTQ_SE_CASES])
+def test_gptq_with_scale_estimation_matches_reference_golden(case):
+    """GPTQ(scale_estimation=True): parameters of every 4-bit group from ScaleEstimation inside the sweep
+    (WC/gptq.py:319-327), against the reference run on the same inputs."""
+    from nncf_b200.gptq import GPTQ
+
+    name, o, C, gs, block, mode, damp, n_in, tokens, xdt = case
+    g = golden("gptq_se")
+    key = f"gptq_se/{name}"
+    H = torch.from_numpy(g[key + "/H"].copy()).cuda()
+    w = torch.from_numpy(g[key + "/w"].copy()).cuda()
+    inputs = [torch.from_numpy(x.copy()).to(TD[xdt]).cuda() for x in g[key + "/x"]]
+    q, s, z = GPTQ(damp, block, n_in, scale_estimation=True)._quantize_weights(_wp(mode, gs), H, w, inputs)
+    qref, sref = g[key + "/q"], g[key + "/scale"]
+    assert tuple(q.shape) == qref.shape and tuple(s.shape) == sref.shape
+    flipped = np.mean(np.abs(q.cpu().numpy() - qref) > 1e-6)
+    bad_scales = np.mean(np.abs(s.cpu().numpy() - sref) > 2e-3 * np.abs(sref))
+    print(f"{name}: differing elements {flipped:.4f}, scales off by more than 2e-3: {bad_scales:.4f}")
+    assert flipped < 0.03 and bad_scales < 0.03
+    if (key + "/zp") in g:
+        assert tuple(z.shape) == g[key + "/zp"].shape
+        assert np.mean(z.cpu().numpy() != g[key + "/zp"]) < 0.05
+    # without the flag the scales are the plain min/max ones: the fixture does exercise the refinement
+    q0, s0, _ = GPTQ(damp, block, n_in)._quantize_weights(
+        _wp(mode, gs), torch.from_numpy(g[key + "/H"].copy()).cuda(), torch.from_numpy(g[key + "/w"].copy()).cuda())
+    assert np.mean(np.abs(s0.cpu().numpy() - sref) > 2e-3 * np.abs(sref)) > 0.3

@@ -180,6 +180,45 @@ def test_gptq_matches_reference(key):
         assert Z.shape == g[key + "/zp"].shape
 
 
+def _gptq_se_stats(g, key):
+    """(s, X) of a GPTQ(scale_estimation=True) fixture: per-input channel means in the activation dtype
+    (WC/gptq.py:382-396), then process_stats with the default subset of 32."""
+    import torch
+
+    xs = list(g[key + "/x"])
+    means = []
+    for x in xs:
+        m = O.mean_reducer(x, -1)
+        if str(g[key + "/xdtype"]) == "bf16":
+            m = torch.from_numpy(m).to(torch.bfloat16).float().numpy()
+        means.append(m)
+    return O.process_stats(means, [x.shape for x in xs], 32)
+
+
+@pytest.mark.parametrize("key", golden("gptq_se").index("gptq_se"))
+def test_gptq_with_scale_estimation_matches_reference(key):
+    g = golden("gptq_se")
+    gs, block = (int(v) for v in g[key + "/meta"])
+    mode = str(g[key + "/mode"])
+    s, X = _gptq_se_stats(g, key)
+    w = g[key + "/w"].copy()
+    hinv = O.gptq_hinv(g[key + "/H"].copy(), w, float(g[key + "/damp"]))
+    Q, S, Z = O.gptq_quantize(w, hinv, mode, gs, block, se_stats=(s.astype(np.float32), X.astype(np.float32)))
+    qref, sref = g[key + "/q"], g[key + "/scale"]
+    assert S.shape == sref.shape
+    flipped = np.mean(np.abs(Q - qref) > 1e-6)
+    assert flipped < 0.02, flipped
+    # the refined scales differ from the min/max ones (otherwise this fixture would not test anything) ...
+    w0 = g[key + "/w"].reshape(w.shape[0], -1, gs)
+    plain = np.abs(w0).max(-1) / 8.0 if mode == "int4_sym" else (w0.max(-1) - w0.min(-1)) / 15.0
+    assert np.mean(np.abs(np.abs(sref[..., 0]) - plain) > 1e-3 * plain) > 0.3
+    # ... and the oracle reproduces them
+    assert np.mean(np.abs(S - sref) > 2e-3 * np.abs(sref)) < 0.03
+    if Z is not None:
+        assert Z.shape == g[key + "/zp"].shape
+        assert np.mean(Z != g[key + "/zp"]) < 0.05
+
+
 # ------------------------------------------------------------------------------------
 # Known-answer vectors of the reference's own tests (numbers only)
 # ------------------------------------------------------------------------------------
