@@ -119,6 +119,60 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Order of the upper-triangle tiles of the Hessian.  Tile (mi, nj) (128 rows x 256 columns) is needed when
+// nj >= mi / 2.  Tiles are numbered band by band, a band being kBandN tile columns wide, and inside a band
+// row by row: the ~148 tiles that are resident together then form a compact patch (about 18 tile rows x 8
+// tile columns) that touches ~4.4 K channels of X instead of all of them, so a wave re-reads a third of X
+// from HBM rather than the whole matrix (X is 0.9 GB per call at C = 14336, seven times the L2).
+constexpr int kBandN = 8;
+
+__host__ __device__ inline int band_tiles(int b, int tiles_m, int tiles_n) {
+  const int n_lo = b * kBandN, n_hi = min(n_lo + kBandN, tiles_n);
+  int total = 0;
+  const int full_rows = min(2 * n_lo, tiles_m);       // rows whose whole band segment is above the diagonal
+  const int width = n_hi - n_lo;
+  total += full_rows * width;
+  if (2 * n_hi <= tiles_m) {
+    total += width * (width + 1);  // rows 2 n_lo .. 2 n_hi - 1 hold width, width, width - 1, width - 1, ..., 1, 1 tiles
+  } else {
+    for (int mi = 2 * n_lo; mi < tiles_m; ++mi) total += n_hi - max(n_lo, mi / 2);
+  }
+  return total;
+}
+
+__host__ __device__ inline int hessian_tile_count(int tiles_m, int tiles_n) {
+  int total = 0;
+  for (int b = 0; b * kBandN < tiles_n; ++b) total += band_tiles(b, tiles_m, tiles_n);
+  return total;
+}
+
+__host__ __device__ inline void hessian_tile_decode(int idx, int tiles_m, int tiles_n, int& mi, int& nj) {
+  int b = 0;
+  for (;; ++b) {
+    const int t = band_tiles(b, tiles_m, tiles_n);
+    if (idx < t) break;
+    idx -= t;
+  }
+  const int n_lo = b * kBandN, n_hi = min(n_lo + kBandN, tiles_n);
+  const int width = n_hi - n_lo;
+  const int full_rows = min(2 * n_lo, tiles_m);
+  if (idx < full_rows * width) {
+    mi = idx / width;
+    nj = n_lo + idx - mi * width;
+    return;
+  }
+  idx -= full_rows * width;
+  for (mi = 2 * n_lo;; ++mi) {
+    const int lo = max(n_lo, mi / 2);
+    const int cnt = n_hi - lo;
+    if (idx < cnt) {
+      nj = lo + idx;
+      return;
+    }
+    idx -= cnt;
+  }
+}
+
 struct __align__(8) Control {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -147,15 +201,8 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
     mi = blockIdx.x / n_tiles_n;
     nj = blockIdx.x - mi * n_tiles_n;
   } else {
-    // tile -> (mi, nj) with nj >= mi / 2 (tiles that touch the upper triangle)
-    int rem = blockIdx.x;
-    for (;;) {
-      const int row_tiles = n_tiles_n - mi / 2;
-      if (rem < row_tiles) break;
-      rem -= row_tiles;
-      ++mi;
-    }
-    nj = mi / 2 + rem;
+    // tile -> (mi, nj) with nj >= mi / 2 (tiles that touch the upper triangle), banded order
+    hessian_tile_decode(blockIdx.x, static_cast<int>((m_bound + kTileM - 1) / kTileM), n_tiles_n, mi, nj);
   }
   const int m0 = mi * kTileM, n0 = nj * kTileN;
   const int k_iters = TRAILING ? 12 : static_cast<int>((tokens + kBlockK - 1) / kBlockK);
@@ -387,8 +434,7 @@ int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t
   if (rc != NNCFB_OK) return rc;
   const int tiles_m = static_cast<int>((C + kTileM - 1) / kTileM);
   const int tiles_n = static_cast<int>((C + kTileN - 1) / kTileN);
-  int n_tiles = 0;
-  for (int mi = 0; mi < tiles_m; ++mi) n_tiles += tiles_n - mi / 2;
+  const int n_tiles = hessian_tile_count(tiles_m, tiles_n);
   constexpr size_t smem = tc_smem_bytes<kStagesHessian>();
   auto kernel = tc_tn_kernel<kStagesHessian, false>;
   NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

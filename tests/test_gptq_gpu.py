@@ -226,3 +226,19 @@ def test_gptq_with_scale_estimation_matches_reference_golden(case):
     q0, s0, _ = GPTQ(damp, block, n_in)._quantize_weights(
         _wp(mode, gs), torch.from_numpy(g[key + "/H"].copy()).cuda(), torch.from_numpy(g[key + "/w"].copy()).cuda())
     assert np.mean(np.abs(s0.cpu().numpy() - sref) > 2e-3 * np.abs(sref)) > 0.3
+
+
+@pytest.mark.parametrize("C", [320, 2304, 2432])
+def test_tensor_core_hessian_tile_order_covers_the_triangle(C):
+    """Channel counts that are not multiples of the 256-column tile and span more than one band of tile columns:
+    every upper-triangle tile must be computed exactly once (a missed tile leaves zeros, a doubled one doubles)."""
+    from nncf_b200 import _lib
+    from nncf_b200.gptq import GPTQ
+
+    gen = torch.Generator().manual_seed(C)
+    x = torch.randn(192, C, generator=gen).to(torch.bfloat16).cuda()
+    H = GPTQ(tensor_cores=True)._calculate_hessian(None, [x])[0]
+    ref = (2.0 * (x.double().T @ x.double())).float()
+    tol = 4e-7 * float(ref.abs().max()) * (192 ** 0.5)
+    assert (H - ref).abs().max().item() <= tol
+    assert torch.equal(H, H.T)
