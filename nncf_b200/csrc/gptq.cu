@@ -301,14 +301,38 @@ __global__ void __launch_bounds__(256) gptq_trailing_kernel(const GptqArgs a, co
 // tensor-core trailing update and its helpers (hessian_tc.cu)
 bool gptq_trailing_tc_available();
 int tc_status_reset(cudaStream_t st);
-int gptq_trailing_tc(float* w_c0, int64_t ld, int64_t rows, int64_t n, const float* hinv, int64_t cols, int i1, int64_t c0,
-                     const __nv_bfloat16* err_planes, int64_t err_ld, __nv_bfloat16* slab_planes, int64_t slab_ld,
-                     cudaStream_t st);
+int gptq_split_slab(const float* hinv, int64_t cols, int i1, int64_t c0, int64_t n, __nv_bfloat16* slab_planes,
+                    int64_t slab_ld, cudaStream_t st);
+int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv_bfloat16* err_planes, int64_t err_ld,
+                     const __nv_bfloat16* slab_c, int64_t slab_ld, cudaStream_t st);
 
 struct GptqTcScratch {
-  __nv_bfloat16* slab_planes = nullptr;  // [3 * 128, slab_ld]
+  __nv_bfloat16* err_planes[2] = {nullptr, nullptr};   // [3 * 128, err_ld] each, alternating between blocks
+  __nv_bfloat16* slab_planes[2] = {nullptr, nullptr};  // [3 * 128, slab_ld] each
   int64_t slab_ld = 0;
 };
+
+// Side stream and events of the look-ahead schedule, one set per device, created on first use.
+struct Lookahead {
+  cudaStream_t side = nullptr;
+  cudaEvent_t panel_done = nullptr, rest_done = nullptr;
+};
+std::mutex g_lookahead_mutex;
+Lookahead g_lookahead[64];
+
+int lookahead_for_current_device(Lookahead** out) {
+  int dev = 0;
+  NNCFB_CUDA(cudaGetDevice(&dev));
+  NNCFB_CHECK_ARG(dev >= 0 && dev < 64, NNCFB_E_UNSUPPORTED, "nncfb_gptq_quantize: device ordinal %d >= 64", dev);
+  Lookahead& l = g_lookahead[dev];
+  if (l.side == nullptr) {
+    NNCFB_CUDA(cudaStreamCreateWithFlags(&l.side, cudaStreamNonBlocking));
+    NNCFB_CUDA(cudaEventCreateWithFlags(&l.panel_done, cudaEventDisableTiming));
+    NNCFB_CUDA(cudaEventCreateWithFlags(&l.rest_done, cudaEventDisableTiming));
+  }
+  *out = &l;
+  return NNCFB_OK;
+}
 
 // ScaleEstimation inside the sweep (WC/gptq.py:319-327): statistics after process_stats
 struct GptqSe {
@@ -323,21 +347,39 @@ int scale_estimation_launch(const void* weight, int32_t weight_dtype, int64_t ro
                             int32_t initial_steps, int32_t scale_steps, float weight_penalty, float* scale_out,
                             int32_t* zp_out, int64_t out_ld, cudaStream_t st);
 
+// Schedule with the tensor-core trailing update ("look-ahead"): the update of block b is split into the panel
+// that the next block needs (its 128 columns) and the rest.  The panel runs on the caller's stream right after
+// the sweep; the rest runs on a side stream, concurrently with the sweep of block b + 1, which is a latency
+// chain on a few SMs while the rest keeps the others busy.  Every element of W still receives the updates of
+// blocks 0, 1, 2, ... in that order (rest(b - 1) completes before panel(b) starts), so results do not depend on
+// the schedule.  Error planes and slab planes alternate between two buffers: block b + 1 writes one set while
+// rest(b) reads the other.
 template <int MODE>
 int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, const GptqSe& se, cudaStream_t st) {
   const size_t smem = SweepSmem::bytes;
   NNCFB_CUDA(cudaFuncSetAttribute(gptq_sweep_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
   const unsigned row_blocks = static_cast<unsigned>((a.rows + kSweepWarps * kSweepRows - 1) / (kSweepWarps * kSweepRows));
-  const bool use_tc = tc.slab_planes != nullptr;
+  const bool use_tc = tc.slab_planes[0] != nullptr;
+  Lookahead* la = nullptr;
+  std::unique_lock<std::mutex> lock(g_lookahead_mutex, std::defer_lock);
   if (use_tc) {
-    const int rc = tc_status_reset(st);
+    int rc = tc_status_reset(st);
+    if (rc != NNCFB_OK) return rc;
+    lock.lock();  // the side stream and its two events are shared by every call on this device
+    rc = lookahead_for_current_device(&la);
     if (rc != NNCFB_OK) return rc;
   }
-  for (int64_t i1 = 0; i1 < a.cols; i1 += block) {
+  // A group that reaches beyond its block makes the sweep read columns the previous block's rest update is
+  // still writing, so the two may only overlap when every group lies inside one block.
+  const bool overlap = use_tc && block % a.gs == 0;
+  bool rest_pending = false;
+  int64_t blk = 0;
+  for (int64_t i1 = 0; i1 < a.cols; i1 += block, ++blk) {
     a.i1 = static_cast<int>(i1);
     a.count = static_cast<int>(std::min<int64_t>(block, a.cols - i1));
     a.given = 0;
+    if (use_tc) a.err_planes = tc.err_planes[blk & 1];
     if (se.importance != nullptr) {
       // The groups that start inside this block are refined now: the tensor-level weight they are computed
       // from has received every earlier block's trailing update and is not touched again before the sweep.
@@ -355,17 +397,38 @@ int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, const GptqSe& se, c
     }
     gptq_sweep_kernel<MODE><<<row_blocks, kSweepWarps * kSweepRows, smem, st>>>(a);
     const int64_t c0 = i1 + a.count;
-    if (c0 < a.cols) {
-      if (use_tc) {
-        const int rc = gptq_trailing_tc(a.w + c0, a.cols, a.rows, a.cols - c0, a.hinv, a.cols, a.i1, c0, a.err_planes,
-                                        a.err_ld, tc.slab_planes, tc.slab_ld, st);
-        if (rc != NNCFB_OK) return rc;
-      } else {
-        const dim3 grid(static_cast<unsigned>((a.cols - c0 + 63) / 64), static_cast<unsigned>((a.rows + 63) / 64));
-        gptq_trailing_kernel<<<grid, 256, 0, st>>>(a, c0);
+    if (c0 >= a.cols) continue;
+    if (!use_tc) {
+      const dim3 grid(static_cast<unsigned>((a.cols - c0 + 63) / 64), static_cast<unsigned>((a.rows + 63) / 64));
+      gptq_trailing_kernel<<<grid, 256, 0, st>>>(a, c0);
+      continue;
+    }
+    __nv_bfloat16* slab = tc.slab_planes[blk & 1];
+    int rc = gptq_split_slab(a.hinv, a.cols, a.i1, c0, a.cols - c0, slab, tc.slab_ld, st);
+    if (rc != NNCFB_OK) return rc;
+    // rest(b - 1) also updates the panel's columns: it has to finish first
+    if (rest_pending) NNCFB_CUDA(cudaStreamWaitEvent(st, la->rest_done, 0));
+    const int64_t panel = std::min<int64_t>(block, a.cols - c0);
+    rc = gptq_trailing_tc(a.w + c0, a.cols, a.rows, panel, a.err_planes, a.err_ld, slab, tc.slab_ld, st);
+    if (rc != NNCFB_OK) return rc;
+    rest_pending = false;
+    if (c0 + panel < a.cols) {
+      cudaStream_t rest_stream = st;
+      if (overlap) {
+        NNCFB_CUDA(cudaEventRecord(la->panel_done, st));
+        NNCFB_CUDA(cudaStreamWaitEvent(la->side, la->panel_done, 0));
+        rest_stream = la->side;
+      }
+      rc = gptq_trailing_tc(a.w + c0 + panel, a.cols, a.rows, a.cols - c0 - panel, a.err_planes, a.err_ld, slab + panel,
+                            tc.slab_ld, rest_stream);
+      if (rc != NNCFB_OK) return rc;
+      if (overlap) {
+        NNCFB_CUDA(cudaEventRecord(la->rest_done, la->side));
+        rest_pending = true;
       }
     }
   }
+  if (rest_pending) NNCFB_CUDA(cudaStreamWaitEvent(st, la->rest_done, 0));  // nothing is left running on the side stream
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
 }
@@ -450,7 +513,7 @@ extern "C" size_t nncfb_gptq_workspace_bytes(int64_t rows) {
 
 extern "C" size_t nncfb_gptq_workspace_bytes_tensor_cores(int64_t rows, int64_t cols) {
   if (rows <= 0 || cols <= 0) return 0;
-  return err_bytes(rows) + planes_bytes(rows) + planes_bytes(cols);
+  return err_bytes(rows) + 2 * planes_bytes(rows) + 2 * planes_bytes(cols);
 }
 
 namespace nncfb {
@@ -489,10 +552,13 @@ static int gptq_quantize_impl(float* weight, int64_t rows, int64_t cols, const f
   if (workspace_bytes >= nncfb_gptq_workspace_bytes_tensor_cores(rows, cols) && block_size == kGptqMaxBlock &&
       cols > kGptqMaxBlock && rows % 8 == 0 && cols % 4 == 0 && aligned16(weight) && aligned16(workspace) &&
       gptq_trailing_tc_available()) {
-    uint8_t* base = static_cast<uint8_t*>(workspace);
-    a.err_planes = reinterpret_cast<__nv_bfloat16*>(base + err_bytes(rows));
+    uint8_t* base = static_cast<uint8_t*>(workspace) + err_bytes(rows);
+    for (int i = 0; i < 2; ++i) {
+      tc.err_planes[i] = reinterpret_cast<__nv_bfloat16*>(base + i * planes_bytes(rows));
+      tc.slab_planes[i] = reinterpret_cast<__nv_bfloat16*>(base + 2 * planes_bytes(rows) + i * planes_bytes(cols));
+    }
+    a.err_planes = tc.err_planes[0];
     a.err_ld = round8(rows);
-    tc.slab_planes = reinterpret_cast<__nv_bfloat16*>(base + err_bytes(rows) + planes_bytes(rows));
     tc.slab_ld = round8(cols);
   }
   a.given = 0;

@@ -475,20 +475,25 @@ int tc_status_reset(cudaStream_t st) {
   return NNCFB_OK;
 }
 
-// W[:, c0 : c0 + n] -= Err @ Hinv[i1 : i1 + 128, c0 : c0 + n].
-//   w_c0      = W + c0 (row stride ld floats; W 16-byte aligned, ld and c0 multiples of 4)
-//   err_planes: bf16 [3 * 128, err_ld], plane p row k column r = plane p of Err[r][k]  (written by the sweep kernel)
-//   slab_planes: bf16 [3 * 128, slab_ld] scratch, filled here from hinv
-int gptq_trailing_tc(float* w_c0, int64_t ld, int64_t rows, int64_t n, const float* hinv, int64_t cols, int i1, int64_t c0,
-                     const __nv_bfloat16* err_planes, int64_t err_ld, __nv_bfloat16* slab_planes, int64_t slab_ld,
-                     cudaStream_t st) {
+// planes[p][k][j] = plane p of Hinv[i1 + k][c0 + j], j < n (bf16 [3 * 128, ld]).
+int gptq_split_slab(const float* hinv, int64_t cols, int i1, int64_t c0, int64_t n, __nv_bfloat16* slab_planes,
+                    int64_t slab_ld, cudaStream_t st) {
   const dim3 sgrid(static_cast<unsigned>((n + 255) / 256), 128);
   gptq_split_slab_kernel<<<sgrid, 256, 0, st>>>(hinv, cols, i1, c0, n, slab_ld, slab_planes);
   NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+// W[:, c : c + n] -= Err @ Hinv[i1 : i1 + 128, c : c + n].
+//   w_c        = W + c (row stride ld floats; 16-byte aligned, ld a multiple of 4)
+//   err_planes : bf16 [3 * 128, err_ld], plane p row k column r = plane p of Err[r][k]  (written by the sweep kernel)
+//   slab_c     : bf16 [3 * 128, slab_ld] planes of the slab, already offset to column c (16-byte aligned)
+int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv_bfloat16* err_planes, int64_t err_ld,
+                     const __nv_bfloat16* slab_c, int64_t slab_ld, cudaStream_t st) {
   CUtensorMap amap, bmap;
   int rc = encode_map(&amap, err_planes, true, rows, 3 * 128, err_ld);
   if (rc != NNCFB_OK) return rc;
-  rc = encode_map(&bmap, slab_planes, true, n, 3 * 128, slab_ld);
+  rc = encode_map(&bmap, slab_c, true, n, 3 * 128, slab_ld);
   if (rc != NNCFB_OK) return rc;
   const int tiles_m = static_cast<int>((rows + kTileM - 1) / kTileM);
   const int tiles_n = static_cast<int>((n + kTileN - 1) / kTileN);
@@ -497,7 +502,7 @@ int gptq_trailing_tc(float* w_c0, int64_t ld, int64_t rows, int64_t n, const flo
   NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   int* status = nullptr;
   if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
-  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, w_c0, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
+  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, w_c, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
                                                status);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
