@@ -378,6 +378,7 @@ def main():
                     help="compress: the headline metric (default); gptq: the secondary GPTQ metric")
     ap.add_argument("--mode", default="nf4", choices=["nf4", "mxfp4", "fp4"], help="mode of the moe workload")
     ap.add_argument("--layers", type=int, default=4, help="layers of the moe workload (32 = the full 90 GB stack)")
+    ap.add_argument("--no-affinity", action="store_true", help="do not bind the process to the CPUs closest to its GPU")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profilers: one decoder layer, no e2e / cpu arm, 1 warm-up, 1 step")
     args = ap.parse_args()
@@ -411,8 +412,11 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    from nncf_b200.pipeline import CompressionPlan, HostStreamingCompressor
+    from nncf_b200.pipeline import CompressionPlan, HostStreamingCompressor, bind_host_thread_near
 
+    # one process per GPU: keep this rank's pinned buffers and copy threads on the CPUs next to its GPU
+    cpus_at_start = os.sched_getaffinity(0)
+    affinity = bind_host_thread_near(device) if not args.no_affinity else "unchanged (--no-affinity)"
     items = build_weight_set(device, seed=1 + rank)
     if args.profile_case:
         items = items[1:8]  # one decoder layer: 436 MB of weights, larger than L2
@@ -550,6 +554,7 @@ def main():
                    "d2h_bytes_per_step": hsc.d2h_bytes, "ms_per_step": round(dt * 1e3, 3), "steps": args.e2e_steps,
                    "api": "nncf_b200.pipeline.HostStreamingCompressor.run (pinned host weights in, packed results "
                           "back in pinned host memory; 3-stream overlap of H2D, kernels, D2H)"}
+            e2e["host_affinity"] = affinity
             if subset_note:
                 e2e["subset"] = subset_note
         else:
@@ -586,6 +591,7 @@ def main():
         "roofline": roofline, "e2e": e2e, "gather_to_rank0": gather, "gpu_launches": args.steps * 2, "clocks": clocks,
     }
     if world == 1 and not args.no_cpu_baseline:
+        os.sched_setaffinity(0, cpus_at_start)  # the CPU baseline gets every core the process started with
         threads = host_threads()
         gbs, dt, nbytes = cpu_reference_sample(threads, 3, 1)
         line["cpu_baseline"] = {

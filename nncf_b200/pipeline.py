@@ -217,6 +217,43 @@ def llama3_8b_weight_shapes(include_embeddings: bool = True) -> list[tuple[str, 
     return shapes
 
 
+def bind_host_thread_near(device) -> str:
+    """Restrict this process to the CPUs NVML reports as closest to ``device`` (same NUMA node / PCIe root), so
+    that pinned staging buffers allocated afterwards are placed in that node's memory and the copy threads run
+    next to it.  With one process per GPU on a multi-socket host this keeps every rank's host<->device traffic
+    off the inter-socket link.  Returns a short description of what was done; any failure leaves the affinity
+    unchanged (NVML missing, the container's CPU set does not intersect the ideal one, ...)."""
+    import os
+
+    try:
+        import pynvml
+
+        index = torch.device(device).index
+        if index is None:
+            index = torch.cuda.current_device()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        pynvml.nvmlInit()
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            handle = (pynvml.nvmlDeviceGetHandleByIndex(int(ids[index])) if ids[index].isdigit()
+                      else pynvml.nvmlDeviceGetHandleByUUID(ids[index]))
+        else:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (ncpu + 63) // 64)
+        ideal = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        target = ideal & allowed
+        if not target:
+            return "unchanged (the ideal CPUs are outside this process's CPU set)"
+        if target == allowed:
+            return f"unchanged (already on the {len(target)} closest CPUs)"
+        os.sched_setaffinity(0, target)
+        return f"bound to {len(target)} CPUs closest to the GPU (of {len(allowed)} allowed)"
+    except Exception as exc:  # noqa: BLE001 - affinity is an optimisation, never a failure
+        return f"unchanged ({type(exc).__name__})"
+
+
 class HostStreamingCompressor:
     """Compress weights that live in (pinned) host memory and return the stored form to host
     memory, overlapping the host->device copy of tensor i+1, the kernel of tensor i and the
