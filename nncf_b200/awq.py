@@ -32,16 +32,21 @@ class AWQ:
 
     def _data_aware_step(self, wp, weight: torch.Tensor, statistics: WCTensorStatistic, act_ch_axis: int = -1,
                          prev_weight: Optional[torch.Tensor] = None,
-                         prev_statistics: Optional[WCTensorStatistic] = None) -> torch.Tensor:
-        """awq.py:243-357 for a 2-D weight.  ``wp`` carries ``compression_config`` and
-        ``reduction_axes`` (a 1-tuple).  Returns the per-input-channel scale [hidden] (fp32)."""
+                         prev_statistics: Optional[WCTensorStatistic] = None,
+                         _prev_s: Optional[float] = None) -> torch.Tensor:
+        """awq.py:243-357.  ``wp`` carries ``compression_config`` and ``reduction_axes`` (a 1-tuple).
+        Returns the per-input-channel scale [hidden] (fp32); for a stacked weight [E, ., .] with statistics
+        [E, hidden] per sample, [E, hidden]: the reference treats the experts independently (top-k channels,
+        groups and alpha search per expert), sharing only the maximum of the previous layer's statistics."""
         config: WeightCompressionConfig = wp.compression_config
         alpha_step = (self._alpha_max - self._alpha_min) / self._steps
+        if weight.ndim == 3:
+            return self._stacked(wp, weight, statistics, act_ch_axis, prev_weight, prev_statistics)
         s, X = process_stats(statistics, self._subset_size, act_ch_axis)
         s = s.to(torch.float32)
         X = X.to(torch.float32).contiguous()
         if weight.ndim != 2:
-            msg = "the AWQ kernel supports 2-D weights"
+            msg = "the AWQ kernel supports 2-D weights and stacks of them"
             raise ValueError(msg)
         reduction_axis = wp.reduction_axes[0]
         dev = weight.device
@@ -49,7 +54,7 @@ class AWQ:
         prev_s, prev_w, prev_rdim = 0.0, None, 0.0
         if prev_statistics is not None and prev_weight is not None:
             ps, _ = process_stats(prev_statistics, self._subset_size, act_ch_axis)
-            prev_s = float(ps.to(torch.float32).max().item())
+            prev_s = float(ps.to(torch.float32).max().item()) if _prev_s is None else _prev_s
             prev_w = prev_weight.float().abs().mean(dim=reduction_axis).contiguous()
             prev_rdim = float(prev_weight.shape[reduction_axis])
         top_k = max(int(hidden * self._percent_to_apply), 1)
@@ -83,6 +88,26 @@ class AWQ:
                 self._steps, _lib.ptr(prev_w), prev_s, prev_rdim, FP16_OVERFLOW_MARGIN * FP16_MAX_VALUE,
                 _lib.ptr(scale), _lib.ptr(workspace), ws_bytes, _lib.stream_handle(dev)))
         return scale
+
+    def _stacked(self, wp, weight, statistics, act_ch_axis, prev_weight, prev_statistics) -> torch.Tensor:
+        """One 2-D search per expert with that expert's slice of every statistic (awq.py:276-300 iterates
+        (expert, group) pairs; prev_s is the maximum over ALL experts, awq.py:264-266)."""
+        axis = wp.reduction_axes[0]
+        wp2 = SimpleNamespace(compression_config=wp.compression_config, reduction_axes=(axis - 1,))
+        prev_s = None
+        if prev_statistics is not None and prev_weight is not None:
+            ps, _ = process_stats(prev_statistics, self._subset_size, act_ch_axis)
+            prev_s = float(ps.to(torch.float32).max().item())
+        scales = []
+        for e in range(weight.shape[0]):
+            st = WCTensorStatistic([m[e] for m in statistics.mean_values], [tuple(sh[1:]) for sh in statistics.shape_values])
+            pst = None
+            if prev_statistics is not None:
+                pst = WCTensorStatistic([m[e] for m in prev_statistics.mean_values],
+                                        [tuple(sh[1:]) for sh in prev_statistics.shape_values])
+            scales.append(self._data_aware_step(wp2, weight[e], st, act_ch_axis,
+                                                prev_weight[e] if prev_weight is not None else None, pst, prev_s))
+        return torch.stack(scales)
 
     def _data_free_step(self, weight: torch.Tensor, axis: int) -> torch.Tensor:
         """1 / max(mean |W| over `axis`, eps).  awq.py:363-366 (a [hidden]-sized reduction)."""

@@ -89,31 +89,37 @@ class GPTQ:
 
     # ------------------------------------------------------------------------------------------
     def _calculate_hessian(self, node, inputs: Sequence[torch.Tensor], is_3d_weight: bool = False) -> torch.Tensor:
-        """gptq.py:200-242 for a 2-D weight: running H = sum (2/n) X^T X over the calibration inputs.
-        ``inputs``: activations [b, T, C] or [T, C] (channel last).  Returns [1, C, C] fp32 like the
-        reference.  ``node`` is accepted for signature compatibility and ignored."""
-        if is_3d_weight:
-            msg = "stacked (3-D) weights: call per expert"
-            raise NotImplementedError(msg)
+        """gptq.py:200-242: running H = sum (2/n) X^T X over the calibration inputs.
+        ``inputs``: activations [b, T, C] or [T, C] (channel last); returns [1, C, C] fp32 like the reference.
+        With ``is_3d_weight`` (stacked experts) every input is [E, T, C], counts as one sample, and the result
+        is [E, C, C]: expert e accumulates the e-th slice of every input.  ``node`` is accepted for signature
+        compatibility and ignored."""
         C = inputs[0].shape[-1]
         dev = inputs[0].device
-        H = torch.zeros((C, C), dtype=torch.float32, device=dev)
+        experts = 1
+        if is_3d_weight:
+            experts = 1
+            for d in inputs[0].shape[:-2]:
+                experts *= int(d)
+        H = torch.zeros((experts, C, C), dtype=torch.float32, device=dev)
         nsamples = 0
         with torch.cuda.device(dev):
             st = _lib.stream_handle(dev)
             for inp in inputs:
-                batch = inp.shape[0] if inp.ndim == 3 else 1
-                x = inp.reshape(-1, C).contiguous()
+                batch = 1 if is_3d_weight or inp.ndim != 3 else inp.shape[0]
+                x = inp.reshape(experts, -1, C) if is_3d_weight else inp.reshape(1, -1, C)
                 if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
                     x = x.float()
+                x = x.contiguous()
                 alpha = nsamples / (nsamples + batch)
                 nsamples += batch
                 beta = 2.0 / nsamples
-                _lib.check(_lib.lib.nncfb_hessian_accumulate(
-                    _lib.ptr(H), C, _lib.ptr(x), _lib.DTYPE_IDS[x.dtype], x.shape[0], alpha, beta,
-                    1 if self._tensor_cores else 0, None, 0, st))
+                for e in range(experts):
+                    _lib.check(_lib.lib.nncfb_hessian_accumulate(
+                        _lib.ptr(H[e]), C, _lib.ptr(x[e]), _lib.DTYPE_IDS[x.dtype], x.shape[1], alpha, beta,
+                        1 if self._tensor_cores else 0, None, 0, st))
             _lib.check(_lib.lib.nncfb_hessian_status(st))
-        return H.unsqueeze(0)
+        return H
 
     def accumulate_hessian(self, H: torch.Tensor, x: torch.Tensor, nsamples: int, batch: int) -> int:
         """One step of the running accumulation for callers that stream activations layer by layer:
@@ -231,3 +237,19 @@ class GPTQ:
         if config.mode not in (CompressWeightsMode.INT8_ASYM, CompressWeightsMode.INT4_ASYM):
             zero_points = None
         return q, scales, zero_points
+
+    def quantize_stacked(self, wc_params, hessian: torch.Tensor, weight_tensor: torch.Tensor,
+                         inputs: Optional[Sequence[torch.Tensor]] = None):
+        """The per-expert loop of GPTQ.apply for a 3-D weight [E, out, C] (gptq.py:147-171): expert e is quantised
+        with hessian[e] and the e-th slice of every input; results are stacked on axis 0.  Returns (dequantised
+        weight [E, out, C], scales [E, out, G, 1], zero points or None)."""
+        qs, scs, zps = [], [], []
+        for e in range(weight_tensor.shape[0]):
+            inp = [i.reshape(weight_tensor.shape[0], -1, i.shape[-1])[e] for i in inputs] if inputs else None
+            w = weight_tensor[e].float().contiguous()
+            q, sc, zp = self._quantize_weights(wc_params, hessian[e], w, inp)
+            qs.append(q)
+            scs.append(sc)
+            zps.append(zp)
+        zero_point = torch.stack(zps) if None not in zps else None
+        return torch.stack(qs), torch.stack(scs), zero_point

@@ -122,6 +122,34 @@ def test_awq_matches_reference_golden(case):
     np.testing.assert_allclose(got, ref, rtol=2e-5)
 
 
+def test_awq_stacked_experts_equal_per_expert_searches():
+    """A 3-D weight [E, out, in] with statistics [E, hidden] per sample: the reference searches every
+    (expert, group) pair on its own (awq.py:276-300), so the stacked call must equal E separate 2-D calls, with
+    the previous layer's activation maximum taken over all experts (awq.py:264-266)."""
+    from nncf_b200.awq import AWQ, make_wp
+    from nncf_b200.config import WCTensorStatistic
+
+    gen = torch.Generator().manual_seed(17)
+    E, out, hid, n = 3, 48, 256, 12
+    w = (torch.randn(E, out, hid, generator=gen) * 0.05).cuda()
+    means = [torch.randn(E, hid, generator=gen).cuda() * (1 + 5 * (torch.arange(hid) % 37 == 0)).cuda() for _ in range(n)]
+    stats = WCTensorStatistic(means, [(E, 16, hid)] * n)
+    prev_w = (torch.randn(E, hid, 64, generator=gen) * 0.05).cuda()   # [E, out_prev = hid, in_prev]
+    prev_means = [torch.randn(E, 64, generator=gen).cuda() * (e + 1) for e in range(n)]
+    prev_stats = WCTensorStatistic(prev_means, [(E, 16, 64)] * n)
+    algo = AWQ(subset_size=32, percent_to_apply=0.02, steps=20)
+    cfg = _cfg("int4_asym", 64)
+    got = algo._data_aware_step(make_wp(cfg, (2,)), w, stats, -1, prev_w, prev_stats)
+    assert tuple(got.shape) == (E, hid)
+    prev_s = float(torch.stack(prev_means).abs().amax().item())
+    for e in range(E):
+        st = WCTensorStatistic([m[e] for m in means], [(16, hid)] * n)
+        pst = WCTensorStatistic([m[e] for m in prev_means], [(16, 64)] * n)
+        one = algo._data_aware_step(make_wp(cfg, (1,)), w[e], st, -1, prev_w[e], pst, prev_s)
+        assert torch.equal(one, got[e])
+        assert (one != 1).any()
+
+
 def test_awq_data_free_matches_reference_golden():
     from nncf_b200.awq import AWQ
 

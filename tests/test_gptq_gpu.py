@@ -242,3 +242,28 @@ def test_tensor_core_hessian_tile_order_covers_the_triangle(C):
     tol = 4e-7 * float(ref.abs().max()) * (192 ** 0.5)
     assert (H - ref).abs().max().item() <= tol
     assert torch.equal(H, H.T)
+
+
+def test_stacked_expert_weights_follow_the_per_expert_loop():
+    """3-D weights [E, out, C] with 3-D inputs [E, T, C] (gptq.py:147-171, :217-241): every expert gets its own
+    Hessian from its slice of each input (one sample per input) and is quantised on its own."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200.gptq import GPTQ
+
+    gen = torch.Generator().manual_seed(21)
+    E, out, C, T = 3, 16, 256, 96
+    inputs = [torch.randn(E, T, C, generator=gen).to(torch.bfloat16).cuda() for _ in range(4)]
+    w = (torch.randn(E, out, C, generator=gen) * 0.05).cuda()
+    g = GPTQ(0.05, 128, 4)
+    H = g._calculate_hessian(None, inputs, is_3d_weight=True)
+    assert tuple(H.shape) == (E, C, C)
+    for e in range(E):
+        ref = O.gptq_hessian([i[e].float().cpu().numpy() for i in inputs])
+        np.testing.assert_allclose(H[e].cpu().numpy(), ref, rtol=0, atol=2e-5 * np.abs(ref).max())
+    q, s, z = g.quantize_stacked(_wp("int4_sym", 64), H.clone(), w.clone(), inputs)
+    assert tuple(q.shape) == (E, out, C) and tuple(s.shape) == (E, out, C // 64, 1) and z is None
+    for e in range(E):
+        qe, se, _ = g._quantize_weights(_wp("int4_sym", 64), H[e].clone(), w[e].clone().contiguous())
+        assert torch.equal(qe, q[e]) and torch.equal(se, s[e])
+    assert not torch.equal(q[0], q[1])
