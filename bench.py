@@ -526,6 +526,9 @@ def main():
                          int(it.name.split(".")[2]) < n_layers]
             subset_note = f"first {n_layers} decoder layers only (host memory budget per rank {budget / 1e9:.1f} GB)"
         if e2e_items:
+            # largest tensors first, the order the reference compresses in (WC/algorithm.py:1198-1199): the copies that
+            # cannot overlap with anything (first tensor in, last result out) are then the cheap ones
+            e2e_items = sorted(e2e_items, key=lambda it: -it.source_bytes)
             e2e_src = sum(it.source_bytes for it in e2e_items)
             specs = [(it.name, tuple(it.weight.shape), it.weight.dtype, it.config) for it in e2e_items]
             host_w = []
