@@ -21,7 +21,9 @@ _TRI_LEAF = 1024  # below this size a triangular block is inverted / multiplied 
 
 
 def _aligned_half(n: int) -> int:
-    return (n // 2 + 127) // 128 * 128
+    """Split point of an n x n triangle: about half, on a multiple of 128 when that still splits."""
+    h = (n // 2 + 127) // 128 * 128
+    return h if 0 < h < n else max(n // 2, 1)
 
 
 def _mul_right_lower(B: torch.Tensor, A: torch.Tensor, out: torch.Tensor) -> None:

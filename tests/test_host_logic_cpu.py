@@ -1,0 +1,88 @@
+"""Host-side logic that needs no GPU: the GEMM-based triangular inverse and the two routes to GPTQ's inverse
+factor (pure torch), and the CPU-affinity helper against a fake NVML."""
+import os
+import sys
+import types
+
+import pytest
+import torch
+
+
+def _gptq_module():
+    # nncf_b200/__init__ loads the CUDA library; the module under test only needs torch for these functions
+    import importlib
+
+    try:
+        return importlib.import_module("nncf_b200.gptq")
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"nncf_b200 cannot be imported here: {exc}")
+
+
+@pytest.mark.parametrize("n", [1, 37, 128, 300, 1000])
+def test_lower_triangular_inverse_matches_dense_inverse(n, monkeypatch):
+    g = _gptq_module()
+    monkeypatch.setattr(g, "_TRI_LEAF", 64)  # force several levels of recursion at small sizes
+    gen = torch.Generator().manual_seed(n)
+    L = torch.tril(torch.randn(n, n, generator=gen, dtype=torch.float64)) * 0.1
+    L.diagonal().copy_(1.0 + torch.rand(n, generator=gen, dtype=torch.float64))
+    got = g.lower_triangular_inverse(L)
+    assert torch.equal(got, torch.tril(got))
+    torch.testing.assert_close(got @ L, torch.eye(n, dtype=torch.float64), rtol=0, atol=1e-10)
+
+
+def test_inverse_factor_routes_agree_on_cpu(monkeypatch):
+    """U with H^-1 = U^T U: the reversed-order route (one Cholesky + triangular inverse) against the reference's
+    three calls (gptq.py:293-295), including dead columns and damping."""
+    g = _gptq_module()
+    monkeypatch.setattr(g, "_TRI_LEAF", 32)
+    gen = torch.Generator().manual_seed(3)
+    C = 200
+    x = torch.randn(512, C, generator=gen, dtype=torch.float64)
+    x[:, 7] = 0
+    H = (2.0 / 4) * (x.T @ x)
+    w = torch.randn(8, C, generator=gen, dtype=torch.float64)
+    out = {}
+    for route in ("reversed", "reference"):
+        Hc, wc = H.clone(), w.clone()
+        out[route] = g.GPTQ(0.01, inverse_factor=route).prepare_hessian_inverse(Hc, wc)
+        assert torch.all(wc[:, 7] == 0)
+        assert getattr(out[route], "_dead_columns")[7]
+    torch.testing.assert_close(out["reversed"], out["reference"], rtol=0, atol=1e-9)
+    Hd = H.clone()
+    Hd[7, 7] = 1
+    Hd.diagonal().add_(0.01 * Hd.diagonal().mean())
+    torch.testing.assert_close(out["reversed"].T @ out["reversed"], torch.linalg.inv(Hd), rtol=0, atol=1e-8)
+
+
+def test_bind_host_thread_near_uses_nvml_cpu_set(monkeypatch):
+    try:
+        from nncf_b200.pipeline import bind_host_thread_near
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"nncf_b200 cannot be imported here: {exc}")
+    allowed = sorted(os.sched_getaffinity(0))
+    if len(allowed) < 2:
+        pytest.skip("needs at least two CPUs")
+    want = set(allowed[: len(allowed) // 2])
+    words = [0] * (max(allowed) // 64 + 1)
+    for c in want:
+        words[c // 64] |= 1 << (c % 64)
+    calls = {}
+    fake = types.SimpleNamespace(
+        nvmlInit=lambda: None,
+        nvmlDeviceGetHandleByIndex=lambda i: calls.setdefault("index", i) or "h",
+        nvmlDeviceGetHandleByUUID=lambda u: "h",
+        nvmlDeviceGetCpuAffinity=lambda h, n: (words + [0] * n)[:n],
+    )
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES", raising=False)
+    before = os.sched_getaffinity(0)
+    try:
+        msg = bind_host_thread_near(torch.device("cuda", 0))
+        assert os.sched_getaffinity(0) == want, msg
+        assert "bound to" in msg
+        # an NVML failure leaves the affinity alone
+        fake.nvmlDeviceGetCpuAffinity = lambda h, n: (_ for _ in ()).throw(RuntimeError("no nvml"))
+        assert "unchanged" in bind_host_thread_near(torch.device("cuda", 0))
+        assert os.sched_getaffinity(0) == want
+    finally:
+        os.sched_setaffinity(0, before)
