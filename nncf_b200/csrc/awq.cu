@@ -7,10 +7,11 @@
 // activations divided by the same scale, and keep the alpha with the smallest mean absolute output
 // error.  The reference runs ~10 tensor operations per (group, alpha) with a host synchronisation
 // each; here
-//   awq_score_kernel   one warp per (group, alpha, output channel): weights in registers, the
-//                      group's activation slices (raw and divided by the candidate scale) staged
-//                      in shared memory; per-block partial error sums go to a scratch buffer
-//                      (deterministic: no atomics);
+//   awq_score_kernel   one block per (group, run of alphas, 64 output channels): the group's activation
+//                      slices (raw and divided by the candidate scale) staged in shared memory, the
+//                      alpha-independent outputs W_g X_g computed once per block, four output channels
+//                      per warp at a time sharing every activation value they fetch; per-block partial
+//                      error sums go to a scratch buffer (deterministic: no atomics);
 //   awq_select_kernel  one block per group: reduces the partials in a fixed order, walks the alphas
 //                      with the reference's strict '<' rule and writes the winning scale.
 #include <algorithm>
@@ -50,146 +51,189 @@ __device__ __forceinline__ float awq_candidate(float gs_i, float alpha, const fl
 
 constexpr int kAwqRowsPerWarp = 8;
 
-template <typename SrcT, int MODE, int EPL>
-__global__ void __launch_bounds__(256) awq_score_kernel(const AwqArgs a) {
+// sum_i v_r[i] * X[i, col] for R vectors at once, i ascending (the same routine as in the ScaleEstimation
+// kernel: every activation value fetched from shared memory serves R rows).
+template <int R, int MAXC>
+__device__ __forceinline__ void awq_project(const float* __restrict__ vbuf, int stride, const float* __restrict__ xs, int gs4,
+                                            int np, int lane, float (&acc)[R][MAXC][2]) {
+  const int chunks = np >> 6;
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) acc[r][c][0] = acc[r][c][1] = 0.0f;
+  for (int i = 0; i < gs4; i += 4) {
+    float dv[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float4 d = *reinterpret_cast<const float4*>(vbuf + r * stride + i);
+      dv[r][0] = d.x; dv[r][1] = d.y; dv[r][2] = d.z; dv[r][3] = d.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float* row = xs + static_cast<size_t>(i + k) * np + 2 * lane;
+#pragma unroll
+      for (int c = 0; c < MAXC; ++c) {
+        if (c < chunks) {
+          const float2 xv = *reinterpret_cast<const float2*>(row + 64 * c);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            acc[r][c][0] = __fmaf_rn(dv[r][k], xv.x, acc[r][c][0]);
+            acc[r][c][1] = __fmaf_rn(dv[r][k], xv.y, acc[r][c][1]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// One block: 64 output channels (8 per warp, R at a time) of one group, for a run of consecutive alphas.
+// The full-precision outputs W_g X_g do not depend on alpha: they are computed once per block and kept in
+// shared memory; per alpha only the candidate scale, the divided activations and the quantised projection
+// are redone.  Sums are accumulated per lane in ascending row order and reduced in a fixed order.
+template <typename SrcT, int MODE, int EPL, int R, int MAXC>
+__global__ void __launch_bounds__(256) awq_score_kernel(const AwqArgs a, const int alphas_per_block) {
   extern __shared__ __align__(16) float smem[];
   const int gs = a.gs, np = a.np;
   const int gs4 = (gs + 3) & ~3;
   float* xs = smem;                                   // raw activations   [gs4, np]
   float* xd = xs + static_cast<size_t>(gs4) * np;     // divided by scale  [gs4, np]
   float* cur = xd + static_cast<size_t>(gs4) * np;    // candidate scale   [gs4]
-  float* vbufs = cur + gs4;                           // [8][gs4]
+  float* vbufs = cur + gs4;                           // [8][R][gs4]
+  float* fps = vbufs + 8 * R * gs4;                   // [64 rows][np] full-precision outputs
   __shared__ float red_sum[8], red_max[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* vbuf = vbufs + warp * gs4;
-  const int grp = blockIdx.z, ai = blockIdx.y, tile = blockIdx.x;
+  float* vbuf = vbufs + warp * R * gs4;
+  const int grp = blockIdx.z, tile = blockIdx.x;
+  const int ai0 = blockIdx.y * alphas_per_block, ai1 = min(ai0 + alphas_per_block, a.n_alpha);
   const int64_t off = static_cast<int64_t>(a.group_idx[grp]) * gs;
-  const float alpha = a.alphas[ai];
+  const SrcT* __restrict__ wsrc = reinterpret_cast<const SrcT*>(a.weight);
 
-  for (int i = threadIdx.x; i < gs4; i += blockDim.x) {
-    cur[i] = i < gs ? awq_candidate(a.gscale[static_cast<int64_t>(grp) * gs + i], alpha, a.prev_w, off + i, a.prev_s,
-                                    a.prev_rdim, a.threshold)
-                    : 1.0f;
-  }
-  __syncthreads();
   for (int idx = threadIdx.x; idx < gs4 * np; idx += blockDim.x) {
     const int i = idx / np, c = idx - i * np;
-    const float v = (i < gs && c < a.n) ? a.x[(off + i) * a.n + c] : 0.0f;
-    xs[idx] = v;
-    xd[idx] = __fdiv_rn(v, cur[i]);
+    xs[idx] = (i < gs && c < a.n) ? a.x[(off + i) * a.n + c] : 0.0f;
   }
-  for (int i = gs + lane; i < gs4; i += 32) vbuf[i] = 0.0f;
+  for (int r = 0; r < R; ++r)
+    for (int i = gs + lane; i < gs4; i += 32) vbuf[r * gs4 + i] = 0.0f;
   __syncthreads();
 
-  const SrcT* __restrict__ wsrc = reinterpret_cast<const SrcT*>(a.weight);
-  float sum = 0.0f, amax = 0.0f;
-  const int64_t row0 = (static_cast<int64_t>(tile) * 8 + warp) * kAwqRowsPerWarp;
-  for (int rr = 0; rr < kAwqRowsPerWarp; ++rr) {
-    const int64_t row = row0 + rr;
-    if (row >= a.rows) break;
-    const SrcT* wrow = wsrc + row * a.cols + off;
-    float w[EPL];
-    bool have[EPL];
+  bool have[EPL];
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      const int i = lane + 32 * j;
-      have[j] = i < gs;
-      w[j] = have[j] ? to_f32<SrcT>(wrow[i]) : 0.0f;
-      if (have[j]) vbuf[i] = w[j];
+  for (int j = 0; j < EPL; ++j) have[j] = lane + 32 * j < gs;
+  const int64_t row0 = (static_cast<int64_t>(tile) * 8 + warp) * kAwqRowsPerWarp;
+
+  // ---- fp32_out = W_g x X_g for the block's rows ---------------------------------------------------------
+  float amax = 0.0f;
+  for (int rr = 0; rr < kAwqRowsPerWarp; rr += R) {
+    if (row0 + rr >= a.rows) break;  // warp-uniform
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const SrcT* wrow = wsrc + min(row0 + rr + r, a.rows - 1) * a.cols + off;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        if (have[j]) vbuf[r * gs4 + lane + 32 * j] = to_f32<SrcT>(wrow[lane + 32 * j]);
+      }
     }
     __syncwarp();
-    float fpc[4][2], qoc[4][2];
-    // fp32_out = W_g x X_g
-    {
-      const int chunks = np >> 6;
+    float fp[R][MAXC][2];
+    awq_project<R, MAXC>(vbuf, gs4, xs, gs4, np, lane, fp);
+    __syncwarp();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) fpc[c][0] = fpc[c][1] = 0.0f;
-      for (int i = 0; i < gs4; ++i) {
-        const float d = vbuf[i];
-        const float* xr = xs + static_cast<size_t>(i) * np + 2 * lane;
+    for (int r = 0; r < R; ++r) {
+      float* dst = fps + static_cast<size_t>(warp * kAwqRowsPerWarp + rr + r) * np + 2 * lane;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (c < chunks) {
-            const float2 xv = *reinterpret_cast<const float2*>(xr + 64 * c);
-            fpc[c][0] = __fmaf_rn(d, xv.x, fpc[c][0]);
-            fpc[c][1] = __fmaf_rn(d, xv.y, fpc[c][1]);
+      for (int c = 0; c < MAXC; ++c) {
+        if (c < (np >> 6)) {
+          *reinterpret_cast<float2*>(dst + 64 * c) = make_float2(fp[r][c][0], fp[r][c][1]);
+          if (row0 + rr + r < a.rows) amax = fmaxf(amax, fmaxf(fabsf(fp[r][c][0]), fabsf(fp[r][c][1])));
+        }
+      }
+    }
+  }
+
+  for (int ai = ai0; ai < ai1; ++ai) {
+    const float alpha = a.alphas[ai];
+    __syncthreads();  // the previous alpha's readers of cur / xd / red_* are done
+    for (int i = threadIdx.x; i < gs4; i += blockDim.x) {
+      cur[i] = i < gs ? awq_candidate(a.gscale[static_cast<int64_t>(grp) * gs + i], alpha, a.prev_w, off + i, a.prev_s,
+                                      a.prev_rdim, a.threshold)
+                      : 1.0f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gs4 * np; idx += blockDim.x) xd[idx] = __fdiv_rn(xs[idx], cur[idx / np]);
+    __syncthreads();
+
+    float sum = 0.0f;
+    for (int rr = 0; rr < kAwqRowsPerWarp; rr += R) {
+      if (row0 + rr >= a.rows) break;
+      // scaled weight, per-channel parameters over the group, quantise-dequantise
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const SrcT* wrow = wsrc + min(row0 + rr + r, a.rows - 1) * a.cols + off;
+        float ws[EPL];
+        float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+          ws[j] = have[j] ? __fmul_rn(to_f32<SrcT>(wrow[lane + 32 * j]), cur[lane + 32 * j]) : 0.0f;
+          if (have[j]) {
+            mn = fminf(mn, ws[j]);
+            mx = fmaxf(mx, ws[j]);
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        Codec<MODE> c;
+        c.from_stats(mn, mx);
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+          float u = 0.0f;
+          if (have[j]) {
+            c.encode(ws[j], u);
+            vbuf[r * gs4 + lane + 32 * j] = __fmul_rn(u, c.scale);
+          }
+        }
+      }
+      __syncwarp();
+      float qo[R][MAXC][2];
+      awq_project<R, MAXC>(vbuf, gs4, xd, gs4, np, lane, qo);
+      __syncwarp();
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (row0 + rr + r < a.rows) {
+          const float* src = fps + static_cast<size_t>(warp * kAwqRowsPerWarp + rr + r) * np + 2 * lane;
+#pragma unroll
+          for (int c = 0; c < MAXC; ++c) {
+            if (c < (np >> 6)) {
+              const float2 f = *reinterpret_cast<const float2*>(src + 64 * c);
+              sum = __fadd_rn(sum, fabsf(__fsub_rn(qo[r][c][0], f.x)));
+              sum = __fadd_rn(sum, fabsf(__fsub_rn(qo[r][c][1], f.y)));
+            }
           }
         }
       }
     }
-    __syncwarp();
-    // scaled weight, per-channel parameters over the group, quantise-dequantise
-    float ws[EPL];
-    float mn = __uint_as_float(0x7f800000u), mx = __uint_as_float(0xff800000u);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      ws[j] = have[j] ? __fmul_rn(w[j], cur[lane + 32 * j]) : 0.0f;
-      if (have[j]) {
-        mn = fminf(mn, ws[j]);
-        mx = fmaxf(mx, ws[j]);
-      }
-    }
+    float m = amax;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     }
-    Codec<MODE> c;
-    c.from_stats(mn, mx);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      float u = 0.0f;
-      if (have[j]) {
-        c.encode(ws[j], u);
-        vbuf[lane + 32 * j] = __fmul_rn(u, c.scale);
+    if (lane == 0) {
+      red_sum[warp] = sum;
+      red_max[warp] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.0f, mm = 0.0f;
+      for (int w8 = 0; w8 < 8; ++w8) {
+        s = __fadd_rn(s, red_sum[w8]);
+        mm = fmaxf(mm, red_max[w8]);
       }
+      a.part[(static_cast<int64_t>(grp) * a.n_alpha + ai) * a.tiles + tile] = s;
+      if (ai == 0) a.pmax[static_cast<int64_t>(grp) * a.tiles + tile] = mm;
     }
-    __syncwarp();
-    {
-      const int chunks = np >> 6;
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) qoc[cc][0] = qoc[cc][1] = 0.0f;
-      for (int i = 0; i < gs4; ++i) {
-        const float d = vbuf[i];
-        const float* xr = xd + static_cast<size_t>(i) * np + 2 * lane;
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          if (cc < chunks) {
-            const float2 xv = *reinterpret_cast<const float2*>(xr + 64 * cc);
-            qoc[cc][0] = __fmaf_rn(d, xv.x, qoc[cc][0]);
-            qoc[cc][1] = __fmaf_rn(d, xv.y, qoc[cc][1]);
-          }
-        }
-      }
-    }
-    __syncwarp();
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-      if (cc < (np >> 6)) {
-        sum = __fadd_rn(sum, fabsf(__fsub_rn(qoc[cc][0], fpc[cc][0])));
-        sum = __fadd_rn(sum, fabsf(__fsub_rn(qoc[cc][1], fpc[cc][1])));
-        amax = fmaxf(amax, fmaxf(fabsf(fpc[cc][0]), fabsf(fpc[cc][1])));
-      }
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  }
-  if (lane == 0) {
-    red_sum[warp] = sum;
-    red_max[warp] = amax;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float s = 0.0f, m = 0.0f;
-    for (int w8 = 0; w8 < 8; ++w8) {
-      s = __fadd_rn(s, red_sum[w8]);
-      m = fmaxf(m, red_max[w8]);
-    }
-    a.part[(static_cast<int64_t>(grp) * a.n_alpha + ai) * a.tiles + tile] = s;
-    if (ai == 0) a.pmax[static_cast<int64_t>(grp) * a.tiles + tile] = m;
   }
 }
 
@@ -228,17 +272,33 @@ __global__ void __launch_bounds__(128) awq_select_kernel(const AwqArgs a) {
   }
 }
 
-template <typename SrcT, int MODE>
-int launch_awq(const AwqArgs& a, cudaStream_t st) {
+inline int awq_rows_at_a_time(int gs, int np) {
+  const int chunks = np >> 6, epl = (gs + 31) / 32;
+  if (chunks <= 1 && epl <= 4) return 4;
+  if (chunks <= 2 && epl <= 8) return 2;
+  return 1;
+}
+inline size_t awq_smem_bytes(int gs, int np) {
+  const int gs4 = (gs + 3) & ~3;
+  return (2 * static_cast<size_t>(gs4) * np + gs4 + 8 * static_cast<size_t>(awq_rows_at_a_time(gs, np)) * gs4 +
+          static_cast<size_t>(8 * kAwqRowsPerWarp) * np) * sizeof(float);
+}
+
+template <typename SrcT, int MODE, int R, int MAXC>
+int launch_awq_rc(const AwqArgs& a, cudaStream_t st) {
   const int epl = (a.gs + 31) / 32;
-  const int gs4 = (a.gs + 3) & ~3;
-  const size_t smem = (2 * static_cast<size_t>(gs4) * a.np + 9 * static_cast<size_t>(gs4)) * sizeof(float);
-  const dim3 grid(a.tiles, a.n_alpha, a.n_groups);
-#define NNCFB_AWQ_LAUNCH(E)                                                                                      \
-  do {                                                                                                           \
-    NNCFB_CUDA(cudaFuncSetAttribute(awq_score_kernel<SrcT, MODE, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                    static_cast<int>(smem)));                                                    \
-    awq_score_kernel<SrcT, MODE, E><<<grid, 256, smem, st>>>(a);                                                 \
+  const size_t smem = awq_smem_bytes(a.gs, a.np);
+  // alphas per block: as many as still leave a few blocks per SM (the alpha-independent part is then amortised)
+  const int64_t units = static_cast<int64_t>(a.tiles) * a.n_groups * a.n_alpha;
+  const int per_block = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(16, units / (8 * sm_count()))));
+  const dim3 grid(a.tiles, (a.n_alpha + per_block - 1) / per_block, a.n_groups);
+#define NNCFB_AWQ_LAUNCH(E)                                                                                       \
+  do {                                                                                                            \
+    if constexpr (E * R <= 16) {                                                                                  \
+      NNCFB_CUDA(cudaFuncSetAttribute(awq_score_kernel<SrcT, MODE, E, R, MAXC>,                                   \
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));      \
+      awq_score_kernel<SrcT, MODE, E, R, MAXC><<<grid, 256, smem, st>>>(a, per_block);                            \
+    }                                                                                                             \
   } while (0)
   if (epl <= 1) NNCFB_AWQ_LAUNCH(1);
   else if (epl <= 2) NNCFB_AWQ_LAUNCH(2);
@@ -250,6 +310,15 @@ int launch_awq(const AwqArgs& a, cudaStream_t st) {
   awq_select_kernel<<<a.n_groups, 128, 0, st>>>(a);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
+}
+
+template <typename SrcT, int MODE>
+int launch_awq(const AwqArgs& a, cudaStream_t st) {
+  switch (awq_rows_at_a_time(a.gs, a.np)) {
+    case 4: return launch_awq_rc<SrcT, MODE, 4, 1>(a, st);
+    case 2: return launch_awq_rc<SrcT, MODE, 2, 2>(a, st);
+    default: return launch_awq_rc<SrcT, MODE, 1, 4>(a, st);
+  }
 }
 
 template <typename SrcT>
@@ -295,8 +364,7 @@ extern "C" int nncfb_awq_search(const void* weight, int32_t weight_dtype, int64_
   NNCFB_CHECK_ARG(n_groups <= 65535 && n_alpha <= 65535, NNCFB_E_TOO_LARGE, "nncfb_awq_search: grid too large");
   const int np = ((n_samples + 63) / 64) * 64;
   NNCFB_CHECK_ARG(np <= 256, NNCFB_E_TOO_LARGE, "nncfb_awq_search: %d samples exceed the maximum of 256", n_samples);
-  const int gs4 = (static_cast<int>(group_size) + 3) & ~3;
-  const size_t smem = (2 * static_cast<size_t>(gs4) * np + 9 * static_cast<size_t>(gs4)) * sizeof(float);
+  const size_t smem = awq_smem_bytes(static_cast<int>(group_size), np);
   NNCFB_CHECK_ARG(smem <= 200 * 1024, NNCFB_E_TOO_LARGE,
                   "nncfb_awq_search: group_size x samples = %lld x %d needs %zu bytes of shared memory (max 200 KiB)",
                   (long long)group_size, n_samples, smem);
