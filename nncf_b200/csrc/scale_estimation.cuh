@@ -86,8 +86,11 @@ constexpr int kSeRowsPerWarp = 8;
 // sequence (WC/scale_estimation.py:160-377): baseline quantisation, `initial_steps` re-estimates from the kept
 // scale, `scale_steps` re-estimates from shrunken baseline scales, keeping a candidate when its output error
 // on the calibration samples is not larger.
+#ifndef NNCFB_SE_MINBLOCKS
+#define NNCFB_SE_MINBLOCKS 2  // resident 256-thread blocks per SM that the register budget must allow
+#endif
 template <typename SrcT, int MODE, int EPL, int R, int MAXC>
-__global__ void __launch_bounds__(256) scale_estimation_kernel(const SEArgs a) {
+__global__ void __launch_bounds__(256, NNCFB_SE_MINBLOCKS) scale_estimation_kernel(const SEArgs a) {
   extern __shared__ __align__(16) float smem[];
   const int gs = a.gs, np = a.np;
   const int gs4 = (gs + 3) & ~3;               // projection walks the group four elements at a time
