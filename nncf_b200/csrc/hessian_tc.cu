@@ -27,6 +27,8 @@
 // kernel returns (the host reports NNCFB_E_TIMEOUT).  No multicast, no cluster, no peer memory.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "nncfb_common.cuh"
 
 namespace nncfb {
@@ -38,11 +40,11 @@ constexpr int kTileN = 256;
 constexpr int kBoxC = 64;    // channels per TMA box (128 bytes of bf16)
 constexpr int kBlockK = 64;  // tokens per pipeline stage
 constexpr int kStagesHessian = 4;
-constexpr int kStagesTrailing = 2;
+constexpr int kStagesTrailing = 4;
 constexpr int kMaxStages = 4;
 constexpr int kBoxBytes = kBoxC * kBlockK * 2;                           // 8192
 constexpr int kStageBytes = (kTileM / kBoxC + kTileN / kBoxC) * kBoxBytes;  // 49152
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;  // two accumulators of kTileN fp32 columns
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -176,43 +178,58 @@ __host__ __device__ inline void hessian_tile_decode(int idx, int tiles_m, int ti
 struct __align__(8) Control {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t acc_ready;
+  uint64_t acc_full[2];   // accumulator buffer b holds a finished tile
+  uint64_t acc_empty[2];  // the epilogue has read accumulator buffer b
   uint32_t tmem_base;
   uint32_t pad;
 };
 
-// TRAILING = false: D = H [C, C], upper-triangle tiles, K = tokens, both operands from `amap`.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent kernel: one CTA per SM walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The operand ring
+// runs on across tile boundaries and the accumulator is double-buffered in tensor memory (2 x 256 columns), so
+// the producer prefetches the next tile's operands and the MMA warp starts it while the epilogue warps are still
+// writing the previous tile back.
+// TRAILING = false: D = H [C, C], upper-triangle tiles in banded order, K = tokens, both operands from `amap`.
 // TRAILING = true:  D = W + c0 [rows, n_bound] with leading dimension ld, all tiles, twelve K segments of 64:
 //                   plane pair (pa, pb) x two halves of the 128-row block; A planes in `amap`, B planes in `bmap`,
 //                   each a 2-D tensor [3 * 128, extent] with plane p at rows [128 p, 128 p + 128).
 template <int kStages, bool TRAILING>
-__global__ void __launch_bounds__(192, TRAILING ? 2 : 1)
+__global__ void __launch_bounds__(192, 1)
 tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, float* __restrict__ H,
              int64_t ld, int64_t m_bound, int64_t n_bound, int64_t tokens, float alpha, float beta, uint32_t idesc,
-             int n_tiles_n, int* __restrict__ status) {
+             int n_tiles_n, int n_tiles, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte aligned operand ring (swizzle-128B atoms must start on 1 KiB), control block behind it
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Control* ctl = reinterpret_cast<Control*>(ring + kStages * kStageBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int mi = 0, nj = 0;
-  if constexpr (TRAILING) {
-    mi = blockIdx.x / n_tiles_n;
-    nj = blockIdx.x - mi * n_tiles_n;
-  } else {
-    // tile -> (mi, nj) with nj >= mi / 2 (tiles that touch the upper triangle), banded order
-    hessian_tile_decode(blockIdx.x, static_cast<int>((m_bound + kTileM - 1) / kTileM), n_tiles_n, mi, nj);
-  }
-  const int m0 = mi * kTileM, n0 = nj * kTileN;
+  const int tiles_m = static_cast<int>((m_bound + kTileM - 1) / kTileM);
   const int k_iters = TRAILING ? 12 : static_cast<int>((tokens + kBlockK - 1) / kBlockK);
+  auto tile_origin = [&](int tile, int& m0, int& n0) {
+    int mi, nj;
+    if constexpr (TRAILING) {
+      mi = tile / n_tiles_n;
+      nj = tile - mi * n_tiles_n;
+    } else {
+      hessian_tile_decode(tile, tiles_m, n_tiles_n, mi, nj);  // nj >= mi / 2: tiles that touch the upper triangle
+    }
+    m0 = mi * kTileM;
+    n0 = nj * kTileN;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
     }
-    mbar_init(&ctl->acc_ready, 1);
+    for (int bf = 0; bf < 2; ++bf) {
+      mbar_init(&ctl->acc_full[bf], 1);
+      mbar_init(&ctl->acc_empty[bf], 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -230,34 +247,37 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
     if (lane == 0) {
       // ---- TMA producer ------------------------------------------------------------------------
       bool ok = true;
-      int issued = 0;
-      for (int it = 0; it < k_iters && ok; ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
-        ok = mbar_wait(&ctl->empty[s], ph ^ 1);
-        if (!ok) {
-          atomicExch(status, 1);
-          break;
-        }
-        uint8_t* stage = ring + s * kStageBytes;
-        mbar_expect_tx(&ctl->full[s], kStageBytes);
-        int ka = it * kBlockK, kb = ka;
-        if constexpr (TRAILING) {
-          // plane pairs, smallest products first: (lo,hi) (hi,lo) (mid,mid) (mid,hi) (hi,mid) (hi,hi); hi = plane 0
-          const int combo = it >> 1, half = it & 1;
-          ka = static_cast<int>((0x001102u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
-          kb = static_cast<int>((0x010120u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
-        }
+      int g = 0;  // stages issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        int m0, n0;
+        tile_origin(tile, m0, n0);
+        for (int it = 0; it < k_iters; ++it, ++g) {
+          const int s = g % kStages;
+          if (!mbar_wait(&ctl->empty[s], ((g / kStages) & 1) ^ 1)) {
+            atomicExch(status, 1);
+            ok = false;
+            break;
+          }
+          uint8_t* stage = ring + s * kStageBytes;
+          mbar_expect_tx(&ctl->full[s], kStageBytes);
+          int ka = it * kBlockK, kb = ka;
+          if constexpr (TRAILING) {
+            // plane pairs, smallest products first: (lo,hi) (hi,lo) (mid,mid) (mid,hi) (hi,mid) (hi,hi); hi = plane 0
+            const int combo = it >> 1, half = it & 1;
+            ka = static_cast<int>((0x001102u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
+            kb = static_cast<int>((0x010120u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
+          }
 #pragma unroll
-        for (int b = 0; b < kTileM / kBoxC; ++b) tma_load_2d(stage + b * kBoxBytes, &amap, m0 + b * kBoxC, ka, &ctl->full[s]);
+          for (int b = 0; b < kTileM / kBoxC; ++b)
+            tma_load_2d(stage + b * kBoxBytes, &amap, m0 + b * kBoxC, ka, &ctl->full[s]);
 #pragma unroll
-        for (int b = 0; b < kTileN / kBoxC; ++b)
-          tma_load_2d(stage + (kTileM / kBoxC + b) * kBoxBytes, &bmap, n0 + b * kBoxC, kb, &ctl->full[s]);
-        ++issued;
+          for (int b = 0; b < kTileN / kBoxC; ++b)
+            tma_load_2d(stage + (kTileM / kBoxC + b) * kBoxBytes, &bmap, n0 + b * kBoxC, kb, &ctl->full[s]);
+        }
       }
       // do not leave while a copy into this CTA's shared memory may still be in flight: wait (bounded)
       // for the last copies issued to each stage
-      for (int it = max(0, issued - kStages); it < issued; ++it) {
+      for (int it = max(0, g - kStages); it < g; ++it) {
         if (!mbar_wait(&ctl->full[it % kStages], (it / kStages) & 1)) {
           atomicExch(status, 4);
           break;
@@ -268,52 +288,75 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
     if (lane == 0) {
       // ---- MMA issuer ----------------------------------------------------------------------------
       bool ok = true;
-      for (int it = 0; it < k_iters && ok; ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
-        ok = mbar_wait(&ctl->full[s], ph);
-        if (!ok) {
-          atomicExch(status, 2);
+      int g = 0, t = 0;  // stages consumed, tiles started
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+        const int bf = t & 1;
+        // the epilogue must have drained this accumulator buffer (two tiles ago); a fresh barrier passes
+        if (!mbar_wait(&ctl->acc_empty[bf], ((t >> 1) & 1) ^ 1)) {
+          atomicExch(status, 5);
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(ring + s * kStageBytes);
-        const uint32_t b_addr = a_addr + (kTileM / kBoxC) * kBoxBytes;
+        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(bf * kTileN);
+        for (int it = 0; it < k_iters; ++it, ++g) {
+          const int s = g % kStages;
+          if (!mbar_wait(&ctl->full[s], (g / kStages) & 1)) {
+            atomicExch(status, 2);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(ring + s * kStageBytes);
+          const uint32_t b_addr = a_addr + (kTileM / kBoxC) * kBoxBytes;
 #pragma unroll
-        for (int k = 0; k < kBlockK / 16; ++k) {
-          // 16 tokens per instruction = two groups of eight 128-byte rows = 2048 bytes
-          const uint64_t adesc = make_desc(a_addr + k * 2048);
-          const uint64_t bdesc = make_desc(b_addr + k * 2048);
-          umma_f16(tmem_base, adesc, bdesc, idesc, (it > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            // 16 tokens per instruction = two groups of eight 128-byte rows = 2048 bytes
+            const uint64_t adesc = make_desc(a_addr + k * 2048);
+            const uint64_t bdesc = make_desc(b_addr + k * 2048);
+            umma_f16(tmem_acc, adesc, bdesc, idesc, (it > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
         }
-        umma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
+        umma_commit(&ctl->acc_full[bf]);  // accumulator complete (or abandoned: the epilogue checks status)
       }
-      umma_commit(&ctl->acc_ready);   // accumulator complete (or abandoned: the epilogue checks status)
     }
   } else {
     // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ------------------------------
     const int q = warp & 3;
-    const int64_t r = static_cast<int64_t>(m0) + q * 32 + lane;
-    // While the MMAs run, pull this thread's row of the D tile (eight 128-byte lines) into L2: the
-    // read-modify-write below would otherwise wait for DRAM once per step.
-    if (r < m_bound) {
-      const float* drow = H + r * ld + n0;
+    // Pull this thread's row of a D tile (eight 128-byte lines) into L2 one tile ahead of its read-modify-write,
+    // which would otherwise wait for DRAM once per step.
+    auto prefetch_tile = [&](int tile) {
+      if (tile >= n_tiles) return;
+      int pm0, pn0;
+      tile_origin(tile, pm0, pn0);
+      const int64_t pr = static_cast<int64_t>(pm0) + q * 32 + lane;
+      if (pr < m_bound) {
+        const float* drow = H + pr * ld + pn0;
 #pragma unroll
-      for (int c = 0; c < kTileN; c += 32) {
-        if (n0 + c < n_bound) asm volatile("prefetch.global.L2 [%0];" ::"l"(drow + c));
+        for (int c = 0; c < kTileN; c += 32) {
+          if (pn0 + c < n_bound) asm volatile("prefetch.global.L2 [%0];" ::"l"(drow + c));
+        }
       }
-    }
-    const bool ok = mbar_wait(&ctl->acc_ready, 0);
-    if (!ok && lane == 0) atomicExch(status, 3);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const bool good = ok && (*reinterpret_cast<volatile int*>(status) == 0);
-    if (good) {
+    };
+    prefetch_tile(blockIdx.x);
+    int t = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+      const int bf = t & 1;
+      int m0, n0;
+      tile_origin(tile, m0, n0);
+      const int64_t r = static_cast<int64_t>(m0) + q * 32 + lane;
+      prefetch_tile(tile + gridDim.x);
+      const bool ok = mbar_wait(&ctl->acc_full[bf], (t >> 1) & 1);
+      if (!ok && lane == 0) atomicExch(status, 3);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!ok || *reinterpret_cast<volatile int*>(status) != 0) break;  // warp-uniform: some role gave up
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(bf * kTileN);
       // tcgen05.ld hands each lane one accumulator row, 32 columns (one 128-byte line of D) per step.  The
       // eight 16-byte loads of a step are issued together, before the first store, so that they overlap.
 #pragma unroll 1
       for (int c = 0; c < kTileN; c += 32) {
         uint32_t acc[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c), acc);
+        tmem_ld32(tmem_acc + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c), acc);
         if (r < m_bound) {
           float* hrow = H + r * ld + n0 + c;
           if (n0 + c + 31 < n_bound) {
@@ -335,6 +378,10 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
           }
         }
       }
+      // this warp has read its quarter of the buffer: hand it back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->acc_empty[bf]);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -441,8 +488,8 @@ int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t
   int* status = nullptr;
   if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
   NNCFB_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
-  kernel<<<n_tiles, 192, smem, st>>>(map, map, H, C, C, C, tokens, alpha, beta, instr_desc(dtype == NNCFB_BF16), tiles_n,
-                                     status);
+  kernel<<<std::min(n_tiles, sm_count()), 192, smem, st>>>(map, map, H, C, C, C, tokens, alpha, beta,
+                                                            instr_desc(dtype == NNCFB_BF16), tiles_n, n_tiles, status);
   NNCFB_CUDA(cudaGetLastError());
   const dim3 mgrid(static_cast<unsigned>((C + 31) / 32), static_cast<unsigned>((C + 31) / 32));
   mirror_upper_tc_kernel<<<mgrid, 256, 0, st>>>(H, C);
@@ -502,8 +549,11 @@ int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv
   NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   int* status = nullptr;
   if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
+  // One CTA per tile here: this kernel shares the GPU with the next block's sweep (whose CTAs fill the shared
+  // memory of the SMs they sit on), so a fixed set of persistent CTAs would leave tiles waiting behind it;
+  // with a CTA per tile the hardware hands tiles to whichever SMs are free.
   kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, w_c, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
-                                               status);
+                                               tiles_m * tiles_n, status);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
 }
