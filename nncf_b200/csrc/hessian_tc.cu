@@ -12,16 +12,18 @@
 // transposed copy of X is ever made.  A TMA box of 64 channels x 64 tokens with 128-byte swizzle is
 // exactly one canonical MN-major swizzle-128B operand atom column (8 token rows per 1024-byte atom).
 //
-// One CTA computes one 128 x 256 tile of the upper triangle of H over all tokens:
-//   warp 0        TMA producer (one elected lane), 4-stage ring, mbarrier expect-tx
+// A CTA computes 128 x 256 tiles of the upper triangle of H over all tokens, one after the other (one
+// persistent CTA per SM; the accumulator is double-buffered in tensor memory so that a tile's epilogue
+// overlaps the next tile's MMAs):
+//   warp 0        TMA producer (one elected lane), 4-stage ring running across tiles, mbarrier expect-tx
 //   warp 1        tensor-memory allocation, MMA issue (one elected lane), tcgen05.commit
 //   warps 2..5    epilogue: tcgen05.ld of the fp32 accumulators, H = alpha*H + beta*acc
 // The same kernel, with two tensor maps and twelve K segments, is the lazy-batch trailing update of the
 // GPTQ sweep, W[:, i2:] -= Err_blk @ Hinv[i1:i2, i2:] (WC/gptq.py:361-363): both fp32 operands are split into
 // three bf16 planes (hi + mid + lo = the fp32 value to 2^-27), stored with the block's 128 rows of K as the
 // slow axis, and six plane products (everything down to 2^-24 relative) are accumulated in fp32 in tensor
-// memory, smallest terms first.  That update is bound by the read-modify-write of W, so its variant keeps
-// two stages per CTA and two CTAs per SM: one CTA's epilogue overlaps the other's loads and MMAs.
+// memory, smallest terms first.  That update is bound by the read-modify-write of W; it is launched with one
+// CTA per tile because it shares the GPU with the next block's sweep kernel.
 // Every wait is bounded: after kSpinLimit polls a role records an error code in a global flag
 // and leaves; the other roles then time out the same way, tensor memory is released and the
 // kernel returns (the host reports NNCFB_E_TIMEOUT).  No multicast, no cluster, no peer memory.
