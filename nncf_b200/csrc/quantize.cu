@@ -146,7 +146,14 @@ int launch_general(const nncfb_quantize_args* p, cudaStream_t st) {
 
   const bool aligned = aligned16(p->weight) && aligned16(p->codes_out) && aligned16(p->values_out) &&
                        aligned16(p->dq_out);
-  const QuantPath path = choose_path(p->group_size, p->inner, aligned);
+  QuantPath path = choose_path(p->group_size, p->inner, aligned);
+  // Storage outputs of a column-group layout with tall groups (per-channel weights stored [in, out]) and whole
+  // 16-byte column vectors: the tiled kernel.  The thread-per-column kernel has too few threads there (one per
+  // column pair) and walks the group serially; for short groups it has plenty and is the faster of the two.
+  if (path == QuantPath::kColumn && p->group_size >= 512 && p->inner % 8 == 0 && aligned && !p->pre_scale && !p->values_out && !p->dq_out &&
+      !p->sqerr_out && (p->codes_format == NNCFB_CODES_NONE || p->codes_out)) {
+    path = QuantPath::kColumnTile;
+  }
   switch (p->weight_dtype) {
 #ifndef NNCFB_ONLY_BF16
     case NNCFB_F32: return launch_quantize_f32(a, p->mode, path, st);

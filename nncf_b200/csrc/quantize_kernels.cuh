@@ -583,4 +583,113 @@ __global__ void __launch_bounds__(256) quant_column_kernel(const QArgs a) {
   }
 }
 
+// =====================================================================================================
+// Column groups, storage path (codes + parameters, computed from the weight): inner % 8 == 0.
+// A 256-thread block owns a tile of 64 columns x one group: 8 column lanes of one 16-byte vector (8 columns)
+// by 32 row lanes, so a warp reads four 128-byte row segments per load.  Each thread keeps its first K vectors
+// in registers (groups of up to 32 * K rows are read from HBM once; longer ones - per-channel weights stored
+// [in, out] - are read a second time for the encoding pass).  Per-column min / max are combined across the row
+// lanes in shared memory; the per-column parameters come back through shared memory.
+// =====================================================================================================
+template <typename SrcT, int MODE>
+__global__ void __launch_bounds__(256) quant_column_tile_kernel(const QArgs a) {
+  constexpr int K = WideCache<SrcT>::K;
+  __shared__ float red_mn[32][64], red_mx[32][64];
+  __shared__ float par_scale[64], par_zp[64];
+  const SrcT* __restrict__ src = reinterpret_cast<const SrcT*>(a.weight);
+  const int64_t gs = a.group_size, inner = a.inner, G = a.groups_per_row;
+  const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const int64_t col_blocks = (inner + 63) / 64;
+  const int64_t n_tiles = a.n_groups / inner;  // outer * G
+  for (int64_t blk = blockIdx.x; blk < n_tiles * col_blocks; blk += gridDim.x) {
+    const int64_t tile = blk / col_blocks, cb = blk - tile * col_blocks;
+    const int64_t c0 = cb * 64 + cl * 8;
+    const bool active = c0 < inner;  // whole vector: inner is a multiple of 8
+    const int64_t o = tile / G, gi = tile - o * G;
+    const int64_t base = (o * G * gs + gi * gs) * inner + c0;  // element (o, gi * gs, c0)
+
+    float mn[8], mx[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      mn[j] = __uint_as_float(0x7f800000u);
+      mx[j] = __uint_as_float(0xff800000u);
+    }
+    auto fold = [&](const Raw8<SrcT>& raw) {
+      float v[8];
+      unpack8(raw, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        mn[j] = fminf(mn[j], v[j]);
+        mx[j] = fmaxf(mx[j], v[j]);
+      }
+    };
+    Raw8<SrcT> cache[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int64_t r = rl + 32 * k;
+      if (active && r < gs) {
+        cache[k] = load_raw8<SrcT>(src + base + r * inner);
+        fold(cache[k]);
+      }
+    }
+    for (int64_t r = rl + 32 * K; active && r < gs; r += 32) fold(load_raw8<SrcT>(src + base + r * inner));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      red_mn[rl][cl * 8 + j] = mn[j];
+      red_mx[rl][cl * 8 + j] = mx[j];
+    }
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      const int col = threadIdx.x;
+      float m = red_mn[0][col], M = red_mx[0][col];
+#pragma unroll
+      for (int q = 1; q < 32; ++q) {
+        m = fminf(m, red_mn[q][col]);
+        M = fmaxf(M, red_mx[q][col]);
+      }
+      if (cb * 64 + col < inner) {
+        Codec<MODE> c;
+        c.from_stats(m, M);
+        store_group_params<MODE>(a, tile * inner + cb * 64 + col, c);
+        par_scale[col] = c.scale;
+        par_zp[col] = c.zp;
+      }
+    }
+    __syncthreads();
+    if (active && a.codes_format != NNCFB_CODES_NONE) {
+      Codec<MODE> cd[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cd[j].from_given(par_scale[cl * 8 + j], par_zp[cl * 8 + j]);
+      auto encode = [&](const Raw8<SrcT>& raw, int64_t e) {
+        float v[8];
+        unpack8(raw, v);
+        uint32_t code[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float u;
+          code[j] = cd[j].encode(v[j], u);
+        }
+        if (a.codes_format == NNCFB_CODES_NIBBLE) {
+          uint32_t w = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w |= Codec<MODE>::nibble(code[j]) << (4 * j);
+          *reinterpret_cast<uint32_t*>(a.codes + (e >> 1)) = w;
+        } else {
+          uint2 w;
+          w.x = (code[0] & 255u) | ((code[1] & 255u) << 8) | ((code[2] & 255u) << 16) | ((code[3] & 255u) << 24);
+          w.y = (code[4] & 255u) | ((code[5] & 255u) << 8) | ((code[6] & 255u) << 16) | ((code[7] & 255u) << 24);
+          *reinterpret_cast<uint2*>(a.codes + e) = w;
+        }
+      };
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int64_t r = rl + 32 * k;
+        if (r < gs) encode(cache[k], base + r * inner);
+      }
+      for (int64_t r = rl + 32 * K; r < gs; r += 32) encode(load_raw8<SrcT>(src + base + r * inner), base + r * inner);
+    }
+    __syncthreads();  // shared arrays are reused by the next tile
+  }
+}
+
 }  // namespace nncfb

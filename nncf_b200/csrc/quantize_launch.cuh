@@ -10,7 +10,7 @@
 namespace nncfb {
 
 // Which kernel serves a validated request.
-enum class QuantPath { kSubwarp, kWide, kGeneric, kColumn };
+enum class QuantPath { kSubwarp, kWide, kGeneric, kColumn, kColumnTile };
 
 inline QuantPath choose_path(int64_t group_size, int64_t inner, bool aligned) {
   if (inner > 1) return QuantPath::kColumn;
@@ -53,6 +53,12 @@ int launch_quantize_mode(const QArgs& a, QuantPath path, cudaStream_t stream) {
       const int64_t blocks_needed = (a.n_groups + (kThreads / 32) - 1) / (kThreads / 32);
       const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks_needed, static_cast<int64_t>(sms) * 8)));
       quant_generic_kernel<SrcT, MODE><<<grid, kThreads, 0, stream>>>(a);
+      break;
+    }
+    case QuantPath::kColumnTile: {
+      const int64_t blocks_needed = (a.n_groups / a.inner) * ((a.inner + 63) / 64);
+      const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks_needed, static_cast<int64_t>(sms) * 8)));
+      quant_column_tile_kernel<SrcT, MODE><<<grid, kThreads, 0, stream>>>(a);
       break;
     }
     case QuantPath::kColumn: {

@@ -175,6 +175,39 @@ def test_strided_and_stacked_layouts_match_oracle(shape, axis, gs, mode):
         _eq(packed.packed, ref_packed, "packed")
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("mode", ["int4_sym", "int4_asym", "int8_sym", "int8_asym", "nf4", "mxfp4"])
+@pytest.mark.parametrize("shape,axis,gs", [((1024, 64), 0, -1), ((2, 1536, 40), 1, 512), ((640, 16), 0, 640),
+                                           ((3, 520, 72), 1, -1)])
+def test_tall_column_groups_stored_form_matches_oracle(shape, axis, gs, mode, dtype):
+    """Weights stored [in, out] (or stacked [E, in, out]) with tall groups - per-channel backup precision or a
+    group size of 512 and more - take the tiled column kernel: packed codes and every parameter output
+    against the oracle, for rows beyond the register cache (more than 32 * 8 rows) and ragged column tiles."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import weight_lowering as wl
+
+    gen = torch.Generator().manual_seed(sum(shape) + len(mode))
+    w = (torch.randn(*shape, generator=gen) * 0.05).to(TORCH_DTYPE[dtype])
+    w_np = w.numpy() if dtype == "f16" else w.float().numpy()
+    ref = O.compress_weight(w_np, axis, mode, gs)
+    cfg = _cfg(mode, gs)
+    st = wl.compress_weight(w.cuda(), axis, cfg, pack=True)
+    _eq(st.scale, ref.scale, "scale")
+    if cfg.is_asym_mode:
+        _eq(st.zero_point, ref.zero_point, "zp")
+    if cfg.is_integer and cfg.num_bits == 4:
+        _eq(st.packed, O.pack_int4(ref.tensor) if mode == "int4_sym" else O.pack_uint4(ref.tensor), "packed")
+    elif cfg.is_integer:
+        _eq(st.packed, ref.tensor, "byte codes")
+    else:
+        codes = O.nibble_code_nf4(ref.tensor) if mode == "nf4" else O.nibble_code_e2m1(ref.tensor)
+        _eq(st.packed, O.pack_uint4(codes), "packed float codes")
+    _eq(st.scale_f16, ref.scale.astype(np.float16), "fp16 scale")
+    if mode == "mxfp4":
+        _eq(st.scale_e8m0, O.e8m0_code(ref.scale), "e8m0")
+
+
 def test_division_selftest_has_no_mismatch():
     from nncf_b200 import _lib
 
