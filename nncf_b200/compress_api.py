@@ -57,6 +57,12 @@ class Dataset:
             yield self._transform(item) if self._transform else item
 
 
+# Model-level GPTQ replays repeated blocks (decoder layers) on cached inputs instead of re-running the model's
+# prefix for every layer.  False restores the plain form (one partial forward of the whole model per layer and
+# calibration item), which computes the same thing and is kept for models the block detection does not fit.
+LAYERWISE_REPLAY = True
+
+
 def _run(model: nn.Module, item: Any) -> None:
     if isinstance(item, dict):
         model(**item)
@@ -461,10 +467,12 @@ def compress_weights(
         g = GPTQ(adv.gptq_params.damp_percent, adv.gptq_params.block_size, adv.gptq_params.subset_size,
                  scale_estimation=cfg["scale_estimation"])
         targets = [p for p in active if not p.is_embedding and p.compression_config.mode not in INT8_MODES]
-        # layers fed by the very same tensor (q/k/v, gate/up) share one Hessian and one factorisation
-        for group in _same_input_groups(model, sample, targets):
-            H, layer_stat = _layer_hessian(model, group[0].module, items[: adv.gptq_params.subset_size], g,
-                                           want_statistics=cfg["scale_estimation"])
+        cal = items[: adv.gptq_params.subset_size]
+
+        def quantise_group(group, runners):
+            """One Hessian for layers fed by the very same tensor (q/k/v, gate/up), one factorisation, then
+            every layer of the group; weights are replaced only after the whole group saw the same inputs."""
+            H, layer_stat = _layer_hessian(runners, group[0].module, g, want_statistics=cfg["scale_estimation"])
             hinv = None
             for p in group:
                 w = p.weight.data.float().contiguous()
@@ -473,9 +481,29 @@ def compress_weights(
                 q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat)
                 precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
                 p._gptq_weight = q
-            for p in group:  # weights are replaced only after the whole group saw the same inputs
+            for p in group:
                 p.module.weight.data = p._gptq_weight.to(p.weight.dtype)
                 del p._gptq_weight
+
+        groups = _same_input_groups(model, sample, targets)
+        blocks = _decoder_blocks(model, targets) if LAYERWISE_REPLAY else None
+        done: set = set()
+        if blocks is not None:
+            # Layer-wise engine (the role of src/nncf/quantization/algorithms/layerwise/engine.py:33-198): the
+            # inputs of the first repeated block are captured once; each block is then replayed on its own on the
+            # outputs of the already-quantised block before it, instead of re-running the whole prefix of the
+            # model for every layer.
+            replay = _BlockReplay(model, blocks, cal)
+            for bi, block in enumerate(blocks):
+                inside = {id(m) for m in block.modules()}
+                for group in groups:
+                    if id(group[0].module) in inside:
+                        quantise_group(group, replay.runners(bi))
+                        done.update(p.weight_name for p in group)
+                replay.advance(bi)
+        for group in groups:  # layers outside the repeated blocks (or models without such blocks)
+            if group[0].weight_name not in done:
+                quantise_group(group, [lambda item=item: _run(model, item) for item in cal])
     elif cfg["scale_estimation"]:
         se = adv.scale_estimation_params
         algo = ScaleEstimation(se.subset_size, se.initial_steps, se.scale_steps, se.weight_penalty)
@@ -517,13 +545,14 @@ def _same_input_groups(model: nn.Module, sample: Any, targets: list) -> list:
     return groups
 
 
-def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ, want_statistics: bool = False):
+def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: bool = False):
     """Hessian of one Linear's input over the calibration items, with every previously processed layer already
     holding its quantised weight (the semantics of the reference's layer-wise engine,
-    src/nncf/quantization/algorithms/layerwise/openvino_iterator.py:183-231).  Activations are consumed as
-    they appear; nothing is stored but, when the sweep refines its scales with ScaleEstimation, the per-sample
-    channel means and shapes (what GPTQ.activations_to_wc_statistics would reduce from stored inputs).
-    Returns (H, statistics or None)."""
+    src/nncf/quantization/algorithms/layerwise/openvino_iterator.py:183-231).  ``runners``: one callable per
+    calibration item that runs the model (or the block that contains ``module``) on it.  Activations are
+    consumed as they appear; nothing is stored but, when the sweep refines its scales with ScaleEstimation, the
+    per-sample channel means and shapes (what GPTQ.activations_to_wc_statistics would reduce from stored
+    inputs).  Returns (H, statistics or None)."""
     C = module.in_features
     stat = WCTensorStatistic() if want_statistics else None
     H = torch.zeros(C, C, dtype=torch.float32, device=module.weight.device)
@@ -545,14 +574,87 @@ def _layer_hessian(model: nn.Module, module: nn.Linear, items: list, g: GPTQ, wa
     h = module.register_forward_pre_hook(hook)
     try:
         with torch.no_grad():
-            for item in items:
+            for run in runners:
                 try:
-                    _run(model, item)
+                    run()
                 except _Stop:
                     pass
     finally:
         h.remove()
     return H, stat
+
+
+def _decoder_blocks(model: nn.Module, targets: list) -> Optional[list]:
+    """The repeated blocks of the model: the nn.ModuleList of callable modules that holds the most target
+    layers (decoder layers of a transformer).  None when there is no such list."""
+    best = None
+    target_ids = {id(p.module) for p in targets}
+    for mod in model.modules():
+        if not isinstance(mod, nn.ModuleList) or len(mod) < 2:
+            continue
+        if any(type(b).forward is nn.Module.forward for b in mod):  # containers without a forward of their own
+            continue
+        n = sum(1 for b in mod for m in b.modules() if id(m) in target_ids)
+        if n and (best is None or n > best[0]):
+            best = (n, list(mod))
+    return best[1] if best else None
+
+
+class _BlockReplay:
+    """Inputs of each repeated block for every calibration item, so that a block can be run on its own.
+
+    One forward pass per item records the positional and keyword arguments each block is called with.  The hidden
+    state (first positional argument) is kept for the first block only; ``advance`` computes the next block's
+    from the current block's output, i.e. through the weights the block holds at that moment.  Objects that
+    accumulate state across calls (key / value caches) are not replayed: they are replaced by None."""
+
+    def __init__(self, model: nn.Module, blocks: list, items: list):
+        self.blocks = blocks
+        self.calls: list = [[] for _ in blocks]   # per block, per item: (other positional args, kwargs, positional?)
+        first_hidden: list = []
+        handles = []
+
+        def make(bi):
+            def hook(mod, args, kwargs):
+                if bi == 0:
+                    first_hidden.append((args[0] if args else kwargs["hidden_states"]).detach())
+                kw = {k: (None if _is_stateful_cache(v) else v) for k, v in kwargs.items() if k != "hidden_states"}
+                if "use_cache" in kw:
+                    kw["use_cache"] = False
+                self.calls[bi].append((tuple(args[1:]) if args else (), kw, bool(args)))
+            return hook
+
+        for bi, b in enumerate(blocks):
+            handles.append(b.register_forward_pre_hook(make(bi), with_kwargs=True))
+        try:
+            with torch.no_grad():
+                for item in items:
+                    _run(model, item)
+        finally:
+            for h in handles:
+                h.remove()
+        self.hidden: list = first_hidden          # per item: input of the current block
+
+    def _call(self, bi: int, k: int):
+        rest, kw, positional = self.calls[bi][k]
+        if positional:
+            return self.blocks[bi](self.hidden[k], *rest, **kw)
+        return self.blocks[bi](hidden_states=self.hidden[k], **kw)
+
+    def runners(self, bi: int) -> list:
+        return [lambda k=k: self._call(bi, k) for k in range(len(self.hidden))]
+
+    def advance(self, bi: int) -> None:
+        """Replace the stored hidden states by block ``bi``'s outputs (the inputs of block ``bi + 1``)."""
+        with torch.no_grad():
+            for k in range(len(self.hidden)):
+                out = self._call(bi, k)
+                self.hidden[k] = (out[0] if isinstance(out, (tuple, list)) else out).detach()
+
+
+def _is_stateful_cache(v: Any) -> bool:
+    return v is not None and not isinstance(v, torch.Tensor) and (
+        hasattr(v, "get_seq_length") or type(v).__name__.endswith("Cache"))
 
 
 def _make_decompressor(p: WeightCompressionParameters, item) -> nn.Module:

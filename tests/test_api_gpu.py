@@ -155,6 +155,40 @@ def test_gptq_with_scale_estimation_model_level():
     assert errs[True] < errs[False] * 1.5, errs
 
 
+def test_gptq_block_replay_equals_full_prefix_runs_on_hf_llama(monkeypatch):
+    """Model-level GPTQ on a Hugging Face Llama: replaying each decoder layer on cached inputs (through the
+    already-quantised layers before it) gives the same compressed model as re-running the whole prefix of the
+    model for every layer, and the key / value cache the model passes to its layers is not replayed."""
+    transformers = pytest.importorskip("transformers")
+    import nncf_b200 as nb
+    from nncf_b200 import compress_api
+
+    cfg = transformers.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+    gen = torch.Generator().manual_seed(0)
+    ids = [torch.randint(0, 96, (1, 24), generator=gen).cuda() for _ in range(6)]
+    states = {}
+    for replay in (True, False):
+        monkeypatch.setattr(compress_api, "LAYERWISE_REPLAY", replay)
+        torch.manual_seed(0)
+        model = transformers.LlamaForCausalLM(cfg).cuda().eval()
+        blocks = compress_api._decoder_blocks(model, compress_api.get_weight_compression_parameters(model, None, ids[0]))
+        assert blocks is not None and len(blocks) == 3
+        model = nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_SYM, group_size=32, dataset=nb.Dataset(ids),
+                                    gptq=True, advanced_parameters=nb.AdvancedCompressionParameters(
+                                        gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.1, subset_size=6)))
+        states[replay] = {k: v.clone() for k, v in model.state_dict().items()}
+        with torch.no_grad():
+            states[replay]["__logits"] = model(ids[0]).logits
+    assert states[True].keys() == states[False].keys()
+    differing = [k for k in states[True] if not torch.equal(states[True][k], states[False][k])]
+    # identical computations; allow for a non-deterministic attention kernel changing a few codes
+    frac = sum(states[True][k].numel() for k in differing) / sum(v.numel() for v in states[True].values())
+    assert frac < 0.05, differing
+    rel = (states[True]["__logits"] - states[False]["__logits"]).norm() / states[False]["__logits"].norm()
+    assert rel < 0.05
+
+
 @pytest.mark.parametrize("mode,gs", [("int4_sym", 128), ("int4_asym", 64), ("int8_asym", -1), ("int8_sym", -1),
                                      ("nf4", 128), ("mxfp4", 32), ("fp8_e4m3", 128), ("mxfp8_e4m3", 32)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
