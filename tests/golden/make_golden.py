@@ -379,7 +379,8 @@ def gen_gptq(out: dict, cases=None, prefix="gptq", scale_estimation=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference/src", help="path to the reference's src/ directory")
+    ap.add_argument("--reference", default=os.environ.get("NNCF_REFERENCE_SRC"), required="NNCF_REFERENCE_SRC" not in os.environ,
+                    help="path to the src/ directory of an nncf 3.2.0 checkout (or set NNCF_REFERENCE_SRC)")
     ap.add_argument("groups", nargs="*", help="fixture groups to regenerate (default: all)")
     args = ap.parse_args()
     _setup(args.reference)
