@@ -259,6 +259,45 @@ def run_gptq_workload(args, device):
     print(json.dumps(out), flush=True)
 
 
+def run_api_workload(args, device):
+    """The model-level API (`nncf_b200.compress_weights`) on a random-init Llama of 1.1 B parameters
+    (hidden 2048, 16 layers, bf16; Hugging Face `LlamaForCausalLM`), 16 calibration sequences of 512 tokens:
+    wall time of the whole call - tracing, statistics, algorithms, kernels, installing the decompressors."""
+    import transformers
+
+    import nncf_b200 as nb
+
+    cfg = transformers.LlamaConfig(vocab_size=32000, hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
+                                   num_attention_heads=32, num_key_value_heads=8, max_position_embeddings=2048)
+    gen = torch.Generator().manual_seed(0)
+    ids = [torch.randint(0, 32000, (1, 512), generator=gen).to(device) for _ in range(16)]
+    cases = (("int4_sym_data_free", {}), ("awq_scale_estimation", {"awq": True, "scale_estimation": True}),
+             ("gptq", {"gptq": True}), ("gptq_scale_estimation", {"gptq": True, "scale_estimation": True}))
+    seconds = {}
+    n_params = 0
+    for name, kw in cases:
+        torch.manual_seed(0)
+        with torch.device(device):
+            model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+        n_params = sum(p.numel() for p in model.parameters())
+        if kw:
+            kw = dict(kw, dataset=nb.Dataset(ids))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        model = nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_SYM, group_size=128, **kw)
+        torch.cuda.synchronize()
+        seconds[name] = round(time.perf_counter() - t0, 3)
+        with torch.no_grad():
+            assert bool(torch.isfinite(model(ids[0]).logits).all()), name
+        del model
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "compress_weights_api_seconds", "unit": "s", "higher_is_better": False, "n_gpus": 1,
+                      "data": "synthetic", "dtype": "bf16 weights",
+                      "config": {"workload": f"LlamaForCausalLM, {n_params / 1e9:.2f} B parameters, random init, INT4_SYM "
+                                             "g128, 16 x 512 calibration tokens"},
+                      "seconds": seconds, "value": seconds["int4_sym_data_free"]}), flush=True)
+
+
 def run_moe_workload(args, device, rank, world, dist):
     """BASELINE.json config 5: NF4 (g128) or MXFP4 (E2M1 values, E8M0 scale per 32) data-free compression of a
     Mixtral-8x7B-shaped expert stack (per layer 8 experts x (w1, w3: 14336 x 4096; w2: 4096 x 14336), bf16
@@ -374,7 +413,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a graph")
-    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "data_aware", "moe"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "data_aware", "moe", "api"],
                     help="compress: the headline metric (default); gptq: the secondary GPTQ metric")
     ap.add_argument("--mode", default="nf4", choices=["nf4", "mxfp4", "fp4"], help="mode of the moe workload")
     ap.add_argument("--layers", type=int, default=4, help="layers of the moe workload (32 = the full 90 GB stack)")
@@ -405,9 +444,10 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    if args.workload in ("gptq", "data_aware"):
+    if args.workload in ("gptq", "data_aware", "api"):
         if rank == 0:
-            (run_gptq_workload if args.workload == "gptq" else run_data_aware_workload)(args, device)
+            {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload}[args.workload](
+                args, device)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
