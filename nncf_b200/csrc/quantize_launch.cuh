@@ -118,6 +118,10 @@ inline FastClass fast_class(const nncfb_quantize_args& p) {
   return none;
 }
 
+// Groups in flight per sub-warp: an fp32 vector of 8 elements takes eight registers instead of four, and four
+// groups of them spill under the 64-register budget of four resident blocks per SM.
+constexpr int rows_in_flight(size_t elem_size) { return elem_size == 4 ? NNCFB_ROWS_U / 2 : NNCFB_ROWS_U; }
+
 template <typename SrcT, int MODE>
 int launch_fast_mode(const FastBatch& b, FastClass cls, cudaStream_t stream) {
   const int sms = sm_count();
@@ -128,7 +132,7 @@ int launch_fast_mode(const FastBatch& b, FastClass cls, cudaStream_t stream) {
     }
   }
   if (cls.kind == 1) {
-    constexpr int U = NNCFB_ROWS_U;
+    constexpr int U = rows_in_flight(sizeof(SrcT));
     const int grid = static_cast<int>(std::max<int64_t>(
         1, std::min<int64_t>((b.iter_start[b.n_tensors] + 7) / 8, static_cast<int64_t>(sms) * NNCFB_ROWS_MINBLOCKS)));
     if (cls.group == 128) {
@@ -175,7 +179,7 @@ int launch_fast_t(const FastBatch& b, int mode, FastClass cls, cudaStream_t stre
 inline int64_t fast_iterations(const FastClass& cls, int64_t n_groups, size_t elem_size) {
   if (cls.kind == 1) {
     const int L = cls.group == 128 ? 8 : (cls.group == 64 ? 4 : 2);
-    const int64_t per_iter = (32 / L) * NNCFB_ROWS_U;  // GPW * U
+    const int64_t per_iter = (32 / L) * rows_in_flight(elem_size);  // GPW * U
     return (n_groups + per_iter - 1) / per_iter;
   }
   const int K = elem_size == 4 ? 4 : 8;
