@@ -267,3 +267,39 @@ def test_stacked_expert_weights_follow_the_per_expert_loop():
         qe, se, _ = g._quantize_weights(_wp("int4_sym", 64), H[e].clone(), w[e].clone().contiguous())
         assert torch.equal(qe, q[e]) and torch.equal(se, s[e])
     assert not torch.equal(q[0], q[1])
+
+
+@pytest.mark.parametrize("rows,cols,gs,block,mode", [
+    (8, 256, 128, 128, "int4_sym"),       # smallest shape that takes the tensor-core trailing update
+    (136, 384, 64, 128, "int4_asym"),     # rows % 128 != 0, three blocks
+    (130, 384, 128, 128, "int4_sym"),     # rows % 8 != 0: CUDA-core trailing update
+    (64, 320, 64, 128, "int4_sym"),       # last block partial (64 columns)
+    (48, 258, 129, 128, "int4_sym"),      # cols % 4 != 0: scalar prologue, groups straddling blocks
+    (40, 512, 256, 128, "int4_asym"),     # groups longer than a block (no look-ahead overlap)
+    (72, 384, 32, 64, "int4_sym"),        # block size below 128
+    (24, 256, -1, 128, "int8_sym"),       # per-channel
+])
+def test_gptq_odd_shapes_match_oracle(rows, cols, gs, block, mode):
+    """Shapes around every branch of the sweep (vector / scalar prologue, tensor-core / CUDA-core trailing
+    update, look-ahead on and off, partial blocks) against the CPU oracle run from the same inverse factor."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200.gptq import GPTQ
+
+    gen = torch.Generator().manual_seed(rows * 1000 + cols)
+    w = torch.randn(rows, cols, generator=gen) * 0.05
+    x = torch.randn(4 * cols, cols, generator=gen)
+    x[:, :4] *= 6.0
+    H = (2.0 / 8) * (x.double().T @ x.double()).float()
+    g = GPTQ(0.05, block, 8)
+    hinv = g.prepare_hessian_inverse(H.clone().cuda(), w.clone().cuda())
+    q, s, z = g._quantize_weights(_wp(mode, gs), H.clone().cuda(), w.clone().cuda(), hinv=hinv)
+    Q, S, Z = O.gptq_quantize(w.numpy().copy(), hinv.cpu().numpy(), mode, gs, block)
+    assert tuple(q.shape) == Q.shape and tuple(s.shape) == S.shape
+    flipped = np.mean(np.abs(q.cpu().numpy() - Q) > 1e-6)
+    assert flipped < 0.02, flipped
+    assert np.mean(np.abs(s.cpu().numpy() - S) > 2e-3 * np.abs(S)) < 0.02
+    if Z is not None:
+        assert np.mean(z.cpu().numpy() != Z) < 0.05
+    else:
+        assert z is None
