@@ -99,6 +99,53 @@ def test_scale_estimation_llama_sized_matches_oracle(dtype):
         assert np.linalg.norm(a - b) / np.linalg.norm(b) <= 1e-3
 
 
+@pytest.mark.parametrize("rows,cols,gs,n", [(13, 256, 128, 64), (5, 512, 256, 40), (70, 256, 64, 70), (9, 256, 128, 150),
+                                            (33, 128, 32, 1), (66, 1024, 512, 20)])
+@pytest.mark.parametrize("mode", ["int4_asym", "int4_sym"])
+def test_scale_estimation_row_and_sample_tilings_match_oracle(rows, cols, gs, n, mode):
+    """Row counts that are not multiples of the four rows a warp handles together, group sizes on both sides of
+    the 128 that the 4-row tiling takes, and sample counts that need one, two and four 64-sample accumulator
+    chunks (each combination is a different instantiation of the kernel)."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200.scale_estimation import ScaleEstimation
+
+    gen = torch.Generator().manual_seed(rows + cols + n)
+    w = (torch.randn(rows, cols, generator=gen) * 0.02).to(torch.bfloat16)
+    means = [(torch.randn(cols, generator=gen) * (1 + 9 * (torch.rand(cols, generator=gen) < 0.03))).float() for _ in range(n)]
+    st = _stats([m.numpy() for m in means], (1, 64, cols))
+    scale, zp = ScaleEstimation.calculate_quantization_params(st, w.cuda(), (1,), _cfg(mode, gs), -1, 256, 5, 5)
+    s, X = O.process_stats([m.numpy() for m in means], [(1, 64, cols)] * n, 256)
+    ref_s, ref_z = O.scale_estimation(s, X, w.float().numpy(), 1, mode, gs, 5, 5)
+    got = scale.cpu().numpy()
+    assert got.shape == ref_s.shape
+    rel = np.abs(got - ref_s) / np.abs(ref_s)
+    assert np.mean(rel > 1e-5) <= 0.02, float(np.mean(rel > 1e-5))
+    if ref_z is not None:
+        np.testing.assert_array_equal(zp.cpu().numpy(), ref_z)
+
+
+@pytest.mark.parametrize("n,gs", [(70, 128), (150, 64), (20, 256)])
+def test_awq_sample_and_group_tilings_match_oracle(n, gs):
+    """AWQ alpha search with sample counts / group sizes that take the 2-row and 1-row variants of the kernel."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200.awq import AWQ, make_wp
+
+    gen = torch.Generator().manual_seed(n + gs)
+    out, hid = 37, 512
+    w = (torch.randn(out, hid, generator=gen) * 0.05)
+    means = [(torch.randn(hid, generator=gen) * (1 + 15 * (torch.arange(hid) % 97 == 3))).float() for _ in range(n)]
+    st = _stats([m.numpy() for m in means], (1, 16, hid))
+    algo = AWQ(subset_size=256, percent_to_apply=0.01, steps=25)
+    got = algo._data_aware_step(make_wp(_cfg("int4_asym", gs)), w.cuda(), st, -1).cpu().numpy()
+    s, X = O.process_stats([m.numpy() for m in means], [(1, 16, hid)] * n, 256)
+    ref = O.awq_data_aware_scale(s, X, w.numpy(), 1, "int4_asym", gs, 0.01, 0.0, 1.0, 25)
+    np.testing.assert_array_equal(got == 1.0, ref == 1.0)
+    np.testing.assert_allclose(got, ref, rtol=2e-5)
+    assert (ref != 1.0).any()
+
+
 @pytest.mark.parametrize("case", AWQ_CASES, ids=[c[0] for c in AWQ_CASES])
 def test_awq_matches_reference_golden(case):
     from nncf_b200.awq import AWQ, make_wp

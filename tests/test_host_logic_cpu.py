@@ -86,3 +86,76 @@ def test_bind_host_thread_near_uses_nvml_cpu_set(monkeypatch):
         assert os.sched_getaffinity(0) == want
     finally:
         os.sched_setaffinity(0, before)
+
+
+def test_block_replay_reproduces_the_model_block_by_block():
+    """The layer-wise engine of model-level GPTQ on CPU: blocks found as the ModuleList of callable modules that
+    holds the targets, replayed with their recorded keyword arguments (stateful cache objects dropped), each
+    block's output feeding the next; the last output equals the model's own."""
+    try:
+        from nncf_b200 import compress_api as api
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"nncf_b200 cannot be imported here: {exc}")
+    from types import SimpleNamespace
+
+    from torch import nn
+
+    class FakeCache:
+        def __init__(self):
+            self.calls = 0
+
+        def get_seq_length(self):
+            return 0
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(8, 8, bias=False)
+            self.b = nn.Linear(8, 8, bias=False)
+
+        def forward(self, hidden_states, shift=None, past=None, use_cache=False):
+            if past is not None:
+                past.calls += 1
+            return (hidden_states + self.b(torch.tanh(self.a(hidden_states))) + shift,)
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.inp = nn.Linear(4, 8, bias=False)
+            self.containers = nn.ModuleList([nn.ModuleDict({"x": nn.Linear(8, 8)}), nn.ModuleDict({"x": nn.Linear(8, 8)})])
+            self.layers = nn.ModuleList([Block() for _ in range(3)])
+            self.out = nn.Linear(8, 2, bias=False)
+            self.cache = FakeCache()
+            self.trace = []
+
+        def forward(self, x):
+            h = self.inp(x)
+            shift = torch.full((1, 8), 0.25)
+            for layer in self.layers:
+                h = layer(h, shift=shift, past=self.cache, use_cache=True)[0]
+                self.trace.append(h)
+            return self.out(h)
+
+    torch.manual_seed(0)
+    model = Model()
+    targets = [SimpleNamespace(module=m) for layer in model.layers for m in (layer.a, layer.b)] + \
+              [SimpleNamespace(module=model.out)]
+    blocks = api._decoder_blocks(model, targets)
+    assert blocks is not None and [id(b) for b in blocks] == [id(b) for b in model.layers]
+    assert api._decoder_blocks(model, [SimpleNamespace(module=model.out)]) is None
+    items = [torch.randn(2, 4), torch.randn(3, 4)]
+    replay = api._BlockReplay(model, blocks, items)
+    calls_after_capture = model.cache.calls
+    want = [model.trace[0:3], model.trace[3:6]]
+    for bi in range(3):
+        outs = [run() for run in replay.runners(bi)]
+        for k in range(2):
+            torch.testing.assert_close(outs[k][0], want[k][bi])
+        replay.advance(bi)
+    assert model.cache.calls == calls_after_capture  # the cache object was not passed to the replayed blocks
+    # weights changed after the capture are seen by later blocks: the replay runs the live modules
+    with torch.no_grad():
+        model.layers[0].a.weight.mul_(2.0)
+    replay2 = api._BlockReplay(model, blocks, items)
+    out0 = replay2.runners(0)[0]()[0]
+    assert not torch.allclose(out0, want[0][0])
