@@ -16,5 +16,6 @@ from . import _lib  # noqa: F401  (fails loudly when the CUDA library is missing
 from . import weight_lowering
 from .weight_lowering import compress_weight
 from .compress_api import Dataset, compress_weights
+from .serialization import get_config, load_from_config, strip
 
 __version__ = "0.1.0"

@@ -30,6 +30,7 @@ from .decompressors import (FloatCodebookWeightsDecompressor, INT4AsymmetricWeig
                             INT4SymmetricWeightsDecompressor, INT8AsymmetricWeightsDecompressor,
                             INT8SymmetricWeightsDecompressor)
 from .errors import InvalidGroupSizeError, ParameterNotSupportedError, ValidationError
+from . import serialization
 from .gptq import GPTQ
 from .parameters import (AdvancedCompressionParameters, BackupMode, CompressionFormat, CompressWeightsMode,
                          GroupSizeFallbackMode, SensitivityMetric)
@@ -707,6 +708,8 @@ def _transform_model(active: list, precomputed: dict) -> None:
         four = p.compression_config.num_bits == 4
         packed = it.packed.reshape(-1, 1) if four else it.packed.reshape(p.weight.shape)
         mod = p.module
+        dense_shape, dense_dtype = tuple(p.weight.shape), p.weight.dtype
         mod.weight.requires_grad_(False)
         mod.weight.data = packed
         parametrize.register_parametrization(mod, "weight", dec, unsafe=True)
+        serialization.record(mod, p.compression_config, dense_shape, dense_dtype)

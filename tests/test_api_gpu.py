@@ -155,6 +155,40 @@ def test_gptq_with_scale_estimation_model_level():
     assert errs[True] < errs[False] * 1.5, errs
 
 
+@pytest.mark.parametrize("kwargs", [dict(mode="int4_asym", group_size=16), dict(mode="int4_sym", group_size=16, all_layers=True),
+                                    dict(mode="int8_sym"), dict(mode="int8_asym"), dict(mode="nf4", group_size=16),
+                                    dict(mode="mxfp4", group_size=32)])
+def test_config_state_dict_round_trip_and_strip(kwargs):
+    """get_config + state_dict rebuild the compressed model on a fresh instance (same logits bit for bit, same
+    state); strip leaves plain dense weights that compute the same outputs."""
+    import json
+
+    import nncf_b200 as nb
+
+    ids = calibration_ids(n=2, seq=12)[0].cuda()
+    kw = dict(kwargs)
+    kw["mode"] = nb.CompressWeightsMode(kw["mode"])
+    model = nb.compress_weights(TinyGatedLM().cuda(), **kw)
+    with torch.no_grad():
+        want = model(ids)
+    config = json.loads(json.dumps(nb.get_config(model)))      # the config survives JSON
+    state = {k: v.cpu() for k, v in model.state_dict().items()}
+    assert config["weights"], "nothing was recorded"
+    fresh = nb.load_from_config(TinyGatedLM(seed=5).cuda(), config, state)
+    with torch.no_grad():
+        assert torch.equal(fresh(ids), want)
+    assert fresh.state_dict().keys() == model.state_dict().keys()
+    sizes = nb.serialization.compressed_nbytes(fresh)
+    assert 0 < sizes["compressed_bytes"] < sizes["dense_bytes"]
+    nb.strip(fresh)
+    assert not any("parametrizations" in k for k in fresh.state_dict())
+    assert all(p.dtype == torch.float32 for p in fresh.parameters())
+    with torch.no_grad():
+        torch.testing.assert_close(fresh(ids), want, rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        nb.load_from_config(TinyGatedLM().cuda(), {"format": "other", "weights": {}})
+
+
 def test_gptq_block_replay_equals_full_prefix_runs_on_hf_llama(monkeypatch):
     """Model-level GPTQ on a Hugging Face Llama: replaying each decoder layer on cached inputs (through the
     already-quantised layers before it) gives the same compressed model as re-running the whole prefix of the
