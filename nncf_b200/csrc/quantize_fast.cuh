@@ -374,6 +374,101 @@ __device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_
       }
     }
   }
+  // Symmetric integer parameters are a handful of instructions: there the gather costs what it saves.
+  if constexpr (GPW * U <= 32 && (mode_is_asym(MODE) || mode_is_fast_float(MODE))) {
+    // The iteration's GPW * U groups are consecutive: group (pass p, sub-warp j) = first + p * GPW + j.  Their
+    // parameters are computed ONCE, by lane p * GPW + j, instead of once per pass with every lane of a sub-warp
+    // repeating the same arithmetic: the reduced (min, -max) pairs are gathered with one shuffle per pass, the
+    // parameters go back with three, and scales / zero points leave as one coalesced store.
+    const int lane = threadIdx.x & 31;
+    const int sub = lane / L;
+    MinNegMax mine;
+    mine.packed = 0u;
+    mine.mn = mine.nmx = 0.0f;
+#pragma unroll
+    for (int p = 0; p < U; ++p) {
+      MinNegMax m = min_negmax<SrcT, VPL>(raw[p]);
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) reduce_step<SrcT>(m, o);
+      const int src_lane = (lane % GPW) * L;  // any lane of sub-warp lane % GPW holds that group's result
+      MinNegMax t;
+      if constexpr (sizeof(SrcT) == 2) {
+        t.packed = __shfl_sync(0xffffffffu, m.packed, src_lane);
+        t.mn = t.nmx = 0.0f;
+      } else {
+        t.packed = 0u;
+        t.mn = __shfl_sync(0xffffffffu, m.mn, src_lane);
+        t.nmx = __shfl_sync(0xffffffffu, m.nmx, src_lane);
+      }
+      if (lane / GPW == p) mine = t;
+    }
+    const int64_t first = g0 - sub;                 // first group of the iteration (warp-uniform)
+    const bool owner = lane < GPW * U && (FULL || first + lane < n_groups);
+    float mn, mx, s, r, zp = 0.0f;
+    bool need_clamp = false;
+    int e8 = 0;
+    finish_minmax<SrcT>(mine, mn, mx);
+    if constexpr (mode_is_fast_float(MODE)) {
+      float_params<MODE>(mn, mx, s, r, e8);
+    } else {
+      int_params<MODE>(mn, mx, s, r, zp, need_clamp);
+    }
+    bool clamp = false;
+    if constexpr (mode_is_asym(MODE)) clamp = __any_sync(0xffffffffu, need_clamp && owner);
+    if (owner) {
+      const int64_t g = first + lane;
+      if constexpr (mode_is_fast_float(MODE)) {
+        if (T.scale) T.scale[g] = s;
+      } else {
+        T.scale[g] = s;
+      }
+      if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
+      if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+      if constexpr (MODE == NNCFB_MXFP4) {
+        if (T.e8m0) T.e8m0[g] = static_cast<uint8_t>(e8 + 127);
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < U; ++p) {
+      const int64_t g = g0 + p * GPW;
+      const bool valid = FULL || g < n_groups;
+      const int owner_lane = p * GPW + sub;
+      const float sp = __shfl_sync(0xffffffffu, s, owner_lane);
+      const float rp = __shfl_sync(0xffffffffu, r, owner_lane);
+      if constexpr (mode_is_fast_float(MODE)) {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          float2 x[4];
+          unpack8_pairs(raw[p][v], x);
+          const uint32_t w = encode8_float<MODE>(x, sp, rp, lut_bound);  // shuffles inside: all lanes
+          if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
+        }
+      } else {
+        float zpp = 0.0f;
+        if constexpr (mode_is_asym(MODE)) zpp = __shfl_sync(0xffffffffu, zp, owner_lane);
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          float2 x[4];
+          unpack8_pairs(raw[p][v], x);
+          uint2 w;
+          if constexpr (mode_is_asym(MODE)) {
+            w = clamp ? encode8_int<MODE, 2>(x, sp, rp, zpp) : encode8_int<MODE, 0>(x, sp, rp, zpp);
+          } else {
+            w = encode8_int<MODE, 1>(x, sp, rp, zpp);
+          }
+          if (valid) {
+            const int64_t e0 = g * GS + (lig + v * L) * 8;
+            if constexpr (mode_bits(MODE) == 4) {
+              __stcs(reinterpret_cast<uint32_t*>(T.codes + (e0 >> 1)), w.x);
+            } else {
+              __stcs(reinterpret_cast<uint2*>(T.codes + e0), w);
+            }
+          }
+        }
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int p = 0; p < U; ++p) {
     const int64_t g = g0 + p * GPW;
