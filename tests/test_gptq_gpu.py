@@ -303,3 +303,46 @@ def test_gptq_odd_shapes_match_oracle(rows, cols, gs, block, mode):
         assert np.mean(z.cpu().numpy() != Z) < 0.05
     else:
         assert z is None
+
+
+def test_gptq_sweep_with_look_ahead_replays_from_a_cuda_graph():
+    """nncfb_gptq_quantize with the tensor-core workspace forks onto a library-owned stream and joins it back;
+    captured into a CUDA graph (after one eager call that does the per-device set-up) the replay must give the
+    eager result, also when replayed again on new contents of the same buffers."""
+    from nncf_b200 import _lib
+    from nncf_b200.gptq import GPTQ
+
+    gen = torch.Generator().manual_seed(9)
+    rows, C = 256, 640
+    w0 = (torch.randn(rows, C, generator=gen) * 0.02).cuda()
+    w1 = (torch.randn(rows, C, generator=gen) * 0.03).cuda()
+    x = torch.randn(2048, C, generator=gen)
+    H = ((2.0 / 8) * (x.double().T @ x.double()).float()).cuda()
+    hinv = GPTQ(0.01).prepare_hessian_inverse(H.clone(), w0.clone())
+    nb = int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, C))
+    ws = torch.empty(nb, dtype=torch.uint8, device="cuda")
+    w = torch.empty_like(w0)
+    q = torch.empty_like(w0)
+    sc = torch.empty(rows, C // 128, device="cuda")
+
+    def call():
+        _lib.check(_lib.lib.nncfb_gptq_quantize(_lib.ptr(w), rows, C, _lib.ptr(hinv), _lib.MODE_IDS["int4_sym"], 128, 128,
+                                                _lib.ptr(q), _lib.ptr(sc), None, _lib.ptr(ws), nb,
+                                                _lib.stream_handle(w.device)))
+
+    eager = []
+    for src in (w0, w1):
+        w.copy_(src)
+        call()
+        torch.cuda.synchronize()
+        eager.append((q.clone(), sc.clone(), w.clone()))
+    graph = torch.cuda.CUDAGraph()
+    w.copy_(w0)
+    with torch.cuda.graph(graph):
+        call()
+    for src, want in ((w0, eager[0]), (w1, eager[1]), (w0, eager[0])):
+        w.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(q, want[0]) and torch.equal(sc, want[1]) and torch.equal(w, want[2])
+    _lib.check(_lib.lib.nncfb_hessian_status(None))
