@@ -264,6 +264,12 @@ def run_gptq_workload(args, device):
         out["breakdown_s"] = {"hessians": round(32 * per_layer_h / 1e3, 2), "sweeps": round(32 * per_layer_s / 1e3, 2),
                               "cholesky_steps_torch_linalg": round(32 * per_layer_f / 1e3, 2),
                               "excluded": "calibration forward passes of the model (not part of the hot path)"}
+    if 14336 in hess:
+        h = hess[14336]
+        out["roofline"] = {"bound": "tensor", "kernel": "tc_tn_kernel<4 stages, Hessian> (tcgen05 / TMEM / TMA), C = 14336",
+                           "achieved": h["TFLOPs_computed"], "peak": peak_tf, "unit": "TFLOP/s",
+                           "frac": h["frac_of_measured_bf16_peak_computed"], "traffic": None,
+                           "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops, burst)"}
     print(json.dumps(out), flush=True)
 
 
