@@ -26,7 +26,7 @@
 // CTA per tile because it shares the GPU with the next block's sweep kernel.
 // Every wait is bounded: after kSpinLimit polls a role records an error code in a global flag
 // and leaves; the other roles then time out the same way, tensor memory is released and the
-// kernel returns (the host reports NNCFB_E_TIMEOUT).  No multicast, no cluster, no peer memory.
+// kernel returns (the host reports NNCFB_E_TIMEOUT).  Single-CTA TMA loads of this GPU's own memory only.
 #include <cuda.h>
 
 #include <algorithm>
