@@ -265,17 +265,20 @@ __device__ __constant__ const float kNf4LutBound[32] = {
     kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone,
     kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, -kLutNone};
 
-__host__ __device__ constexpr bool mode_is_fast_float(int m) { return m == NNCFB_NF4 || m == NNCFB_FP4 || m == NNCFB_MXFP4; }
+__host__ __device__ constexpr bool mode_is_fast_float(int m) {
+  return m == NNCFB_NF4 || m == NNCFB_FP4 || m == NNCFB_MXFP4 || m == NNCFB_FP8_E4M3 || m == NNCFB_MXFP8_E4M3;
+}
 
-// Scale of a float-mode group, WC/weight_lowering.py:106-126: max|w| (/ 6 for E2M1), eps guard, power of
-// two for MX.  `r` is the correctly rounded reciprocal (exact for a power of two).
+// Scale of a float-mode group, WC/weight_lowering.py:106-126: max|w| (/ 6 for E2M1, / 448 for E4M3), eps guard,
+// power of two for MX.  `r` is the correctly rounded reciprocal (exact for a power of two).
 template <int MODE>
 __device__ __forceinline__ void float_params(float mn, float mx, float& s, float& r, int& e8) {
   float a = fmaxf(fabsf(mn), fabsf(mx));
-  if constexpr (MODE != NNCFB_NF4) a = exact_quotient(a, 6.0f, 1.0f / 6.0f);
+  if constexpr (MODE == NNCFB_FP4 || MODE == NNCFB_MXFP4) a = exact_quotient(a, 6.0f, 1.0f / 6.0f);
+  if constexpr (MODE == NNCFB_FP8_E4M3 || MODE == NNCFB_MXFP8_E4M3) a = exact_quotient(a, 448.0f, 1.0f / 448.0f);
   a = (a < kEps32) ? kEps32 : a;
   e8 = 0;
-  if constexpr (MODE == NNCFB_MXFP4) {
+  if constexpr (mode_is_mx(MODE)) {
     e8 = e8m0_exponent(a);
     s = exp2_int(e8);
     r = exp2_int(-e8);
@@ -346,6 +349,36 @@ __device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s,
     const uint32_t nz = (m | (m >> 1) | (m >> 2)) & 0x11111111u;
     return w & (0x77777777u | (nz * 8u));
   }
+}
+
+// E4M3 bytes of 8 elements, WC/fp8_conversion.py:43-228: the quotient is rounded to fp16 and from there to E4M3,
+// both to nearest even - the two hardware conversions below.  With the scale taken from the group itself the
+// quotient never exceeds 448, so the reference's "beyond 448 becomes NaN" rule and the conversion's saturation
+// cannot differ; fp16 subnormals (below 2^-14, far under half the smallest E4M3 step 2^-9) become signed zero
+// in both.
+template <int MODE>
+__device__ __forceinline__ uint2 encode8_fp8(const float2 (&v)[4], float s, float r) {
+  const float2 r2 = f2(r, r), ns2 = f2(-s, -s);
+  uint32_t b[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 q;
+    if constexpr (mode_is_mx(MODE)) {
+      q = __fmul2_rn(v[i], r2);  // the scale is a power of two: one multiply is the exact quotient
+    } else {
+      const float2 q0 = __fmul2_rn(v[i], r2);
+      const float2 e = __ffma2_rn(ns2, q0, v[i]);
+      q = __ffma2_rn(e, r2, q0);
+    }
+    const __half2 h = __floats2half2_rn(q.x, q.y);
+    uint16_t pair;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(pair) : "r"(*reinterpret_cast<const uint32_t*>(&h)));
+    b[i] = pair;  // low byte = element 2 i, high byte = element 2 i + 1
+  }
+  uint2 out;
+  out.x = b[0] | (b[1] << 16);
+  out.y = b[2] | (b[3] << 16);
+  return out;
 }
 
 // =====================================================================================================
@@ -424,7 +457,7 @@ __device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_
       }
       if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
       if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
-      if constexpr (MODE == NNCFB_MXFP4) {
+      if constexpr (mode_is_mx(MODE)) {
         if (T.e8m0) T.e8m0[g] = static_cast<uint8_t>(e8 + 127);
       }
     }
@@ -440,8 +473,13 @@ __device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_
         for (int v = 0; v < VPL; ++v) {
           float2 x[4];
           unpack8_pairs(raw[p][v], x);
-          const uint32_t w = encode8_float<MODE>(x, sp, rp, lut_bound);  // shuffles inside: all lanes
-          if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
+          if constexpr (mode_bits(MODE) == 8) {
+            const uint2 w = encode8_fp8<MODE>(x, sp, rp);
+            if (valid) __stcs(reinterpret_cast<uint2*>(T.codes + (g * GS + (lig + v * L) * 8)), w);
+          } else {
+            const uint32_t w = encode8_float<MODE>(x, sp, rp, lut_bound);  // shuffles inside: all lanes
+            if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
+          }
         }
       } else {
         float zpp = 0.0f;
@@ -486,13 +524,18 @@ __device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_
       for (int v = 0; v < VPL; ++v) {
         float2 x[4];
         unpack8_pairs(raw[p][v], x);
-        const uint32_t w = encode8_float<MODE>(x, s, r, lut_bound);  // shuffles inside: all lanes
-        if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
+        if constexpr (mode_bits(MODE) == 8) {
+          const uint2 w = encode8_fp8<MODE>(x, s, r);
+          if (valid) __stcs(reinterpret_cast<uint2*>(T.codes + (g * GS + (lig + v * L) * 8)), w);
+        } else {
+          const uint32_t w = encode8_float<MODE>(x, s, r, lut_bound);  // shuffles inside: all lanes
+          if (valid) __stcs(reinterpret_cast<uint32_t*>(T.codes + ((g * GS + (lig + v * L) * 8) >> 1)), w);
+        }
       }
       if (valid && lig == 0) {
         if (T.scale) T.scale[g] = s;
         if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
-        if constexpr (MODE == NNCFB_MXFP4) {
+        if constexpr (mode_is_mx(MODE)) {
           if (T.e8m0) T.e8m0[g] = static_cast<uint8_t>(e8 + 127);
         }
       }

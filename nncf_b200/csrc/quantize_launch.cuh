@@ -106,8 +106,8 @@ inline FastClass fast_class(const nncfb_quantize_args& p) {
   if (!(mode_is_integer(p.mode) || fast_float) || p.inner != 1 || p.pre_scale || p.pre_zp || p.values_out ||
       p.dq_out || p.sqerr_out || !p.codes_out)
     return none;
-  if (p.scale_e8m0_out && p.mode != NNCFB_MXFP4) return none;
-  if (!p.scale_out && !(p.mode == NNCFB_MXFP4 && p.scale_e8m0_out)) return none;
+  if (p.scale_e8m0_out && !mode_is_mx(p.mode)) return none;
+  if (!p.scale_out && !(mode_is_mx(p.mode) && p.scale_e8m0_out)) return none;
   if (mode_is_asym(p.mode) && !p.zp_out) return none;
   const bool four = mode_bits(p.mode) == 4;
   if (p.codes_format != (four ? NNCFB_CODES_NIBBLE : NNCFB_CODES_BYTE)) return none;
@@ -169,6 +169,8 @@ int launch_fast_t(const FastBatch& b, int mode, FastClass cls, cudaStream_t stre
     case NNCFB_NF4: return launch_fast_mode<SrcT, NNCFB_NF4>(b, cls, stream);
     case NNCFB_FP4: return launch_fast_mode<SrcT, NNCFB_FP4>(b, cls, stream);
     case NNCFB_MXFP4: return launch_fast_mode<SrcT, NNCFB_MXFP4>(b, cls, stream);
+    case NNCFB_FP8_E4M3: return launch_fast_mode<SrcT, NNCFB_FP8_E4M3>(b, cls, stream);
+    case NNCFB_MXFP8_E4M3: return launch_fast_mode<SrcT, NNCFB_MXFP8_E4M3>(b, cls, stream);
     default: break;
   }
   set_error("fast path: unsupported mode %d", mode);

@@ -147,6 +147,14 @@ def test_compress_weight_matches_oracle(rows, cols, gs, dtype, kind, mode):
     else:
         if cfg.is_integer:
             _eq(packed.packed, ref.tensor, "byte codes")
+        else:
+            # E4M3 bytes: the quotient rounded to fp16, then to E4M3 (zero keeps the quotient's sign)
+            grouped = w_np.astype(np.float32)
+            if gs != -1:
+                grouped, _ = O.reshape_for_groups(grouped, 1, gs)
+            with np.errstate(over="ignore"):
+                h = (grouped / ref.scale).astype(np.float32).astype(np.float16).view(np.uint16)
+            _eq(packed.packed, O.f16_bits_to_e4m3_bits(h).reshape(tuple(packed.packed.shape)), "e4m3 bytes")
     _eq(packed.scale_f16, ref.scale.astype(np.float16), "fp16 scale")
     if mode in ("mxfp4", "mxfp8_e4m3"):
         _eq(packed.scale_e8m0, O.e8m0_code(ref.scale), "e8m0")
