@@ -164,9 +164,12 @@ int nncfb_awq_search(const void* weight, int32_t weight_dtype, int64_t rows, int
  * beta = 2/(n+b) per call.  With allow_tensor_cores != 0 and a 16-bit activation whose channel count is a
  * multiple of 64 (>= 256) the contraction runs on tcgen05 tensor cores (exact 16-bit products, fp32
  * accumulation in tensor memory, operands by TMA); otherwise an fp32 CUDA-core kernel runs.  The
- * tensor-core kernels (this one and the GPTQ trailing update) bound every wait; nncfb_hessian_status()
- * (synchronises the stream) returns NNCFB_E_TIMEOUT if one gave up since the flag was last cleared (every
- * Hessian launch and every nncfb_gptq_quantize call clears it first).  workspace is reserved (may be NULL).
+ * tensor-core kernels (this one and the GPTQ trailing update) bound every wait in time (4 s); a launch whose
+ * wait ran out stops, frees its tensor memory and raises a per-device sticky flag.  nncfb_hessian_status()
+ * (synchronises the stream) returns NNCFB_E_TIMEOUT if any launch on the device gave up since the flag was last
+ * read, and clears it: one check after a series of calls sees an error in any of them.  The flag is shared by
+ * all streams of the device (a timeout reported after concurrent calls does not say which of them it was); the
+ * word the roles of one launch use to stop one another is per launch.  workspace is reserved (may be NULL).
  * Replaces WC/gptq.py:200-242 (GPTQ._calculate_hessian).
  */
 int nncfb_hessian_accumulate(float* hessian, int64_t channels, const void* x, int32_t dtype, int64_t tokens,
@@ -246,7 +249,8 @@ int nncfb_channel_stats(const void* x, int32_t dtype, int64_t tokens, int64_t ch
 /*
  * Decompression of stored weights in one pass: codes (nibble-packed for 4-bit modes, bytes for 8-bit) +
  * per-group scale (+ zero point) -> n_elements values of out_dtype (NNCFB_F32 / F16 / BF16), groups of
- * `group_size` consecutive elements (a multiple of 8).
+ * `group_size` consecutive elements (any size; multiples of 8 with a 16-byte aligned output and 8-byte aligned
+ * codes take the vector kernel, everything else an element-per-thread kernel with the same arithmetic).
  *   integer modes: scale = fp16 [n_groups] (the decompressor's `_scale` buffer); zero_point = uint8 per group
  *                  (INT8_ASYM) or nibble-packed in flat group order (INT4_ASYM), NULL for symmetric modes;
  *                  arithmetic in fp16 exactly as the reference: (x.f16 - zp.f16) * scale.f16, then the cast;
@@ -272,6 +276,14 @@ int nncfb_unpack_nibbles(const uint8_t* packed, int64_t n_bytes, int32_t sub, in
  * pseudo-random operand pairs drawn from `seed`; writes the number of mismatches to
  * *mismatch_out (device int64).  Test hook, no reference counterpart. */
 int nncfb_selftest_division(int64_t n, uint64_t seed, int64_t* mismatch_out, void* stream);
+
+/* Self test of the bounded waits of the tensor-core kernels: runs the Hessian kernel on x_bf16
+ * [tokens, channels] (256 <= channels <= 1024, multiple of 64; 64 <= tokens <= 4096) with a 1 ms limit per
+ * wait and a producer that leaves out the last pipeline stage of every tile, so that the MMA role's wait runs
+ * out; every role then stops, tensor memory is released and the kernel returns with `hessian` partly written.
+ * Nothing traps or faults.  nncfb_hessian_status() afterwards returns NNCFB_E_TIMEOUT (and clears the flag);
+ * later launches are unaffected.  Test hook, no reference counterpart. */
+int nncfb_selftest_bounded_wait(float* hessian, int64_t channels, const void* x_bf16, int64_t tokens, void* stream);
 
 /* Library information */
 int nncfb_abi_version(void);

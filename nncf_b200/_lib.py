@@ -75,6 +75,7 @@ def _load() -> C.CDLL:
         "nncfb_pack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_unpack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_selftest_division": ([i64, u64, vp, vp], C.c_int),
+        "nncfb_selftest_bounded_wait": ([vp, i64, vp, i64, vp], C.c_int),
     }
     for name, (argtypes, restype) in sigs.items():
         fn = getattr(lib, name)
@@ -90,10 +91,21 @@ EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_qu
             "nncfb_gptq_workspace_bytes_tensor_cores", "nncfb_gptq_quantize",
             "nncfb_gptq_quantize_se", "nncfb_gptq_quantize_noalloc", "nncfb_decompress",
             "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
-            "nncfb_selftest_division"]
+            "nncfb_selftest_division", "nncfb_selftest_bounded_wait"]
+
+
+_calls = 0
+
+
+def launch_count() -> int:
+    """How many checked calls into the library this process has made (kernel-launching calls all go
+    through ``check``); callers use the difference around a region to count their launches."""
+    return _calls
 
 
 def check(code: int) -> None:
+    global _calls
+    _calls += 1
     if code == OK:
         return
     message = (lib.nncfb_last_error() or b"").decode("utf-8", "replace")

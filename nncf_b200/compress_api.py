@@ -188,11 +188,15 @@ def _execution_order(model: nn.Module, sample: Any) -> dict:
 def get_weight_compression_parameters(model: nn.Module, ignored_scope: Optional[Iterable[str]] = None,
                                       sample: Any = None) -> list[WeightCompressionParameters]:
     """All Linear (matmul) and Embedding weights in execution order (algorithm.py:961-1088 for the
-    two layer kinds handled here; reduction axis = last for both, src/nncf/torch/model_graph_manager.py:350-383)."""
+    two layer kinds handled here; reduction axis = last for both, src/nncf/torch/model_graph_manager.py:350-383).
+    A Parameter held by several modules (tied embeddings) appears once, under the module that runs first, like
+    the reference's de-duplication by weight name (algorithm.py:992-1007); the other holders are listed in
+    ``shared_modules``.  The returned list carries ``is_last_layer_skipped`` (algorithm.py:1003-1006): True
+    when the last layer in execution order was dropped as such a duplicate."""
     ignored = set(ignored_scope or [])
     order = _execution_order(model, sample) if sample is not None else {}
     params = []
-    for idx, (name, m) in enumerate(model.named_modules()):
+    for idx, (name, m) in enumerate(model.named_modules(remove_duplicate=False)):
         if not isinstance(m, (nn.Linear, nn.Embedding)) or name in ignored:
             continue
         if m.weight.dtype not in (torch.float32, torch.float16, torch.bfloat16):
@@ -201,7 +205,25 @@ def get_weight_compression_parameters(model: nn.Module, ignored_scope: Optional[
             weight_name=name, module=m, weight_attr="weight", reduction_axes=(1,),
             is_embedding=isinstance(m, nn.Embedding), order=order.get(id(m), 10 ** 9 + idx)))
     params.sort(key=lambda p: p.order)
-    return params
+    unique: list = _ParameterList()
+    by_weight: dict = {}
+    seen_modules: set = set()
+    for i, p in enumerate(params):
+        if id(p.module) in seen_modules:   # the same module registered under two names
+            continue
+        seen_modules.add(id(p.module))
+        first = by_weight.get(id(p.module.weight))
+        if first is not None:
+            first.shared_modules.append(p.module)
+            unique.is_last_layer_skipped = i == len(params) - 1
+            continue
+        by_weight[id(p.module.weight)] = p
+        unique.append(p)
+    return unique
+
+
+class _ParameterList(list):
+    is_last_layer_skipped = False
 
 
 def _ratio_defining(params, mode, all_layers):
@@ -209,7 +231,7 @@ def _ratio_defining(params, mode, all_layers):
     if mode in INT8_MODES:
         return list(params)
     rd = [p for p in params if not p.is_embedding]
-    if not all_layers:
+    if not all_layers and not getattr(params, "is_last_layer_skipped", False):
         rd = rd[:-1]
     if all_layers:
         rd += [p for p in params if p.is_embedding]
@@ -582,6 +604,11 @@ def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: b
                     pass
     finally:
         h.remove()
+    from . import _lib
+
+    with torch.cuda.device(H.device):
+        # a bounded wait of the tensor-core kernel that ran out in ANY of the accumulation steps raises here
+        _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(H.device)))
     return H, stat
 
 
@@ -711,5 +738,7 @@ def _transform_model(active: list, precomputed: dict) -> None:
         dense_shape, dense_dtype = tuple(p.weight.shape), p.weight.dtype
         mod.weight.requires_grad_(False)
         mod.weight.data = packed
-        parametrize.register_parametrization(mod, "weight", dec, unsafe=True)
-        serialization.record(mod, p.compression_config, dense_shape, dense_dtype)
+        # tied weights: every holder of the Parameter gets the same decompressor over the one packed tensor
+        for holder in [mod, *p.shared_modules]:
+            parametrize.register_parametrization(holder, "weight", dec, unsafe=True)
+            serialization.record(holder, p.compression_config, dense_shape, dense_dtype)

@@ -97,6 +97,9 @@ class WeightCompressionParameters:
     compression_config: Optional[WeightCompressionConfig] = None
     is_embedding: bool = False
     order: int = 0
+    # other modules that hold the very same Parameter (tied weights, e.g. lm_head.weight is embed_tokens.weight):
+    # the weight is compressed once and every holder gets the decompressor over the one packed tensor
+    shared_modules: list = field(default_factory=list)
 
     @property
     def weight(self) -> torch.Tensor:

@@ -105,8 +105,71 @@ __global__ void __launch_bounds__(256) decompress_kernel(const DecompressArgs a)
   }
 }
 
+// One element per thread, group index per element: group sizes that are not a multiple of 8 (a per-channel
+// INT8 layer whose inner dimension is, say, 100), where a group may end inside an 8-element vector.  Same
+// arithmetic as the vector kernel.
+template <typename OutT, int MODE>
+__global__ void __launch_bounds__(256) decompress_scalar_kernel(const DecompressArgs a) {
+  constexpr bool kFour = mode_bits(MODE) == 4;
+  for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < a.n;
+       e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t g = e / a.group_size;
+    uint32_t code;
+    if constexpr (kFour) code = (a.codes[e >> 1] >> (4 * (e & 1))) & 15u;
+    else code = a.codes[e];
+    float r;
+    if constexpr (mode_is_integer(MODE)) {
+      const __half s = reinterpret_cast<const __half*>(a.scale)[g];
+      int q;
+      if constexpr (MODE == NNCFB_INT4_SYM) q = static_cast<int>(code) - 8;
+      else if constexpr (MODE == NNCFB_INT8_SYM) q = static_cast<int>(static_cast<int8_t>(code));
+      else q = static_cast<int>(code);
+      __half x = __int2half_rn(q);
+      if constexpr (MODE == NNCFB_INT8_ASYM) x = __hsub(x, __int2half_rn(a.zp[g]));
+      if constexpr (MODE == NNCFB_INT4_ASYM) x = __hsub(x, __int2half_rn((a.zp[g >> 1] >> (4 * (g & 1))) & 15));
+      r = __half2float(__hmul(x, s));
+    } else {
+      float s;
+      if constexpr (mode_is_mx(MODE)) s = exp2_int(static_cast<int>(reinterpret_cast<const uint8_t*>(a.scale)[g]) - 127);
+      else s = reinterpret_cast<const float*>(a.scale)[g];
+      float u;
+      if constexpr (MODE == NNCFB_NF4) {
+        u = kNf4Levels[code];
+      } else if constexpr (mode_bits(MODE) == 8) {
+        u = e4m3_value(code);
+      } else {
+        const float mag = e2m1_magnitude(static_cast<int>(code & 7u));
+        u = (code & 8u) ? -mag : mag;
+      }
+      r = __fmul_rn(u, s);
+    }
+    reinterpret_cast<OutT*>(a.out)[e] = cast_out<OutT>(r);
+  }
+}
+
 template <typename OutT>
 int launch_decompress(const DecompressArgs& a, cudaStream_t st) {
+  if (a.group_size % 8 != 0 || !aligned16(a.out) || (reinterpret_cast<uintptr_t>(a.codes) & 7u) != 0) {
+    const int sgrid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((a.n + 255) / 256, static_cast<int64_t>(sm_count()) * 32)));
+#define NNCFB_DQS(M) decompress_scalar_kernel<OutT, M><<<sgrid, 256, 0, st>>>(a); break
+    switch (a.mode) {
+      case NNCFB_INT8_SYM: NNCFB_DQS(NNCFB_INT8_SYM);
+      case NNCFB_INT8_ASYM: NNCFB_DQS(NNCFB_INT8_ASYM);
+      case NNCFB_INT4_SYM: NNCFB_DQS(NNCFB_INT4_SYM);
+      case NNCFB_INT4_ASYM: NNCFB_DQS(NNCFB_INT4_ASYM);
+      case NNCFB_NF4: NNCFB_DQS(NNCFB_NF4);
+      case NNCFB_FP4: NNCFB_DQS(NNCFB_FP4);
+      case NNCFB_MXFP4: NNCFB_DQS(NNCFB_MXFP4);
+      case NNCFB_FP8_E4M3: NNCFB_DQS(NNCFB_FP8_E4M3);
+      case NNCFB_MXFP8_E4M3: NNCFB_DQS(NNCFB_MXFP8_E4M3);
+      default:
+        set_error("nncfb_decompress: mode %d is not supported", a.mode);
+        return NNCFB_E_UNSUPPORTED;
+    }
+#undef NNCFB_DQS
+    NNCFB_CUDA(cudaGetLastError());
+    return NNCFB_OK;
+  }
   const int64_t nvec = a.n >> 3;
   const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((nvec + 255) / 256, static_cast<int64_t>(sm_count()) * 16)));
 #define NNCFB_DQ(M) decompress_kernel<OutT, M><<<grid, 256, 0, st>>>(a); break
@@ -139,10 +202,9 @@ extern "C" int nncfb_decompress(const void* codes, int32_t mode, int64_t n_eleme
   NNCFB_CHECK_ARG(n_elements > 0 && group_size > 0 && n_elements % group_size == 0, NNCFB_E_BAD_ARG,
                   "nncfb_decompress: %lld elements are not a whole number of groups of %lld", (long long)n_elements,
                   (long long)group_size);
-  NNCFB_CHECK_ARG(group_size % 8 == 0, NNCFB_E_UNSUPPORTED, "nncfb_decompress: group size must be a multiple of 8");
   NNCFB_CHECK_ARG(!mode_is_asym(mode) || zero_point, NNCFB_E_BAD_ARG, "nncfb_decompress: zero_point is null");
-  NNCFB_CHECK_ARG(aligned16(out) && (reinterpret_cast<uintptr_t>(codes) & 7u) == 0, NNCFB_E_ALIGNMENT,
-                  "nncfb_decompress: out must be 16-byte and codes 8-byte aligned");
+  NNCFB_CHECK_ARG(mode_bits(mode) != 4 || n_elements % 2 == 0, NNCFB_E_BAD_ARG,
+                  "nncfb_decompress: %lld 4-bit codes do not fill whole bytes", (long long)n_elements);
   DecompressArgs a;
   a.codes = static_cast<const uint8_t*>(codes);
   a.scale = scale;

@@ -300,7 +300,6 @@ __global__ void __launch_bounds__(256) gptq_trailing_kernel(const GptqArgs a, co
 
 // tensor-core trailing update and its helpers (hessian_tc.cu)
 bool gptq_trailing_tc_available();
-int tc_status_reset(cudaStream_t st);
 int gptq_split_slab(const float* hinv, int64_t cols, int i1, int64_t c0, int64_t n, __nv_bfloat16* slab_planes,
                     int64_t slab_ld, cudaStream_t st);
 int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv_bfloat16* err_planes, int64_t err_ld,
@@ -364,10 +363,8 @@ int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, const GptqSe& se, c
   Lookahead* la = nullptr;
   std::unique_lock<std::mutex> lock(g_lookahead_mutex, std::defer_lock);
   if (use_tc) {
-    int rc = tc_status_reset(st);
-    if (rc != NNCFB_OK) return rc;
     lock.lock();  // the side stream and its two events are shared by every call on this device
-    rc = lookahead_for_current_device(&la);
+    const int rc = lookahead_for_current_device(&la);
     if (rc != NNCFB_OK) return rc;
   }
   // A group that reaches beyond its block makes the sweep read columns the previous block's rest update is
@@ -654,8 +651,11 @@ extern "C" int nncfb_gptq_quantize_noalloc(float* weight, int64_t rows, int64_t 
   if (rc != NNCFB_OK) return rc;
   // Nothing in the scratch has to start at zero: each block's sweep writes every error column of every
   // row before the trailing update reads it, so contents left by an earlier call are never observed.
+  // The size handed on is the minimum for `rows`, not the size of the array: a larger figure would let mid-size
+  // problems qualify for the tensor-core look-ahead schedule, which creates a stream and two events on first
+  // use and rounds differently.  With the minimum, the fp32 CUDA-core trailing update always runs.
   return nncfb_gptq_quantize(weight, rows, cols, hinv, mode, group_size, block_size, q_out, scale_out, zp_out, scratch,
-                             static_cast<size_t>(kNoAllocMaxRows) * kGptqMaxBlock * sizeof(float), stream);
+                             nncfb_gptq_workspace_bytes(rows), stream);
 }
 
 namespace nncfb {

@@ -24,12 +24,13 @@
 // slow axis, and six plane products (everything down to 2^-24 relative) are accumulated in fp32 in tensor
 // memory, smallest terms first.  That update is bound by the read-modify-write of W; it is launched with one
 // CTA per tile because it shares the GPU with the next block's sweep kernel.
-// Every wait is bounded: after kSpinLimit polls a role records an error code in a global flag
-// and leaves; the other roles then time out the same way, tensor memory is released and the
-// kernel returns (the host reports NNCFB_E_TIMEOUT).  Single-CTA TMA loads of this GPU's own memory only.
+// Every wait is bounded in time: a role that waited longer than the limit records its code in the launch's
+// status word (and in a per-device sticky flag), and leaves; the other roles then see the word or time out
+// the same way, tensor memory is released and the kernel returns (the host reports NNCFB_E_TIMEOUT).  Single-CTA TMA loads of this GPU's own memory only.
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "nncfb_common.cuh"
 
@@ -47,7 +48,7 @@ constexpr int kMaxStages = 4;
 constexpr int kBoxBytes = kBoxC * kBlockK * 2;                           // 8192
 constexpr int kStageBytes = (kTileM / kBoxC + kTileN / kBoxC) * kBoxBytes;  // 49152
 constexpr int kTmemCols = 512;  // two accumulators of kTileN fp32 columns
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint64_t kWaitLimitNs = 4000000000ull;  // 4 s per wait: far beyond any legitimate wait of this kernel
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -68,13 +69,29 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false after kSpinLimit unsuccessful polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up (returns false) once `limit_ns` nanoseconds have passed without the barrier
+// completing the phase.  The clock is read only after a batch of unsuccessful polls, so a wait that is
+// satisfied quickly costs what a plain poll loop costs.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i) {
     if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
   }
-  return false;
+  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_test(bar, parity)) return true;
+    }
+    if (global_timer_ns() - t0 > limit_ns) return false;
+    __nanosleep(64);
+  }
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -186,6 +203,16 @@ struct __align__(8) Control {
   uint32_t pad;
 };
 
+// Per-device sticky record of a bounded wait that ran out (static device memory: nothing is allocated).  It is
+// raised by any tensor-core launch and cleared only when the host reads it (nncfb_hessian_status), so an
+// error in one call of a series is still visible after the last one.
+__device__ int g_hessian_status;
+
+__device__ __forceinline__ void give_up(int* status, int role) {
+  atomicExch(status, role);           // this launch: the other roles stop at their next check
+  atomicMax(&g_hessian_status, role);  // the device: reported by the next nncfb_hessian_status
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -202,7 +229,7 @@ template <int kStages, bool TRAILING>
 __global__ void __launch_bounds__(192, 1)
 tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, float* __restrict__ H,
              int64_t ld, int64_t m_bound, int64_t n_bound, int64_t tokens, float alpha, float beta, uint32_t idesc,
-             int n_tiles_n, int n_tiles, int* __restrict__ status) {
+             int n_tiles_n, int n_tiles, int* __restrict__ status, uint64_t wait_ns, int producer_short) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte aligned operand ring (swizzle-128B atoms must start on 1 KiB), control block behind it
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -253,10 +280,12 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         int m0, n0;
         tile_origin(tile, m0, n0);
-        for (int it = 0; it < k_iters; ++it, ++g) {
+        // producer_short is 0 except in the self test of the bounded waits, where the producer leaves out the last
+        // stage(s) of every tile so that the MMA role's wait for them runs out
+        for (int it = 0; it < k_iters - producer_short; ++it, ++g) {
           const int s = g % kStages;
-          if (!mbar_wait(&ctl->empty[s], ((g / kStages) & 1) ^ 1)) {
-            atomicExch(status, 1);
+          if (!mbar_wait(&ctl->empty[s], ((g / kStages) & 1) ^ 1, wait_ns)) {
+            give_up(status, 1);
             ok = false;
             break;
           }
@@ -280,8 +309,8 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
       // do not leave while a copy into this CTA's shared memory may still be in flight: wait (bounded)
       // for the last copies issued to each stage
       for (int it = max(0, g - kStages); it < g; ++it) {
-        if (!mbar_wait(&ctl->full[it % kStages], (it / kStages) & 1)) {
-          atomicExch(status, 4);
+        if (!mbar_wait(&ctl->full[it % kStages], (it / kStages) & 1, wait_ns)) {
+          give_up(status, 4);
           break;
         }
       }
@@ -294,16 +323,16 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
         const int bf = t & 1;
         // the epilogue must have drained this accumulator buffer (two tiles ago); a fresh barrier passes
-        if (!mbar_wait(&ctl->acc_empty[bf], ((t >> 1) & 1) ^ 1)) {
-          atomicExch(status, 5);
+        if (!mbar_wait(&ctl->acc_empty[bf], ((t >> 1) & 1) ^ 1, wait_ns)) {
+          give_up(status, 5);
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(bf * kTileN);
         for (int it = 0; it < k_iters; ++it, ++g) {
           const int s = g % kStages;
-          if (!mbar_wait(&ctl->full[s], (g / kStages) & 1)) {
-            atomicExch(status, 2);
+          if (!mbar_wait(&ctl->full[s], (g / kStages) & 1, wait_ns)) {
+            give_up(status, 2);
             ok = false;
             break;
           }
@@ -348,8 +377,8 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
       tile_origin(tile, m0, n0);
       const int64_t r = static_cast<int64_t>(m0) + q * 32 + lane;
       prefetch_tile(tile + gridDim.x);
-      const bool ok = mbar_wait(&ctl->acc_full[bf], (t >> 1) & 1);
-      if (!ok && lane == 0) atomicExch(status, 3);
+      const bool ok = mbar_wait(&ctl->acc_full[bf], (t >> 1) & 1, wait_ns);
+      if (!ok && lane == 0) give_up(status, 3);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (!ok || *reinterpret_cast<volatile int*>(status) != 0) break;  // warp-uniform: some role gave up
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(bf * kTileN);
@@ -431,13 +460,22 @@ EncodeTiledFn encode_tiled_fn() {
 
 }  // namespace
 
-// Per-device error flag of the tensor-core kernel (static device memory: nothing is allocated).
-__device__ int g_hessian_status;
+// Status words of individual launches: a ring in static device memory.  Each launch takes the next word and
+// clears it on its stream before the kernel starts; the roles of that launch use it to tell one another that
+// one of them gave up.  A word is reused after kStatusSlots further launches, by which time its launch has
+// long ended in any realistic schedule (a stale non-zero word would only make a launch stop early and report
+// a timeout, never compute wrongly in silence).
+constexpr int kStatusSlots = 256;
+__device__ int g_launch_status[kStatusSlots];
 
 namespace {
 
-int status_address(int** status) {
-  NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(status), g_hessian_status));
+int next_launch_status(int** status, cudaStream_t st) {
+  static std::atomic<unsigned> counter{0};
+  int* base = nullptr;
+  NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_launch_status));
+  *status = base + (counter.fetch_add(1) % kStatusSlots);
+  NNCFB_CUDA(cudaMemsetAsync(*status, 0, sizeof(int), st));
   return NNCFB_OK;
 }
 
@@ -473,8 +511,8 @@ constexpr size_t tc_smem_bytes() { return static_cast<size_t>(kStages) * kStageB
 
 }  // namespace
 
-int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t tokens, float alpha, float beta,
-                          void* /*workspace*/, size_t /*workspace_bytes*/, cudaStream_t st) {
+static int hessian_tc_launch(float* H, int64_t C, const void* x, int dtype, int64_t tokens, float alpha, float beta,
+                             cudaStream_t st, uint64_t wait_ns, int producer_short) {
   if (C % 64 != 0 || C < 256 || !aligned16(x) || !aligned16(H) || tokens <= 0 || tokens > 0x7fffffff ||
       C > 0x7fffffff / 2)
     return NNCFB_E_UNSUPPORTED;
@@ -488,15 +526,20 @@ int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t
   auto kernel = tc_tn_kernel<kStagesHessian, false>;
   NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   int* status = nullptr;
-  if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
-  NNCFB_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  if (const int sr = next_launch_status(&status, st); sr != NNCFB_OK) return sr;
   kernel<<<std::min(n_tiles, sm_count()), 192, smem, st>>>(map, map, H, C, C, C, tokens, alpha, beta,
-                                                            instr_desc(dtype == NNCFB_BF16), tiles_n, n_tiles, status);
+                                                            instr_desc(dtype == NNCFB_BF16), tiles_n, n_tiles, status,
+                                                            wait_ns, producer_short);
   NNCFB_CUDA(cudaGetLastError());
   const dim3 mgrid(static_cast<unsigned>((C + 31) / 32), static_cast<unsigned>((C + 31) / 32));
   mirror_upper_tc_kernel<<<mgrid, 256, 0, st>>>(H, C);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
+}
+
+int hessian_tc_accumulate(float* H, int64_t C, const void* x, int dtype, int64_t tokens, float alpha, float beta,
+                          void* /*workspace*/, size_t /*workspace_bytes*/, cudaStream_t st) {
+  return hessian_tc_launch(H, C, x, dtype, tokens, alpha, beta, st, kWaitLimitNs, 0);
 }
 
 // ---- GPTQ trailing update on the tensor cores -------------------------------------------------------
@@ -516,13 +559,6 @@ __global__ void __launch_bounds__(256) gptq_split_slab_kernel(const float* __res
 
 bool gptq_trailing_tc_available() { return encode_tiled_fn() != nullptr; }
 
-// Clears the sticky error flag the tensor-core kernels share (read back with nncfb_hessian_status).
-int tc_status_reset(cudaStream_t st) {
-  int* status = nullptr;
-  if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
-  NNCFB_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
-  return NNCFB_OK;
-}
 
 // planes[p][k][j] = plane p of Hinv[i1 + k][c0 + j], j < n (bf16 [3 * 128, ld]).
 int gptq_split_slab(const float* hinv, int64_t cols, int i1, int64_t c0, int64_t n, __nv_bfloat16* slab_planes,
@@ -550,23 +586,27 @@ int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv
   auto kernel = tc_tn_kernel<kStagesTrailing, true>;
   NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   int* status = nullptr;
-  if (const int sr = status_address(&status); sr != NNCFB_OK) return sr;
+  if (const int sr = next_launch_status(&status, st); sr != NNCFB_OK) return sr;
   // One CTA per tile here: this kernel shares the GPU with the next block's sweep (whose CTAs fill the shared
   // memory of the SMs they sit on), so a fixed set of persistent CTAs would leave tiles waiting behind it;
   // with a CTA per tile the hardware hands tiles to whichever SMs are free.
   kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, w_c, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
-                                               tiles_m * tiles_n, status);
+                                               tiles_m * tiles_n, status, kWaitLimitNs, 0);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
 }
 
-// Reads the error flag of the last tensor-core Hessian launch on this device (synchronises the stream).
+// Reads the device's sticky flag after everything enqueued on `st` has run, and clears it when it was set.
 int hessian_tc_status(cudaStream_t st) {
   int* status = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_hessian_status) != cudaSuccess) return -1;
   int h = 0;
   if (cudaMemcpyAsync(&h, status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
   if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
+  if (h != 0) {
+    if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
+  }
   return h;
 }
 
@@ -579,8 +619,24 @@ extern "C" int nncfb_hessian_status(void* stream) {
     return NNCFB_E_CUDA;
   }
   if (s != 0) {
-    nncfb::set_error("tensor-core Hessian kernel gave up a bounded wait (role %d: 1 = producer, 2 = MMA, 3 = epilogue)", s);
+    nncfb::set_error("a tensor-core kernel gave up a bounded wait (role %d: 1 = producer, 2 = MMA, 3 = epilogue, "
+                     "4 = producer drain, 5 = MMA waiting for the epilogue)", s);
     return NNCFB_E_TIMEOUT;
   }
   return NNCFB_OK;
+}
+
+// Self test of the bounded waits: the Hessian kernel with a 1 ms limit per wait and a producer that leaves out the
+// last pipeline stage of every tile.  The MMA role's wait for that stage runs out, it records its code, the
+// other roles stop, tensor memory is freed and the kernel returns; H is left partly written.  Nothing traps and
+// no wait is unbounded.  The caller then reads NNCFB_E_TIMEOUT from nncfb_hessian_status.
+extern "C" int nncfb_selftest_bounded_wait(float* hessian, int64_t channels, const void* x_bf16, int64_t tokens,
+                                           void* stream) {
+  NNCFB_CHECK_ARG(hessian && x_bf16, NNCFB_E_BAD_ARG, "nncfb_selftest_bounded_wait: null pointer");
+  NNCFB_CHECK_ARG(channels >= 256 && channels <= 1024 && channels % 64 == 0 && tokens >= 64 && tokens <= 4096,
+                  NNCFB_E_BAD_ARG, "nncfb_selftest_bounded_wait: 256 <= channels <= 1024 (multiple of 64), 64 <= tokens <= 4096");
+  const int rc = nncfb::hessian_tc_launch(hessian, channels, x_bf16, NNCFB_BF16, tokens, 0.0f, 1.0f,
+                                          static_cast<cudaStream_t>(stream), 1000000ull, 1);
+  if (rc == NNCFB_E_UNSUPPORTED) nncfb::set_error("nncfb_selftest_bounded_wait: the tensor-core path is unavailable");
+  return rc;
 }

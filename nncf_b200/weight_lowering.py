@@ -212,6 +212,50 @@ def quantize_launch(
     return out
 
 
+class _MultiAxis:
+    """Several reduction axes at once (convolutions: every axis but the output channel,
+    src/nncf/torch/model_graph_manager.py:374-380; always per channel, never grouped).  The weight is viewed as
+    [kept, reduced]: kept axes first, reduced axes flattened behind them.  For the usual layout (reduced axes
+    trailing) that is a free reshape; otherwise (transposed convolutions keep axis 1) one permuted copy.  The
+    kernel then sees an ordinary per-row problem and the results are shaped back."""
+
+    def __init__(self, weight: torch.Tensor, axes: Sequence[int]):
+        nd = weight.ndim
+        self.reduced = sorted({a % nd for a in axes})
+        self.kept = [i for i in range(nd) if i not in self.reduced]
+        self.perm = self.kept + self.reduced
+        self.shape = tuple(weight.shape)
+        kept_n = 1
+        for i in self.kept:
+            kept_n *= self.shape[i]
+        self.flat = weight.permute(self.perm).contiguous().reshape(kept_n, -1)
+        self.param_shape = tuple(1 if i in self.reduced else d for i, d in enumerate(self.shape))
+
+    def restore(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """[kept, reduced]-shaped result -> the weight's own layout."""
+        if t is None:
+            return None
+        inv = [0] * len(self.perm)
+        for pos, ax in enumerate(self.perm):
+            inv[ax] = pos
+        return t.reshape([self.shape[i] for i in self.perm]).permute(inv).contiguous()
+
+    def params(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        return None if t is None else t.reshape(self.param_shape)
+
+    def flat_params(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        return None if t is None else t.reshape(-1, 1)
+
+
+def _multi_axis(weight: torch.Tensor, config: WeightCompressionConfig, reduction_axes) -> Optional[_MultiAxis]:
+    if not isinstance(reduction_axes, (tuple, list)) or len(reduction_axes) <= 1:
+        return None
+    if config.group_size != -1:
+        msg = f"Group-wise quantization expects a single reduction axis, but given: {reduction_axes}."
+        raise UnsupportedModelError(msg)
+    return _MultiAxis(weight, reduction_axes)
+
+
 def _grouped(weight: torch.Tensor, config: WeightCompressionConfig, reduction_axes, scale):
     """Resolves (weight as the caller will see it, axis into it, group size along that axis)."""
     if config.group_size != -1 and reduction_axes is not None:
@@ -247,6 +291,10 @@ def calculate_integer_quantization_params(weight: torch.Tensor, reduction_axes: 
     if not config.is_integer:
         msg = "The function supports integer quantization only"
         raise InternalError(msg)
+    ma = _multi_axis(weight, WeightCompressionConfig(config.mode, -1), reduction_axes)
+    if ma is not None:
+        scale, zp = calculate_integer_quantization_params(ma.flat, 1, config)
+        return ma.params(scale), ma.params(zp)
     w, axis, gs = _grouped(weight, WeightCompressionConfig(config.mode, -1), reduction_axes, None)
     o = quantize_launch(w, config, axis, gs, want_codes="none")
     shape = _keepdims_shape(w.shape, axis)
@@ -272,6 +320,13 @@ def _integer(weight, config, reduction_axes, precomputed_scale, precomputed_zero
         msg = ("If precomputed quantization parameters are provided, both scale and zero point are required "
                "for asymmetric quantization.")
         raise ValueError(msg)
+    ma = _multi_axis(weight, config, reduction_axes)
+    if ma is not None:
+        cw, extra = _integer(ma.flat, config, 1, ma.flat_params(precomputed_scale), ma.flat_params(precomputed_zero_point),
+                             dq, sqerr)
+        cw = CompressedWeight(ma.restore(cw.tensor), ma.params(cw.scale), ma.params(cw.zero_point))
+        extra = {"dq": ma.restore(extra["dq"]), "sqerr": extra["sqerr"], "shape": ma.shape, "axis": None}
+        return cw, extra
     w, axis, gs = _grouped(weight, config, reduction_axes, precomputed_scale)
     o = quantize_launch(w, config, axis, gs, precomputed_scale, precomputed_zero_point, want_codes="byte",
                         want_dq=dq, want_sqerr=sqerr)
@@ -320,6 +375,9 @@ def get_integer_quantization_error(weight: torch.Tensor, reduction_axes: Reducti
     if not config.is_integer:
         msg = "The function supports integer quantization only"
         raise InternalError(msg)
+    ma = _multi_axis(weight, config, reduction_axes)
+    if ma is not None:
+        return get_integer_quantization_error(ma.flat, 1, config, reduction)
     w, axis, gs = _grouped(weight, config, reduction_axes, None)
     o = quantize_launch(w, config, axis, gs, want_codes="none", want_sqerr=True, want_params=False)
     sq = o["sqerr"].reshape(_keepdims_shape(w.shape, axis))
@@ -342,6 +400,9 @@ def calculate_float_quantization_params(weight: torch.Tensor, reduction_axes: Re
     if signed:
         msg = "signed scales are used by code-book modes only, which are not supported"
         raise InternalError(msg)
+    ma = _multi_axis(weight, WeightCompressionConfig(config.mode, -1), reduction_axes)
+    if ma is not None:
+        return ma.params(calculate_float_quantization_params(ma.flat, 1, config))
     w, axis, gs = _grouped(weight, WeightCompressionConfig(config.mode, -1), reduction_axes, None)
     o = quantize_launch(w, config, axis, gs, want_codes="none")
     return o["scale"].reshape(_keepdims_shape(w.shape, axis))
@@ -352,6 +413,14 @@ def _float(weight, config, reduction_axes, precomputed_scale, dq: bool):
     if config.mode not in _SUPPORTED_FLOAT:
         msg = f"{config.mode.value} is not supported."
         raise InternalError(msg)
+    ma = _multi_axis(weight, config, reduction_axes)
+    if ma is not None:
+        cw, dqv = _float(ma.flat, config, 1, ma.flat_params(precomputed_scale), dq)
+        out = CompressedWeight(ma.restore(cw.tensor), ma.params(cw.scale))
+        out.packed = ma.restore(cw.packed)
+        if getattr(cw, "scale_e8m0", None) is not None:
+            out.scale_e8m0 = ma.params(cw.scale_e8m0)
+        return out, ma.restore(dqv)
     w, axis, gs = _grouped(weight, config, reduction_axes, precomputed_scale)
     o = quantize_launch(w, config, axis, gs, precomputed_scale, None, want_codes="byte", want_values=True, want_dq=dq)
     pshape = _keepdims_shape(w.shape, axis)
@@ -421,6 +490,21 @@ def compress_weight(weight: torch.Tensor, reduction_axes: ReductionAxes, config:
         msg = ("If precomputed quantization parameters are provided, both scale and zero point are required "
                "for asymmetric quantization.")
         raise ValueError(msg)
+    ma = _multi_axis(weight, config, reduction_axes)
+    if ma is not None:
+        # convolution weights: per-channel storage; trailing reduced axes make this a reshape, not a copy
+        pre = None if ps is None else CompressedWeight(None, ma.flat_params(ps), ma.flat_params(pz))
+        cw = compress_weight(ma.flat, 1, config, pre, pack=True)
+        if config.num_bits != 4:
+            cw.packed = ma.restore(cw.packed)
+        elif ma.perm != list(range(len(ma.perm))):
+            msg = "nibble-packed storage of a weight whose reduced axes are not trailing is not supported"
+            raise UnsupportedModelError(msg)
+        cw.scale, cw.zero_point, cw.scale_f16 = ma.params(cw.scale), ma.params(cw.zero_point), ma.params(cw.scale_f16)
+        if getattr(cw, "scale_e8m0", None) is not None:
+            cw.scale_e8m0 = ma.params(cw.scale_e8m0)
+        cw.grouped_shape = ma.shape
+        return cw
     w, axis, gs = _grouped(weight, config, reduction_axes, ps)
     four_bit = config.num_bits == 4
     o = quantize_launch(w, config, axis, gs, ps, pz, want_codes="nibble" if four_bit else "byte",

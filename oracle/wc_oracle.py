@@ -367,6 +367,42 @@ def compress_weight(weight, reduction_axis, mode, group_size=-1, scale=None, zer
     return do_float_quantization(weight, mode, group_size, reduction_axis, scale)
 
 
+def stored_form(weight: np.ndarray, mode: str, group_size: int = -1, rows_per_chunk: int = 8192) -> dict:
+    """What the reference's per-weight loop leaves behind for an [out, in] weight (reduction over the
+    last axis): ``compress_weight`` (WC/weight_lowering.py:377-407) followed by the decompressor's
+    ``pack_weight`` (src/nncf/torch/quantization/layers.py:1325-1332, 1358-1362, 1400-1404, 1444-1451).
+    Returns flat arrays: ``packed`` (4-bit modes: two codes per byte, INT4_SYM offset by 8; 8-bit modes:
+    one byte per code), ``scale`` fp32 [groups], ``zero_point`` int32 [groups] (asymmetric modes) and
+    ``scale_e8m0`` (MX modes).  NF4 / E2M1 nibbles are this build's storage choice (the reference's torch
+    path has none).  Rows are independent, so the weight is processed in chunks of rows to bound memory."""
+    weight = np.asarray(weight)
+    assert weight.ndim == 2
+    out: dict = {"packed": [], "scale": [], "zero_point": [], "scale_e8m0": []}
+    for r0 in range(0, weight.shape[0], rows_per_chunk):
+        w = np.ascontiguousarray(weight[r0:r0 + rows_per_chunk]).astype(F32)
+        cw = compress_weight(w, 1, mode, group_size)
+        if is_integer(mode):
+            if num_bits(mode) == 4:
+                codes = pack_int4(cw.tensor) if mode == INT4_SYM else pack_uint4(cw.tensor)
+            else:
+                codes = cw.tensor
+        elif mode in (FP8_E4M3, MXFP8_E4M3):
+            # E4M3 bytes: the quotient rounded to fp16, then to E4M3 (WC/fp8_conversion.py:211-228)
+            grouped = w if group_size == -1 else reshape_for_groups(w, 1, group_size)[0]
+            with np.errstate(over="ignore"):
+                h = (grouped / cw.scale).astype(F32).astype(np.float16).view(np.uint16)
+            codes = f16_bits_to_e4m3_bits(h)
+        else:
+            codes = pack_uint4(nibble_code_nf4(cw.tensor) if mode == NF4 else nibble_code_e2m1(cw.tensor))
+        out["packed"].append(np.ascontiguousarray(codes).reshape(-1))
+        out["scale"].append(cw.scale.reshape(-1))
+        if cw.zero_point is not None:
+            out["zero_point"].append(cw.zero_point.reshape(-1).astype(np.int32))
+        if mode in (MXFP4, MXFP8_E4M3):
+            out["scale_e8m0"].append(e8m0_code(cw.scale).reshape(-1))
+    return {k: np.concatenate(v) for k, v in out.items() if v}
+
+
 # ---------------------------------------------------------------------------------------
 # Nibble packing and run-time decompression
 # (src/nncf/torch/quantization/quantize_functions.py:389-473)

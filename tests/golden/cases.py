@@ -1,5 +1,7 @@
 """Case tables shared by the fixture generator (make_golden.py) and the tests."""
 
+import numpy as np
+
 QUANT_CASES = [
     # name, shape, reduction axis, group size, kind
     ("g128", (8, 256), 1, 128, "normal"),
@@ -67,3 +69,23 @@ GPTQ_SE_CASES = [
     ("se_int4_asym_g64_b128", 24, 256, 64, 128, "int4_asym", 0.05, 5, 64, "f32"),
     ("se_int4_sym_g128", 32, 256, 128, 128, "int4_sym", 0.01, 4, 160, "bf16"),
 ]
+
+
+# inputs of the large GPTQ fixtures are regenerated in the tests from this frozen generator (np.random.RandomState
+# streams never change between numpy versions), so only the reference's outputs are stored
+GPTQ_LARGE = dict(rows=512, cols=1024, group_size=128, block=128, damp=0.01, n_inputs=8, tokens=128, seed=20240)
+
+
+def gptq_large_inputs():
+    """(w fp32 [rows, cols], list of bf16-representable fp32 activations [1, tokens, cols])."""
+    import torch
+
+    c = GPTQ_LARGE
+    rs = np.random.RandomState(c["seed"])
+    w = (rs.randn(c["rows"], c["cols"]) * 0.02).astype(np.float32)
+    mix = np.eye(c["cols"], dtype=np.float32) + 0.5 * (rs.randn(c["cols"], c["cols"]).astype(np.float32) / np.sqrt(c["cols"]))
+    xs = []
+    for _ in range(c["n_inputs"]):
+        x = rs.randn(1, c["tokens"], c["cols"]).astype(np.float32) @ mix
+        xs.append(torch.from_numpy(x).to(torch.bfloat16).float().numpy())
+    return w, xs

@@ -21,7 +21,8 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
-from cases import AWQ_CASES, DTYPES, GPTQ_CASES, GPTQ_SE_CASES, MODES, QUANT_CASES, SE_CASES  # noqa: E402
+from cases import (AWQ_CASES, DTYPES, GPTQ_CASES, GPTQ_LARGE, GPTQ_SE_CASES, MODES, QUANT_CASES, SE_CASES,  # noqa: E402
+                   gptq_large_inputs)
 
 
 def _setup(ref_src: str):
@@ -377,6 +378,99 @@ def gen_gptq(out: dict, cases=None, prefix="gptq", scale_estimation=False):
     out[f"{prefix}/index"] = np.array(names)
 
 
+def gen_gptq_large(out: dict):
+    """GPTQ at 512 x 1024, group 128, block 128, damping 0.01 by the reference's TORCH backend (the oracle of
+    record), INT4_SYM and INT4_ASYM on the same weight and activations; plus the same problem on the reference's
+    numpy backend, whose distance from the torch result is the reference's own self-noise floor."""
+    import torch
+
+    from nncf.parameters import CompressWeightsMode
+    from nncf.quantization.algorithms.weight_compression.config import WeightCompressionConfig
+    from nncf.quantization.algorithms.weight_compression.gptq import GPTQ
+    from nncf.tensor import Tensor
+    from nncf.tensor import functions as fns
+
+    MM = object()
+    be = SimpleNamespace(matmul_metatypes=[MM], convolution_metatypes=[])
+    node = SimpleNamespace(metatype=MM, node_name="mm",
+                           layer_attributes=SimpleNamespace(input_attributes={"transpose": False},
+                                                            constant_attributes={1: {"transpose": True}}))
+    c = GPTQ_LARGE
+    w, xs = gptq_large_inputs()
+    iu = np.triu_indices(c["cols"])
+
+    def run(backend: str, mode: str):
+        g = GPTQ(damp_percent=c["damp"], block_size=c["block"], subset_size=c["n_inputs"])
+        g._backend_entity = be
+        if backend == "torch":
+            inputs = [Tensor(torch.from_numpy(x).to(torch.bfloat16)) for x in xs]
+            wt = Tensor(torch.from_numpy(w.copy()))
+        else:
+            inputs = [Tensor(x.copy()) for x in xs]
+            wt = Tensor(w.copy())
+        H = g._calculate_hessian(node, inputs)
+        Hc = Tensor(H.data[0].clone() if backend == "torch" else H.data[0].copy())
+        cfg = WeightCompressionConfig(CompressWeightsMode(mode), c["group_size"])
+        wp = SimpleNamespace(node_with_weight=node, weight_port_id=1, compression_config=cfg, reduction_axes=(1,))
+        q, s, z = g._quantize_weights(wp, Hc, wt, inputs)
+        return _np(H.data[0]), _np(q), _np(s), (None if z is None else _np(z))
+
+    names = []
+    for mode in ("int4_sym", "int4_asym"):
+        H, q, s, z = run("torch", mode)
+        _, qn, _, _ = run("numpy", mode)
+        key = f"gptq_large/{mode}"
+        names.append(key)
+        # codes: q = (code - zp) * scale exactly (WC/weight_lowering.py:428-448), so integer codes + parameters
+        # reproduce the reference's dequantised weight bit for bit
+        sg = np.repeat(s.reshape(c["rows"], -1), c["group_size"], axis=1)
+        zg = 0 if z is None else np.repeat(z.reshape(c["rows"], -1), c["group_size"], axis=1).astype(np.float32)
+        codes = np.rint(q / sg + zg)
+        assert np.array_equal(((codes - zg) * sg).astype(np.float32), q)
+        out[key + "/codes"] = codes.astype(np.int8 if z is None else np.uint8)
+        out[key + "/scale"] = s
+        if z is not None:
+            out[key + "/zp"] = z
+        out[key + "/numpy_backend_rel_fro"] = np.float64(np.linalg.norm(qn - q) / np.linalg.norm(q))
+        out[key + "/numpy_backend_diff_frac"] = np.float64(np.mean(qn != q))
+        if "gptq_large/H_triu" not in out:
+            out["gptq_large/H_triu"] = H[iu]
+            # the factor the reference's sweep used: its three calls (WC/gptq.py:269-295) on this Hessian
+            Ht = Tensor(torch.from_numpy(H.copy()))
+            damp = c["damp"] * fns.mean(fns.diag(Ht))
+            d = fns.arange(c["cols"], backend=Ht.backend, device=Ht.device)
+            Ht[d, d] += damp
+            U = fns.linalg.cholesky(fns.linalg.cholesky_inverse(fns.linalg.cholesky(Ht)), upper=True)
+            out["gptq_large/U_triu"] = _np(U)[iu]
+    out["gptq_large/index"] = np.array(names)
+    out["gptq_large/params"] = np.array([c[k] for k in ("rows", "cols", "group_size", "block", "n_inputs", "tokens", "seed")],
+                                        dtype=np.int64)
+    out["gptq_large/damp"] = np.float64(c["damp"])
+
+
+def gen_config1(out: dict):
+    """SHA-256 digests of every tensor of the state dict the reference's ``nncf.compress_weights`` produces for
+    8 stacked Linear(4096 -> 4096) fp32 layers (INT4_SYM, group 128, ratio 1.0, CPU): a few hundred bytes that
+    pin 8 x 16.8 M codes, their fp16 scales and the INT8_ASYM backup layer."""
+    import hashlib
+
+    import nncf
+    from models import StackedLinear
+
+    model = StackedLinear(8, 4096).eval()
+    cm = nncf.compress_weights(model, mode=nncf.CompressWeightsMode.INT4_SYM, group_size=128, ratio=1.0,
+                               dataset=nncf.Dataset([model.example_input()]))
+    names, digests, metas = [], [], []
+    for k, v in cm.state_dict().items():
+        a = np.ascontiguousarray(_np(v))
+        names.append(k)
+        digests.append(hashlib.sha256(a.tobytes()).hexdigest())
+        metas.append(f"{a.dtype}{list(a.shape)}")
+    out["config1/keys"] = np.array(names)
+    out["config1/sha256"] = np.array(digests)
+    out["config1/meta"] = np.array(metas)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("NNCF_REFERENCE_SRC"), required="NNCF_REFERENCE_SRC" not in os.environ,
@@ -392,6 +486,8 @@ def main():
         "awq": gen_awq,
         "gptq": gen_gptq,
         "gptq_se": gen_gptq_se,
+        "gptq_large": gen_gptq_large,
+        "config1": gen_config1,
         "api": gen_api,
     }
     only = [a for a in sys.argv[1:] if a in groups]

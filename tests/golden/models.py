@@ -32,6 +32,28 @@ class TinyGatedLM(nn.Module):
         return self.head(x)
 
 
+class StackedLinear(nn.Module):
+    """n stacked Linear(width -> width, bias=False) layers with N(0, 0.02^2) weights from seed 0: with 8 layers
+    of width 4096 in fp32 this is the CPU-runnable benchmark configuration of the compression path."""
+
+    def __init__(self, n_layers: int = 8, width: int = 4096, seed: int = 0):
+        super().__init__()
+        self.width = width
+        self.layers = nn.ModuleList(nn.Linear(width, width, bias=False) for _ in range(n_layers))
+        g = torch.Generator().manual_seed(seed)
+        with torch.no_grad():
+            for lin in self.layers:
+                lin.weight.copy_(torch.randn(lin.weight.shape, generator=g) * 0.02)
+
+    def forward(self, x):
+        for lin in self.layers:
+            x = lin(x)
+        return x
+
+    def example_input(self):
+        return torch.randn(1, self.width, generator=torch.Generator().manual_seed(1))
+
+
 def calibration_ids(n=6, seq=16, vocab=64, seed=1):
     g = torch.Generator().manual_seed(seed)
     return [torch.randint(0, vocab, (1, seq), generator=g) for _ in range(n)]

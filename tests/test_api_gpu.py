@@ -288,3 +288,59 @@ def test_hf_llama_model_awq_scale_estimation_end_to_end():
     assert sd["lm_head.parametrizations.weight.original"].shape == (256, 64)           # INT8 backup, unpacked bytes
     assert sd["model.embed_tokens.parametrizations.weight.original"].shape == (256, 64)
     assert sd["model.layers.0.mlp.down_proj.parametrizations.weight.original"].shape == (64 * 128 // 2, 1)
+
+
+def test_tied_embedding_and_head_are_compressed_once_and_both_keep_working():
+    """``lm_head.weight is embed_tokens.weight`` (the default of many Hugging Face models): the shared Parameter is
+    compressed once, in the embedding's precision (INT8_ASYM backup), both modules decompress the one packed
+    tensor, the last remaining Linear stays in the primary precision (the reference skips a shared last layer,
+    algorithm.py:992-1007, 559-561), and the model's outputs stay close to the dense model's."""
+    transformers = pytest.importorskip("transformers")
+    import nncf_b200 as nb
+
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, vocab_size=256, max_position_embeddings=64,
+                                   tie_word_embeddings=True)
+    model = transformers.LlamaForCausalLM(cfg).cuda().eval()
+    assert model.lm_head.weight is model.model.embed_tokens.weight
+    ids = torch.randint(0, 256, (1, 24), generator=torch.Generator().manual_seed(2)).cuda()
+    with torch.no_grad():
+        base = model(input_ids=ids).logits.float()
+    cm = nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_SYM, group_size=32)
+    sd = cm.state_dict()
+    emb = sd["model.embed_tokens.parametrizations.weight.original"]
+    head = sd["lm_head.parametrizations.weight.original"]
+    assert emb.dtype == torch.uint8 and tuple(emb.shape) == (256, 64)            # INT8_ASYM, unpacked bytes
+    assert head.data_ptr() == emb.data_ptr()                                       # one packed tensor, two holders
+    assert cm.lm_head.parametrizations.weight[0] is cm.model.embed_tokens.parametrizations.weight[0]
+    assert tuple(cm.lm_head.weight.shape) == (256, 64) and cm.lm_head.weight.dtype == base.dtype
+    # the last decoder layer's down_proj is the last remaining Linear: still 4-bit (nibble-packed)
+    assert tuple(sd["model.layers.1.mlp.down_proj.parametrizations.weight.original"].shape) == (64 * 128 // 2, 1)
+    with torch.no_grad():
+        out = cm(input_ids=ids).logits.float()
+    assert float((out - base).norm() / base.norm()) < 0.25
+
+
+@pytest.mark.parametrize("mode,kw", [("int8_asym", {}), ("int8_sym", {}),
+                                     ("int4_asym", dict(group_size=4, all_layers=True)),
+                                     ("int4_sym", dict(group_size=10, all_layers=True))])
+def test_inner_dimension_that_is_not_a_multiple_of_8_compresses_and_runs(mode, kw):
+    """Linear(100 -> 20 -> 100): per-channel groups of 100 elements (or groups of 4 / 10) end inside an 8-element vector
+    of the decompression kernel's fast path; the element-per-thread path must give the oracle's fp16 arithmetic."""
+    from oracle import wc_oracle as O
+
+    import nncf_b200 as nb
+
+    torch.manual_seed(1)
+    model = torch.nn.Sequential(torch.nn.Linear(100, 20, bias=False), torch.nn.Linear(20, 100, bias=False)).cuda().half()
+    dense = [m.weight.detach().clone() for m in model]
+    cm = nb.compress_weights(model, mode=nb.CompressWeightsMode(mode), **kw)
+    x = torch.randn(3, 100, device="cuda", dtype=torch.float16)
+    assert torch.isfinite(cm(x)).all()
+    for m, w in zip(cm, dense):
+        gs = kw.get("group_size", -1)
+        ref = O.compress_weight(w.cpu().numpy(), 1, mode, gs)
+        s16 = ref.scale.astype(np.float16)
+        dq = O.decompress_asymmetric(ref.tensor, s16, ref.zero_point) if O.is_asym(mode) else O.decompress_symmetric(ref.tensor, s16)
+        np.testing.assert_array_equal(m.weight.detach().cpu().numpy(), dq.reshape(w.shape))

@@ -159,3 +159,39 @@ def test_block_replay_reproduces_the_model_block_by_block():
     replay2 = api._BlockReplay(model, blocks, items)
     out0 = replay2.runners(0)[0]()[0]
     assert not torch.allclose(out0, want[0][0])
+
+
+def test_tied_weights_are_listed_once_and_the_last_layer_counts_as_skipped():
+    """A Parameter shared by the embedding and the output head (tied embeddings) must appear once, under the
+    module that runs first, with the other holder recorded; the last layer then counts as skipped, so that
+    the last *remaining* Linear is not demoted to the backup precision (algorithm.py:540-575, 992-1007)."""
+    try:
+        from nncf_b200 import CompressWeightsMode
+        from nncf_b200.compress_api import _ratio_defining, get_weight_compression_parameters
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"nncf_b200 cannot be imported here: {exc}")
+
+    class Tied(torch.nn.Module):
+        def __init__(self, tie: bool):
+            super().__init__()
+            self.embed = torch.nn.Embedding(32, 16)
+            self.a = torch.nn.Linear(16, 16, bias=False)
+            self.b = torch.nn.Linear(16, 16, bias=False)
+            self.head = torch.nn.Linear(16, 32, bias=False)
+            if tie:
+                self.head.weight = self.embed.weight
+
+        def forward(self, ids):
+            return self.head(self.b(self.a(self.embed(ids))))
+
+    ids = torch.randint(0, 32, (1, 4))
+    tied = get_weight_compression_parameters(Tied(True), None, ids)
+    assert [p.weight_name for p in tied] == ["embed", "a", "b"]
+    assert tied.is_last_layer_skipped
+    assert [type(m).__name__ for m in tied[0].shared_modules] == ["Linear"]
+    assert [p.weight_name for p in _ratio_defining(tied, CompressWeightsMode.INT4_SYM, False)] == ["a", "b"]
+    plain = get_weight_compression_parameters(Tied(False), None, ids)
+    assert [p.weight_name for p in plain] == ["embed", "a", "b", "head"]
+    assert not plain.is_last_layer_skipped
+    assert [p.weight_name for p in _ratio_defining(plain, CompressWeightsMode.INT4_SYM, False)] == ["a", "b"]
+    assert [p.weight_name for p in _ratio_defining(plain, CompressWeightsMode.INT4_SYM, True)] == ["a", "b", "head", "embed"]

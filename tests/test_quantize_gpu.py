@@ -426,3 +426,40 @@ def test_random_shapes_modes_and_dtypes_match_oracle():
             elif cfg.num_bits == 4:
                 codes = O.nibble_code_nf4(ref.tensor) if mode == "nf4" else O.nibble_code_e2m1(ref.tensor)
                 _eq(st.packed, O.pack_uint4(codes), tag + " packed float codes")
+
+
+@pytest.mark.parametrize("mode", ["int8_asym", "int8_sym", "int4_sym", "int4_asym", "nf4", "fp8_e4m3"])
+@pytest.mark.parametrize("shape,axes", [((24, 16, 3, 3), (1, 2, 3)),     # Conv2d [out, in, kh, kw]: channel axis 0
+                                        ((16, 24, 3, 3), (0, 2, 3)),     # ConvTranspose2d [in, out, kh, kw]: channel axis 1
+                                        ((8, 12, 5), (1, 2)),            # Conv1d
+                                        ((6, 4, 2, 3, 3), (1, 2, 3, 4))])  # Conv3d
+def test_convolution_weights_reduce_over_every_axis_but_the_channel(shape, axes, mode):
+    """Several reduction axes at once (src/nncf/torch/model_graph_manager.py:374-380: all axes of a convolution
+    weight except its output channel; per channel, i.e. the backup precision): codes, scale and zero point in
+    the weight's own layout against the oracle with the same tuple of axes; group-wise quantisation over
+    several axes is refused like in the reference."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import weight_lowering as wl
+    from nncf_b200.errors import UnsupportedModelError
+
+    gen = torch.Generator().manual_seed(sum(shape) + len(mode))
+    w = (torch.randn(*shape, generator=gen) * 0.05).to(torch.bfloat16)
+    ref = O.compress_weight(w.float().numpy(), axes, mode, -1)
+    cfg = _cfg(mode, -1)
+    cw = wl.compress_weight(w.cuda(), axes, cfg)
+    _eq(cw.tensor, ref.tensor, "tensor")
+    _eq(cw.scale, ref.scale, "scale")
+    if cfg.is_asym_mode:
+        _eq(cw.zero_point, ref.zero_point, "zp")
+    if cfg.is_integer:
+        s, z = wl.calculate_integer_quantization_params(w.cuda(), axes, cfg)
+        _eq(s, ref.scale, "params scale")
+        dq = wl.integer_quantize_dequantize_weight(w.cuda(), cfg, axes)
+        _eq(dq, O.do_integer_dequantization(ref), "dequantised")
+        if cfg.num_bits == 8:
+            st = wl.compress_weight(w.cuda(), axes, cfg, pack=True)
+            _eq(st.packed, ref.tensor, "stored bytes")
+            _eq(st.scale_f16, ref.scale.astype(np.float16), "fp16 scale")
+    with pytest.raises(UnsupportedModelError):
+        wl.compress_weight(w.cuda(), axes, _cfg(mode, 4))

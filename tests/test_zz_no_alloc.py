@@ -59,6 +59,21 @@ def test_noalloc_entry_matches_workspace_entry_on_two_calls_in_a_row():
         assert torch.isfinite(got[0]).all()
 
 
+@pytest.mark.parametrize("rows,cols", [(1024, 1024), (1024, 4096), (2048, 4096)])
+def test_noalloc_entry_keeps_the_fp32_trailing_update_for_shapes_the_tensor_core_path_would_take(rows, cols):
+    """Rows that are a multiple of 8 with several 128-column blocks qualify for the tensor-core trailing update
+    when the workspace is large enough (3.7 MB for 1024 x 1024, exactly 8 MiB for 1024 x 4096, more than the
+    built-in array for 2048 x 4096).  The allocation-free entry must not switch to it: it creates a stream
+    and events on first use and rounds differently.  Its result has to equal, bit for bit, that of the regular
+    entry given the minimum workspace (which always runs the fp32 CUDA-core update)."""
+    w, hinv = _problem(rows, cols, 3)
+    ref = _run("workspace", w, hinv, "int4_sym", 128, 128)
+    got = _run("noalloc", w, hinv, "int4_sym", 128, 128)
+    for a, b in zip(ref, got):
+        if a is not None:
+            assert torch.equal(a, b)
+
+
 def test_noalloc_entry_rejects_sizes_beyond_its_scratch():
     from nncf_b200 import _lib
 
