@@ -2,20 +2,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
-A step is one pass of the hot path over one synthetic Llama-3-8B-shaped bf16 weight set
+A step is one pass of the hot path over ONE synthetic Llama-3-8B-shaped bf16 weight set
 (8.03e9 parameters, 16.06 GB): INT4_SYM group 128 on the 224 decoder matrices and INT8_ASYM per
 channel on the embedding and lm_head, which is what ``compress_weights(mode=INT4_SYM,
-group_size=128, ratio=1.0)`` does with its default backup rule.  Weights are N(0, 0.02^2) from
-seed 1 (+ rank).  With N > 1 every rank compresses its own weight set of that size (weak
-scaling: the global job is an N-times larger set of layers split by bytes); nothing is exchanged
-in the timed region.
+group_size=128, ratio=1.0)`` does with its default backup rule.  Every weight is N(0, 0.02^2) from
+a seed derived from the configuration's seed 1 and the tensor's index.
 
-One JSON line is printed by rank 0: `value` is source-weight GB/s over all ranks with inputs
-resident in HBM (CUDA-graph replay of the kernel launches, CUDA events, max over ranks); `e2e` is
-the same metric through the host-buffer API (pinned host weights -> device -> packed results back
-in host memory, copies inside the timed region); `roofline` describes the dominant kernel;
-`cpu_baseline` is the reference's torch CPU op chain (a port kept under oracle/) on 1/32 of the
-workload.  `--impl reference` times only that CPU arm.
+N = 1: `value` is source-weight GB/s with inputs resident in HBM (CUDA-graph replay of the two
+batched launches, CUDA events).  N > 1 (one process per GPU, torchrun): the SAME model is split over
+the ranks by source bytes and every packed result is collected on rank 0 over NCCL while the ranks
+are still compressing; `value` is the model's source bytes over the time of compress + gather (max
+over ranks), i.e. strong scaling; `multi_gpu` gives the halves on their own.
+
+The one JSON line rank 0 prints also carries: `e2e`, the same metric through the host-buffer API
+(pinned host weights -> device -> packed results back in host memory, copies inside the timed region;
+for N > 1 the model split over the ranks' PCIe links); `roofline` of the dominant kernel; `parity`, a
+check of what the timed passes wrote against the CPU oracle; `gptq`, the second half of the metric
+(GPTQ seconds per 8B model: calibration through a random-init Llama-3-8B-architecture model);
+`cpu_baseline`, the reference's own CPU implementation on 1/32 of the workload (N = 1 only).
+`--impl reference` times only that CPU arm.
 """
 
 from __future__ import annotations
@@ -97,29 +102,26 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_weight_set(device, seed: int):
-    """The synthetic weight set on `device`: list of (name, tensor, config)."""
-    from nncf_b200 import CompressWeightsMode, WeightCompressionConfig
-    from nncf_b200.pipeline import llama3_8b_weight_shapes
-
-    int4 = WeightCompressionConfig(CompressWeightsMode.INT4_SYM, 128)
-    int8 = WeightCompressionConfig(CompressWeightsMode.INT8_ASYM, -1)
-    gen = torch.Generator(device=device).manual_seed(seed)
-    items = []
-    for name, shape in llama3_8b_weight_shapes():
-        w = torch.empty(shape, dtype=torch.bfloat16, device=device)
-        w.normal_(0.0, 0.02, generator=gen)
-        backup = name in ("model.embed_tokens", "lm_head")
-        items.append((name, w, int8 if backup else int4))
-    return items
-
-
 def cpu_reference_sample(threads: int, steps: int, warmup: int):
-    """The reference's CPU path (torch op chain, all host threads) on 1/32 of the workload:
-    one decoder layer's 7 matrices (INT4_SYM g128) and 1/32 of the embedding and lm_head rows
-    (INT8_ASYM per channel), compress + pack.  Returns (GB/s, seconds per step, source bytes)."""
-    from oracle import wc_oracle_torch as T
+    """The reference's CPU path with all host threads on 1/32 of the workload: one decoder layer's 7 matrices
+    (INT4_SYM g128) and 1/32 of the embedding and lm_head rows (INT8_ASYM per channel), compress + pack per
+    weight as its torch backend does.  Runs the unmodified reference package when a copy of it is present
+    (oracle/_ref, made by oracle/make_ref.py; kind "reference"), else the restatement of its torch op chain
+    kept under oracle/ (kind "port").  Returns (GB/s, seconds per step, source bytes, kind, note)."""
+    kind, note, step_fn = "port", "", None
+    try:
+        from oracle import ref_loader
 
+        ref_loader.load()
+        step_fn = ref_loader.compress_and_pack
+        kind = "reference"
+        note = ("unmodified reference (nncf 3.2.0) from oracle/_ref: weight_lowering.compress_weight + "
+                "decompressor.pack_weight per weight, torch CPU backend")
+    except Exception as exc:  # noqa: BLE001 - any import problem falls back to the port, and the line says so
+        from oracle import wc_oracle_torch as T
+
+        step_fn = T.compress_and_pack
+        note = f"port of the reference's torch op chain (oracle/wc_oracle_torch.py); oracle/_ref unusable: {exc}"
     torch.set_num_threads(threads)
     gen = torch.Generator().manual_seed(1)
     shapes = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336)]
@@ -129,9 +131,9 @@ def cpu_reference_sample(threads: int, steps: int, warmup: int):
 
     def step():
         for w in ws:
-            T.compress_and_pack(w, "int4_sym", 128)
+            step_fn(w, "int4_sym", 128)
         for w in emb:
-            T.compress_and_pack(w, "int8_asym", -1)
+            step_fn(w, "int8_asym", -1)
 
     for _ in range(warmup):
         step()
@@ -139,7 +141,7 @@ def cpu_reference_sample(threads: int, steps: int, warmup: int):
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / steps
-    return nbytes / dt / 1e9, dt, nbytes
+    return nbytes / dt / 1e9, dt, nbytes, kind, note
 
 
 def host_threads() -> int:
@@ -153,16 +155,16 @@ def run_reference(args, rank: int, world: int):
     if rank != 0:
         return
     threads = host_threads()
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-    gbs, dt, nbytes = cpu_reference_sample(threads, steps, warmup)
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    gbs, dt, nbytes, kind, note = cpu_reference_sample(threads, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": "1/32 of the workload per step"},
-        "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port",
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": "each step is 1/32 of the workload (a rate on the same tensor mix)"},
+        "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": kind,
                          "sample": f"1 decoder layer (7 matrices) INT4_SYM g128 + 1/32 of embed/lm_head rows INT8_ASYM, "
-                                   f"{nbytes / 1e6:.0f} MB source, compress + pack, torch CPU op chain of the reference"},
+                                   f"{nbytes / 1e6:.0f} MB source per step, compress + pack; {note}"},
         "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -170,7 +172,7 @@ def run_reference(args, rank: int, world: int):
 
 
 def run_gptq_workload(args, device):
-    """Secondary metric of BASELINE.json: GPTQ seconds per 8B model.  Measures the two kernels that make up
+    """GPTQ kernels one by one on Llama-3-8B shapes (the model-level run is `run_gptq_model`).  Measures the two kernels that make up
     GPTQ on Llama-3-8B shapes - Hessian accumulation (tcgen05) on bf16 activations and the blocked sweep
     (+ Cholesky steps by torch.linalg) - and combines them into a per-model figure for 128 x 2048 calibration
     tokens: per layer 4 distinct Hessians (q/k/v share, o, gate/up share, down) and 7 sweeps."""
@@ -313,7 +315,7 @@ def run_api_workload(args, device):
 
 
 def run_moe_workload(args, device, rank, world, dist):
-    """BASELINE.json config 5: NF4 (g128) or MXFP4 (E2M1 values, E8M0 scale per 32) data-free compression of a
+    """Benchmark configuration 5: NF4 (g128) or MXFP4 (E2M1 values, E8M0 scale per 32) data-free compression of a
     Mixtral-8x7B-shaped expert stack (per layer 8 experts x (w1, w3: 14336 x 4096; w2: 4096 x 14336), bf16
     N(0, 0.02^2), seed 4), experts sharded over the ranks by bytes.  `--layers` sets how many of the 32 layers
     are generated (90 GB for all 32)."""
@@ -417,6 +419,396 @@ def run_data_aware_workload(args, device):
     print(json.dumps(out), flush=True)
 
 
+def tensor_seed(index: int) -> int:
+    """Seed of weight `index` of the synthetic model (configuration seed 1): the same tensor has the same values
+    whichever rank generates it."""
+    return 1 * 1000003 + index
+
+
+def make_weight(shape, index: int, device):
+    gen = torch.Generator(device=device).manual_seed(tensor_seed(index))
+    w = torch.empty(shape, dtype=torch.bfloat16, device=device)
+    w.normal_(0.0, 0.02, generator=gen)
+    return w
+
+
+def model_specs():
+    """(name, shape, dtype, config) of the 226 weights: INT4_SYM g128, embed_tokens / lm_head on the INT8_ASYM backup."""
+    from nncf_b200 import CompressWeightsMode, WeightCompressionConfig
+    from nncf_b200.pipeline import llama3_8b_weight_shapes
+
+    int4 = WeightCompressionConfig(CompressWeightsMode.INT4_SYM, 128)
+    int8 = WeightCompressionConfig(CompressWeightsMode.INT8_ASYM, -1)
+    return [(name, shape, torch.bfloat16, int8 if name in ("model.embed_tokens", "lm_head") else int4)
+            for name, shape in llama3_8b_weight_shapes()]
+
+
+def parity_gate(specs, results: dict, device) -> dict:
+    """Checks what the timed passes left behind against the CPU oracle: the seven matrices of decoder layer 0 in
+    full and the first 1/32 of the embedding's and lm_head's rows (rows are independent, so a row range of the
+    weight maps to a byte range of every output).  `results`: {name: {field: tensor}} on this rank, for N > 1
+    including what other ranks compressed and sent.  Weights are regenerated here from their seeds."""
+    from oracle import wc_oracle as O
+
+    checked, mismatched, compared = 0, 0, 0
+    for i, (name, shape, _, cfg) in enumerate(specs):
+        backup = name in ("model.embed_tokens", "lm_head")
+        if not (backup or name.startswith("model.layers.0.")) or name not in results:
+            continue
+        rows = shape[0] // 32 if backup else shape[0]
+        w = make_weight(shape, i, device)[:rows].float().cpu().numpy()
+        ref = O.stored_form(w, cfg.mode.value, cfg.group_size)
+        gs = shape[1] if cfg.group_size == -1 else cfg.group_size
+        per_row = {"packed": shape[1] // 2 if cfg.num_bits == 4 else shape[1], "scale": shape[1] // gs,
+                   "zero_point": shape[1] // gs, "scale_e8m0": shape[1] // gs}
+        for field, want in ref.items():
+            got = results[name][field][: rows * per_row[field]].cpu().numpy().reshape(-1)
+            if got.dtype != want.dtype:
+                got = got.view(want.dtype)
+            mismatched += int((got != want).sum())
+            compared += want.size * want.itemsize
+        checked += 1
+    return {"checked_tensors": checked, "compared_bytes": compared, "mismatched_bytes": mismatched,
+            "against": "numpy oracle of the reference's arithmetic (oracle/wc_oracle.py), after the timed passes",
+            "what": "decoder layer 0 (7 matrices, full) + first 1/32 of embed_tokens and lm_head rows"}
+
+
+def run_gptq_model(args, device, rank, world, dist):
+    """Benchmark configuration 4 as written: a random-init Llama-3-8B-architecture bf16 model (Hugging Face
+    LlamaForCausalLM, N(0, 0.02^2), seed 1), 128 sequences of 2048 token ids uniform in [0, 128256) from seed 3
+    run through the model, INT4_SYM group 128, gptq=True, damping 0.01, block 128, fp32 Hessians - through
+    nncf_b200.compress_weights.  `--gptq-layers k` keeps only the first k decoder layers of the model (the line
+    says so); the default is all 32.  Returns the `gptq` object of the JSON line."""
+    import transformers
+
+    import nncf_b200 as nb
+    from nncf_b200 import compress_api
+
+    layers = args.gptq_layers
+    cfg = transformers.LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=layers,
+                                   num_attention_heads=32, num_key_value_heads=8, max_position_embeddings=8192,
+                                   rope_theta=500000.0, tie_word_embeddings=False, initializer_range=0.02)
+    torch.manual_seed(1)
+    t0 = time.perf_counter()
+    with torch.device(device):
+        model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    torch.cuda.synchronize()
+    t_build = time.perf_counter() - t0
+    gen = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 128256, (args.gptq_samples, args.gptq_tokens), generator=gen)
+    items = [{"input_ids": ids[k:k + 1].to(device)} for k in range(args.gptq_samples)]
+    adv = nb.AdvancedCompressionParameters(gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.01, block_size=128,
+                                                                                subset_size=args.gptq_samples))
+    compress_api.COLLECT_TIMERS = True
+    compress_api.TIMERS.clear()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_SYM, group_size=128, ratio=1.0, gptq=True,
+                        dataset=nb.Dataset(items), subset_size=args.gptq_samples, advanced_parameters=adv)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    with torch.no_grad():
+        finite = bool(torch.isfinite(model(input_ids=items[0]["input_ids"][:, :128]).logits).all())
+    split = {k: round(v, 3) for k, v in compress_api.TIMERS.items()}
+    n_params = sum(p.numel() for p in model.parameters())
+    del model, items
+    torch.cuda.empty_cache()
+    peak_tf = 1373.9
+    try:
+        peak_tf = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops_sustained"])
+    except Exception:
+        pass
+    out = {"metric": "gptq_seconds_per_8b_model", "value": round(seconds * 32 / layers, 2) if layers != 32 else round(seconds, 2),
+           "unit": "s", "higher_is_better": False, "measured_seconds": round(seconds, 2), "decoder_layers_run": layers,
+           "config": {"workload": f"LlamaForCausalLM random init, Llama-3-8B architecture with {layers} of 32 decoder "
+                                  f"layers, bf16; {args.gptq_samples} x {args.gptq_tokens} calibration token ids (seed 3) "
+                                  "through the model; compress_weights(INT4_SYM, group 128, gptq=True, damp 0.01, block "
+                                  "128), embed_tokens / lm_head on the INT8_ASYM backup",
+                      "extrapolated": None if layers == 32 else f"value = measured x 32 / {layers} (per-layer work is identical)"},
+           "split_seconds": split, "model_build_seconds": round(t_build, 2), "outputs_finite": finite,
+           "weights_in_model": n_params}
+    tokens = args.gptq_samples * args.gptq_tokens
+    if split.get("hessians"):
+        # per decoder layer 3 Hessians over 4096 channels and 1 over 14336; the kernel multiplies the 128 x 256
+        # tiles that touch the upper triangle
+        def computed(C):
+            tm, tn = (C + 127) // 128, (C + 255) // 256
+            return 2.0 * tokens * sum(tn - mi // 2 for mi in range(tm)) * 128 * 256
+        flops = layers * (3 * computed(4096) + computed(14336))
+        tf = flops / split["hessians"] / 1e12
+        out["roofline"] = {"bound": "tensor", "kernel": "tc_tn_kernel<4 stages, Hessian> (tcgen05 / TMEM / TMA), inside the model run",
+                           "achieved": round(tf, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(tf / peak_tf, 4),
+                           "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops_sustained)",
+                           "flops": "computed tiles (upper triangle) of 3 x C=4096 + 1 x C=14336 Hessians per layer",
+                           "timed": "CUDA events around every accumulation call, summed"}
+    return out
+
+
+def run_compress(args, device, rank, world, local_rank, dist):
+    from nncf_b200.pipeline import CompressionPlan, HostStreamingCompressor, bind_host_thread_near, partition_by_bytes
+    from nncf_b200.sharding import ShardedCompression
+
+    # one process per GPU: keep this rank's pinned buffers and copy threads on the CPUs next to its GPU
+    cpus_at_start = os.sched_getaffinity(0)
+    affinity = bind_host_thread_near(device) if not args.no_affinity else "unchanged (--no-affinity)"
+    specs = model_specs()
+    if args.profile_case:
+        specs = specs[1:8]  # one decoder layer: 436 MB of weights, larger than L2
+        args.steps, args.no_e2e, args.no_cpu_baseline, args.no_gptq, args.no_parity = 1, True, True, True, True
+    sc = ShardedCompression(specs, device, rank, world, dst=0, n_chunks=args.chunks, dst_share=args.dst_share)
+    index_of = {s[0]: i for i, s in enumerate(specs)}
+    weights = {i: make_weight(specs[i][1], i if not args.profile_case else i + 1, device) for i in sc.local_indices}
+    sc.bind(weights)
+    plan = sc.plan
+    idx4 = [k for k, it in enumerate(plan.items) if it.config.num_bits == 4]
+    idx8 = [k for k, it in enumerate(plan.items) if it.config.num_bits == 8]
+    alg4 = sum(plan.items[k].algorithmic_bytes() for k in idx4)
+    src_total = sc.source_bytes_total
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    use_graph = world == 1 and not (args.no_graph or args.profile_case)
+    if world == 1:
+        if use_graph:
+            g4 = plan.capture(idx4)
+            g8 = plan.capture(idx8) if idx8 else None
+            run4 = g4.replay
+            run8 = g8.replay if g8 is not None else (lambda: None)
+        else:
+            run4 = lambda: plan.launch(idx4)  # noqa: E731
+            run8 = (lambda: plan.launch(idx8)) if idx8 else (lambda: None)  # noqa: E731
+
+        def step():
+            run4()
+            run8()
+        launches_per_step = 2 if idx8 else 1
+    else:
+        def step():
+            sc.run()
+            sc.wait()
+        launches_per_step = len(sc._chunk_items)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)] if world == 1 else None
+    t_begin.record()
+    for s_ in range(args.steps):
+        if world == 1:
+            ev[s_][0].record()
+            run4()
+            ev[s_][1].record()
+            run8()
+            ev[s_][2].record()
+        else:
+            step()
+    t_end.record()
+    barrier()
+    total_ms = t_begin.elapsed_time(t_end)
+    t = torch.tensor([total_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    value = src_total / (ms_per_step * 1e-3) / 1e9
+
+    # ---- the halves on their own (N > 1): kernels without transfers, transfers without kernels ------------
+    multi = None
+    if world == 1:
+        ms4 = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+        ms8 = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    else:
+        def timed(fn, reps):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            barrier()
+            return a.elapsed_time(b) / reps
+
+        own_ms = timed(lambda: sc.run(transfer=False), args.steps)
+        ms4 = timed(lambda: plan.launch(idx4), args.steps) if idx4 else 0.0
+        ms8 = 0.0
+
+        def transfer_only():
+            sc.run(compute=False)
+            sc.wait()
+        xfer_ms = timed(transfer_only, max(3, args.steps // 2))
+        tt = torch.tensor([own_ms, xfer_ms], dtype=torch.float64, device=device)
+        mx = tt.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        gathered = [torch.zeros_like(tt) for _ in range(world)]
+        dist.all_gather(gathered, tt)
+        compress_ms, gather_ms = float(mx[0]), float(mx[1])
+        multi = {
+            "partition": "ONE model split by source bytes (LPT greedy); the collecting rank's share is sized so that its "
+                         "own kernels and its NVLink ingest finish together",
+            "dst_share_of_source_bytes": round(sc.dst_share, 4),
+            "source_GB_per_rank": [round(sum(specs[i][1][0] * specs[i][1][1] * 2 for i in a) / 1e9, 3) for a in sc.assignment],
+            "chunks_per_sender": args.chunks,
+            "compress_only": {"ms_per_step_max_over_ranks": round(compress_ms, 4),
+                              "value": round(src_total / (compress_ms * 1e-3) / 1e9, 1),
+                              "ms_per_rank": [round(float(g[0]), 4) for g in gathered]},
+            "gather_only": {"ms_per_step": round(gather_ms, 4), "bytes_into_rank0": sc.output_bytes_total -
+                            sum(sc.out_sizes[i] for i in sc.assignment[0]),
+                            "ingest_GBps": round((sc.output_bytes_total - sum(sc.out_sizes[i] for i in sc.assignment[0])) /
+                                                 (gather_ms * 1e-3) / 1e9, 1)},
+            "gather_exposed_ms": round(ms_per_step - compress_ms, 4),
+            "bound_ms": round(max(compress_ms, gather_ms), 4),
+            "how": "per chunk one nncfb_quantize_batch launch, an event, one NCCL isend of the chunk's contiguous output "
+                   "range on a side stream; rank 0 posts irecvs straight into the final arena (no repacking, no manifest)",
+            "nccl_env": {k: v for k, v in os.environ.items() if k.startswith("NCCL_")},
+        }
+
+    if rank == 0 and not args.profile_case:
+        # the timed region lasts tens of milliseconds, less than one nvidia-smi sampling period: keep the same
+        # kernels running (untimed) for a moment so that the clock record is taken under this load
+        t_probe = time.time() + 0.7
+        while time.time() < t_probe:
+            for _ in range(10):
+                plan.launch()
+            torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "warm-up + timed region + 0.7 s of the same kernels"
+    if world > 1:
+        step()   # the probe loop overwrote nothing, but leave a complete pass behind for the parity gate
+    barrier()
+
+    # ---- parity gate on what the timed passes wrote ------------------------------------------------------
+    parity = None
+    if rank == 0 and not args.no_parity:
+        parity = parity_gate(specs, sc.results(), device)
+    barrier()
+
+    # ---- end to end through host buffers: the model split evenly over the ranks' PCIe links --------------
+    e2e = None
+    n_launch = args.steps * launches_per_step
+    if not args.no_e2e:
+        import psutil
+
+        sizes = [s[1][0] * s[1][1] * 2 for s in specs]
+        mine = partition_by_bytes(sizes, world)[rank]
+        out_sizes = sc.out_sizes
+        need = sum(sizes[i] + out_sizes[i] for i in mine)
+        budget = psutil.virtual_memory().available / (2.5 * max(world, 1)) * (1 if world == 1 else 1)
+        subset_note = None
+        if need > budget:
+            # keep whole decoder layers' tensors until the budget is used
+            keep, acc = [], 0
+            for i in sorted(mine, key=lambda i: -sizes[i]):
+                if acc + sizes[i] + out_sizes[i] <= budget:
+                    keep.append(i)
+                    acc += sizes[i] + out_sizes[i]
+            subset_note = f"{len(keep)} of this rank's {len(mine)} tensors (host memory budget per rank {budget / 1e9:.1f} GB)"
+            mine = keep
+        # largest tensors first, the order the reference compresses in (WC/algorithm.py:1198-1199): the copies that
+        # cannot overlap with anything (first tensor in, last result out) are then the cheap ones
+        mine = sorted(mine, key=lambda i: -sizes[i])
+        host_w = []
+        for i in mine:
+            h = torch.empty(specs[i][1], dtype=torch.bfloat16, pin_memory=True)
+            h.copy_(weights[i] if i in weights else make_weight(specs[i][1], i, device))
+            host_w.append(h)
+        torch.cuda.synchronize()
+        e2e_specs = [(specs[i][0], specs[i][1], specs[i][2], specs[i][3]) for i in mine]
+        del plan, weights
+        sc.plan, sc.arena = None, None
+        del sc
+        torch.cuda.empty_cache()
+        if e2e_specs:
+            hsc = HostStreamingCompressor(e2e_specs, device)
+            hsc.run(host_w)
+            hsc.synchronize()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.e2e_steps):
+                hsc.run(host_w)
+                hsc.synchronize()
+            barrier()
+            dt = (time.perf_counter() - t0) / args.e2e_steps
+            agg = torch.tensor([dt, float(hsc.h2d_bytes), float(hsc.d2h_bytes)], dtype=torch.float64, device=device)
+            if world > 1:
+                mx = agg.clone()
+                dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+                dist.all_reduce(agg, op=dist.ReduceOp.SUM)
+                dt = float(mx[0])
+            e2e = {"value": round(float(agg[1]) / dt / 1e9, 3), "unit": UNIT, "h2d_bytes_per_step": int(agg[1]),
+                   "d2h_bytes_per_step": int(agg[2]), "ms_per_step": round(dt * 1e3, 3), "steps": args.e2e_steps,
+                   "api": "nncf_b200.pipeline.HostStreamingCompressor.run (pinned host weights in, packed results "
+                          "back in pinned host memory; 3-stream overlap of H2D, kernels, D2H)",
+                   "split": "the one model's tensors split evenly by bytes over the ranks, each rank on its own PCIe link; "
+                            "bytes are totals over all ranks, time is the slowest rank's" if world > 1 else "single GPU",
+                   "host_affinity": affinity}
+            n_launch += (1 + args.e2e_steps) * len(e2e_specs)
+            if subset_note:
+                e2e["subset"] = subset_note
+            del hsc, host_w
+        else:
+            e2e = {"value": None, "unit": UNIT, "skipped": "not enough free host memory to pin even one tensor"}
+        torch.cuda.empty_cache()
+
+    # ---- GPTQ seconds per 8B model (the second half of the metric) ---------------------------------------
+    gptq = None
+    if not args.no_gptq and world == 1:
+        gptq = run_gptq_model(args, device, rank, world, dist)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = _peaks()
+    achieved = alg4 / (ms4 * 1e-3) / 1e9 if ms4 > 0 else 0.0
+    roofline = {
+        "bound": "hbm", "kernel": "quant_rows_batch_kernel<bf16, INT4_SYM, 8 lanes x 2 vectors per group, 4 groups in flight> "
+                                  "(one launch for all of this rank's 4-bit tensors)",
+        "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+        "peak_source": peak_src, "launches_per_step": 1, "tensors_per_launch": len(idx4), "avg_launch_us": round(ms4 * 1e3, 2),
+        "algorithmic_bytes_per_launch": alg4, "traffic": None,
+        "traffic_note": "not measured in this run (needs a profiler); an ncu capture of the same kernel on one decoder "
+                        "layer read DRAM bytes = 0.93 of the algorithmic bytes: part of the writes was still in L2",
+        "timed_on": "rank 0" if world > 1 else "the single GPU",
+    }
+    if world == 1:
+        roofline["int8_kernel"] = {"kernel": "quant_channel_batch_kernel<bf16, INT8_ASYM, 64 threads/row>", "ms_per_step": round(ms8, 4)}
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD if not args.profile_case else "profile case: one decoder layer (7 matrices, 436 MB)",
+                   "total_source_bytes": src_total,
+                   "value_is": "compress only (inputs resident in HBM)" if world == 1 else
+                               "compress + gather of every packed result on rank 0 (one model over all ranks)",
+                   "launch": "cuda-graph replay" if use_graph else "per-call launches",
+                   "l2": "inputs (16 GB per step over all ranks) exceed L2 (126 MB); no flush needed",
+                   "seed": "per tensor, from configuration seed 1 and the tensor's index", "distribution": "N(0, 0.02^2) bf16"},
+        "roofline": roofline, "e2e": e2e, "multi_gpu": multi, "parity": parity, "gptq": gptq,
+        "gpu_launches": n_launch, "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        os.sched_setaffinity(0, cpus_at_start)  # the CPU baseline gets every core the process started with
+        threads = host_threads()
+        gbs, dt, nbytes, kind, note = cpu_reference_sample(threads, 3, 1)
+        line["cpu_baseline"] = {
+            "value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": kind,
+            "sample": f"1/32 of the workload ({nbytes / 1e6:.0f} MB source: 1 decoder layer INT4_SYM g128 + 1/32 of "
+                      f"embed/lm_head rows INT8_ASYM), compress + pack, 3 timed passes after 1 warm-up; {note}",
+            "seconds_per_pass": round(dt, 3)}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -426,9 +818,19 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed passes' outputs")
+    ap.add_argument("--no-gptq", action="store_true", help="skip the GPTQ half of the metric")
+    ap.add_argument("--gptq-layers", type=int, default=32, help="decoder layers of the GPTQ model (32 = the whole model)")
+    ap.add_argument("--gptq-samples", type=int, default=128)
+    ap.add_argument("--gptq-tokens", type=int, default=2048)
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a graph")
-    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "data_aware", "moe", "api"],
-                    help="compress: the headline metric (default); gptq: the secondary GPTQ metric")
+    ap.add_argument("--chunks", type=int, default=4, help="N > 1: pieces a sender's work is cut into (one send each)")
+    ap.add_argument("--dst-share", type=float, default=None,
+                    help="N > 1: share of the source bytes the collecting rank compresses itself (default: balanced "
+                         "against its NVLink ingest)")
+    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "gptq_model", "data_aware", "moe", "api"],
+                    help="compress: the headline line (default); gptq: per-kernel GPTQ timings; gptq_model: only the "
+                         "GPTQ model run of the headline line")
     ap.add_argument("--mode", default="nf4", choices=["nf4", "mxfp4", "fp4"], help="mode of the moe workload")
     ap.add_argument("--layers", type=int, default=4, help="layers of the moe workload (32 = the full 90 GB stack)")
     ap.add_argument("--no-affinity", action="store_true", help="do not bind the process to the CPUs closest to its GPU")
@@ -449,6 +851,13 @@ def main():
     torch.cuda.set_device(device)
     import torch.distributed as dist
 
+    if world > 1:
+        # NCCL point-to-point transfers between two GPUs use few channels by default; the gather is one-to-one
+        # traffic into a single rank, so let every pair use all of them (set before the communicator exists;
+        # values already in the environment win)
+        os.environ.setdefault("NCCL_NCHANNELS_PER_PEER", "32")
+        os.environ.setdefault("NCCL_MIN_P2P_NCHANNELS", "32")
+        os.environ.setdefault("NCCL_MAX_P2P_NCHANNELS", "64")
     if args.workload == "moe":
         if world > 1:
             dist.init_process_group("nccl", device_id=device)
@@ -458,207 +867,17 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    if args.workload in ("gptq", "data_aware", "api"):
+    if args.workload in ("gptq", "data_aware", "api", "gptq_model"):
         if rank == 0:
-            {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload}[args.workload](
-                args, device)
+            if args.workload == "gptq_model":
+                print(json.dumps(run_gptq_model(args, device, rank, 1, dist)), flush=True)
+            else:
+                {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload}[args.workload](
+                    args, device)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-
-    from nncf_b200.pipeline import CompressionPlan, HostStreamingCompressor, bind_host_thread_near
-
-    # one process per GPU: keep this rank's pinned buffers and copy threads on the CPUs next to its GPU
-    cpus_at_start = os.sched_getaffinity(0)
-    affinity = bind_host_thread_near(device) if not args.no_affinity else "unchanged (--no-affinity)"
-    items = build_weight_set(device, seed=1 + rank)
-    if args.profile_case:
-        items = items[1:8]  # one decoder layer: 436 MB of weights, larger than L2
-        args.steps, args.no_e2e, args.no_cpu_baseline = 1, True, True
-    plan = CompressionPlan(items, device)
-    idx4 = [i for i, it in enumerate(plan.items) if it.config.num_bits == 4]
-    idx8 = [i for i, it in enumerate(plan.items) if it.config.num_bits == 8]
-    alg4 = sum(plan.items[i].algorithmic_bytes() for i in idx4)
-    n4, n_items = len(idx4), len(plan.items)
-    src_bytes, out_bytes = plan.source_bytes, plan.output_bytes
-    torch.cuda.synchronize()
-
-    if args.no_graph or args.profile_case:
-        run4 = lambda: plan.launch(idx4)  # noqa: E731
-        run8 = lambda: plan.launch(idx8)  # noqa: E731
-    else:
-        g4 = plan.capture(idx4)
-        g8 = plan.capture(idx8) if idx8 else None
-        run4 = g4.replay
-        run8 = g8.replay if g8 is not None else (lambda: None)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    for _ in range(args.warmup):
-        run4()
-        run8()
-    barrier()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_begin.record()
-    for s in range(args.steps):
-        ev[s][0].record()
-        run4()
-        ev[s][1].record()
-        run8()
-        ev[s][2].record()
-    t_end.record()
-    barrier()
-    if rank == 0 and not args.profile_case:
-        # the timed region lasts tens of milliseconds, less than one nvidia-smi sampling period: keep the same
-        # kernels running (untimed) for a moment so that the clock record is taken under this load
-        t_probe = time.time() + 0.7
-        while time.time() < t_probe:
-            for _ in range(10):
-                run4()
-                run8()
-            torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None:
-        clocks["window"] = "warm-up + timed region + 0.7 s of the same kernels"
-    barrier()
-    total_ms = t_begin.elapsed_time(t_end)
-    ms4 = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    ms8 = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
-    t = torch.tensor([total_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / args.steps
-    value = world * src_bytes / (ms_per_step * 1e-3) / 1e9
-
-    # ---- the one exchange step of the multi-GPU path: packed results to rank 0 (NCCL) ------------------
-    gather = None
-    if world > 1 and not args.profile_case:
-        from nncf_b200.sharding import gather_results
-
-        named = {f"r{rank}/{it.name}": it.output_tensors() for it in plan.items}
-        gather_results(named, dst=0)  # warm-up (communicator set-up)
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(3):
-            merged = gather_results(named, dst=0)
-            del merged
-        g1.record()
-        barrier()
-        gt = torch.tensor([g0.elapsed_time(g1) / 3], dtype=torch.float64, device=device)
-        dist.all_reduce(gt, op=dist.ReduceOp.MAX)
-        gms = float(gt.item())
-        gather = {"ms_per_step": round(gms, 3), "bytes_into_rank0": (world - 1) * out_bytes,
-                  "ingest_GBps": round((world - 1) * out_bytes / (gms * 1e-3) / 1e9, 1),
-                  "value_with_gather": round(world * src_bytes / ((ms_per_step + gms) * 1e-3) / 1e9, 2),
-                  "how": "torch.distributed isend/irecv (NCCL) of one flat buffer per rank, not overlapped with compute"}
-        del named
-        torch.cuda.empty_cache()
-
-    # ---- end to end through host buffers ---------------------------------------------------------
-    e2e = None
-    if not args.no_e2e:
-        import psutil
-
-        need = src_bytes + out_bytes
-        # every rank of the node pins its own buffers; if the whole set does not fit comfortably, the end-to-end
-        # run uses as many whole decoder layers as do (and says so)
-        budget = psutil.virtual_memory().available / (2.5 * max(world, 1))
-        e2e_items = list(plan.items)
-        subset_note = None
-        if need > budget:
-            per_layer = need * 218103808 / 8030261248  # one decoder layer (7 matrices) holds 218.1 M of 8.03 G params
-            n_layers = max(0, min(32, int(budget // per_layer)))
-            e2e_items = [it for it in plan.items if it.name.startswith("model.layers.") and
-                         int(it.name.split(".")[2]) < n_layers]
-            subset_note = f"first {n_layers} decoder layers only (host memory budget per rank {budget / 1e9:.1f} GB)"
-        if e2e_items:
-            # largest tensors first, the order the reference compresses in (WC/algorithm.py:1198-1199): the copies that
-            # cannot overlap with anything (first tensor in, last result out) are then the cheap ones
-            e2e_items = sorted(e2e_items, key=lambda it: -it.source_bytes)
-            e2e_src = sum(it.source_bytes for it in e2e_items)
-            specs = [(it.name, tuple(it.weight.shape), it.weight.dtype, it.config) for it in e2e_items]
-            host_w = []
-            for it in e2e_items:
-                h = torch.empty(it.weight.shape, dtype=it.weight.dtype, pin_memory=True)
-                h.copy_(it.weight)
-                host_w.append(h)
-            torch.cuda.synchronize()
-            del plan, items, e2e_items
-            torch.cuda.empty_cache()
-            hsc = HostStreamingCompressor(specs, device)
-            hsc.run(host_w)
-            hsc.synchronize()
-            barrier()
-            t0 = time.perf_counter()
-            for _ in range(args.e2e_steps):
-                hsc.run(host_w)
-                hsc.synchronize()
-            barrier()
-            dt = (time.perf_counter() - t0) / args.e2e_steps
-            tt = torch.tensor([dt], dtype=torch.float64, device=device)
-            if world > 1:
-                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            dt = float(tt.item())
-            e2e = {"value": round(world * e2e_src / dt / 1e9, 3), "unit": UNIT, "h2d_bytes_per_step": hsc.h2d_bytes,
-                   "d2h_bytes_per_step": hsc.d2h_bytes, "ms_per_step": round(dt * 1e3, 3), "steps": args.e2e_steps,
-                   "api": "nncf_b200.pipeline.HostStreamingCompressor.run (pinned host weights in, packed results "
-                          "back in pinned host memory; 3-stream overlap of H2D, kernels, D2H)"}
-            e2e["host_affinity"] = affinity
-            if subset_note:
-                e2e["subset"] = subset_note
-        else:
-            e2e = {"value": None, "unit": UNIT, "skipped": "not enough free host memory to pin even one decoder layer"}
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    peak, peak_src = _peaks()
-    achieved = alg4 / (ms4 * 1e-3) / 1e9
-    roofline = {
-        "bound": "hbm", "kernel": "quant_rows_batch_kernel<bf16, INT4_SYM, 8 lanes x 2 vectors per group, 4 groups in flight> (one launch for all 224 tensors)",
-        "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-        "peak_source": peak_src, "launches_per_step": 1, "tensors_per_launch": n4, "avg_launch_us": round(ms4 * 1e3, 2),
-        "algorithmic_bytes_per_step": alg4, "traffic": None,
-        "int8_kernel": {"kernel": "quant_channel_batch_kernel<bf16, INT8_ASYM, 64 threads/row>", "ms_per_step": round(ms8, 4)},
-    }
-    # DRAM traffic of the INT4 launch: dram__bytes_read + dram__bytes_write of one ncu capture of the same
-    # kernel on one decoder layer (profiles/quant_rows_batch_kernel_int4sym_g128_bf16_one_layer.md: 515.7 MB for
-    # 218.1 M elements = 2.364 B/element), scaled to this launch by its element count (traffic is proportional
-    # to the elements processed: every weight is read once and every code written once)
-    if not args.profile_case:
-        roofline["traffic"] = int(2.364 * alg4 / 2.53125)
-        roofline["traffic_source"] = "ncu capture of one decoder layer, scaled by elements"
-    line = {
-        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD if not args.profile_case else "profile case: one decoder layer (7 matrices, 436 MB)",
-                   "per_rank_source_bytes": src_bytes, "launch": "per-call" if (args.no_graph or args.profile_case) else "cuda-graph replay",
-                   "l2": "inputs (16 GB per step) exceed L2 (126 MB); no flush needed",
-                   "seed": "1 + rank", "distribution": "N(0, 0.02^2) bf16"},
-        "roofline": roofline, "e2e": e2e, "gather_to_rank0": gather, "gpu_launches": args.steps * 2, "clocks": clocks,
-    }
-    if world == 1 and not args.no_cpu_baseline:
-        os.sched_setaffinity(0, cpus_at_start)  # the CPU baseline gets every core the process started with
-        threads = host_threads()
-        gbs, dt, nbytes = cpu_reference_sample(threads, 3, 1)
-        line["cpu_baseline"] = {
-            "value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"1/32 of the workload ({nbytes / 1e6:.0f} MB source: 1 decoder layer INT4_SYM g128 + 1/32 of "
-                      f"embed/lm_head rows INT8_ASYM), compress + pack, 3 timed passes after 1 warm-up",
-            "seconds_per_pass": round(dt, 3)}
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    run_compress(args, device, rank, world, local_rank, dist)
 
 
 if __name__ == "__main__":

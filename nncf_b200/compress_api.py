@@ -64,6 +64,37 @@ class Dataset:
 LAYERWISE_REPLAY = True
 
 
+# Where the time of a model-level GPTQ run goes: seconds per phase ("hessians", "inverse_factors", "sweeps",
+# "total"; the calibration forward passes are the remainder), filled when COLLECT_TIMERS is set.  Phases are
+# bracketed by CUDA events on the current stream and resolved once at the end, so collecting them adds no
+# synchronisation.
+COLLECT_TIMERS = False
+TIMERS: dict = {}
+
+
+class _PhaseTimer:
+    def __init__(self, enabled: bool):
+        self.enabled = enabled
+        self.pairs: dict = {}
+
+    def start(self, key: str):
+        if not self.enabled:
+            return None
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        self.pairs.setdefault(key, []).append((a, b))
+        return b
+
+    @staticmethod
+    def stop(handle) -> None:
+        if handle is not None:
+            handle.record()
+
+    def resolve(self) -> dict:
+        torch.cuda.synchronize()
+        return {k: sum(a.elapsed_time(b) for a, b in v) / 1e3 for k, v in self.pairs.items()}
+
+
 def _run(model: nn.Module, item: Any) -> None:
     if isinstance(item, dict):
         model(**item)
@@ -491,17 +522,24 @@ def compress_weights(
                  scale_estimation=cfg["scale_estimation"])
         targets = [p for p in active if not p.is_embedding and p.compression_config.mode not in INT8_MODES]
         cal = items[: adv.gptq_params.subset_size]
+        timer = _PhaseTimer(COLLECT_TIMERS)
+        t_total = timer.start("total")
 
         def quantise_group(group, runners):
             """One Hessian for layers fed by the very same tensor (q/k/v, gate/up), one factorisation, then
             every layer of the group; weights are replaced only after the whole group saw the same inputs."""
-            H, layer_stat = _layer_hessian(runners, group[0].module, g, want_statistics=cfg["scale_estimation"])
+            H, layer_stat = _layer_hessian(runners, group[0].module, g, want_statistics=cfg["scale_estimation"],
+                                           timer=timer)
             hinv = None
             for p in group:
                 w = p.weight.data.float().contiguous()
                 if hinv is None:
+                    h = timer.start("inverse_factors")
                     hinv = g.prepare_hessian_inverse(H, w)
+                    timer.stop(h)
+                h = timer.start("sweeps")
                 q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat)
+                timer.stop(h)
                 precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
                 p._gptq_weight = q
             for p in group:
@@ -527,6 +565,12 @@ def compress_weights(
         for group in groups:  # layers outside the repeated blocks (or models without such blocks)
             if group[0].weight_name not in done:
                 quantise_group(group, [lambda item=item: _run(model, item) for item in cal])
+        timer.stop(t_total)
+        if COLLECT_TIMERS:
+            TIMERS.clear()
+            TIMERS.update(timer.resolve())
+            TIMERS["calibration_forward_and_host"] = TIMERS["total"] - sum(
+                TIMERS.get(k, 0.0) for k in ("hessians", "inverse_factors", "sweeps"))
     elif cfg["scale_estimation"]:
         se = adv.scale_estimation_params
         algo = ScaleEstimation(se.subset_size, se.initial_steps, se.scale_steps, se.weight_penalty)
@@ -568,7 +612,8 @@ def _same_input_groups(model: nn.Module, sample: Any, targets: list) -> list:
     return groups
 
 
-def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: bool = False):
+def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: bool = False,
+                   timer: Optional[_PhaseTimer] = None):
     """Hessian of one Linear's input over the calibration items, with every previously processed layer already
     holding its quantised weight (the semantics of the reference's layer-wise engine,
     src/nncf/quantization/algorithms/layerwise/openvino_iterator.py:183-231).  ``runners``: one callable per
@@ -587,7 +632,9 @@ def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: b
     def hook(mod, args):
         x = args[0]
         batch = x.shape[0] if x.ndim == 3 else 1
+        h = timer.start("hessians") if timer is not None else None
         state["n"] = g.accumulate_hessian(H, x, state["n"], batch)
+        _PhaseTimer.stop(h)
         if stat is not None:
             one = g.activations_to_wc_statistics([x])
             stat.mean_values.append(one.mean_values[0])

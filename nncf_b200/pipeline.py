@@ -65,6 +65,48 @@ class PlanItem:
         return n
 
 
+ARENA_ALIGN = 256  # every output starts on a 256-byte boundary inside an arena
+
+
+def _pad(n: int) -> int:
+    return (n + ARENA_ALIGN - 1) // ARENA_ALIGN * ARENA_ALIGN
+
+
+def stored_outputs(name: str, shape: Sequence[int], axis: int, cfg: WeightCompressionConfig,
+                   fp16_scales: bool = False) -> list[tuple[str, torch.dtype, int]]:
+    """(field, dtype, element count) of everything the stored form of one weight consists of, in the order the
+    plan allocates them.  Depends only on shape and configuration, so a rank can lay out another rank's results
+    without asking it."""
+    outer, reduce, inner = _split(tuple(shape), axis % len(shape))
+    gs = cfg.group_size if cfg.group_size != -1 else reduce
+    if reduce % gs != 0:
+        from .errors import InvalidGroupSizeError
+
+        msg = f"Channel size {reduce} should be divisible by size of group {gs}."
+        raise InvalidGroupSizeError(msg)
+    n, n_groups = outer * reduce * inner, outer * (reduce // gs) * inner
+    four_bit = cfg.num_bits == 4
+    nibble_ok = four_bit and n % 2 == 0 and ((inner > 1 and inner % 2 == 0) or (inner == 1 and gs % 2 == 0))
+    if four_bit and not nibble_ok:
+        msg = f"{name}: shape {tuple(shape)} cannot be nibble-packed in one pass"
+        raise ValueError(msg)
+    signed8 = cfg.is_integer and not cfg.is_asym_mode and not four_bit  # FP8 bit patterns are unsigned bytes
+    outs = [("packed", torch.int8 if signed8 else torch.uint8, n // 2 if four_bit else n),
+            ("scale", torch.float32, n_groups)]
+    if fp16_scales:
+        outs.append(("scale_f16", torch.float16, n_groups))
+    if cfg.is_integer and cfg.is_asym_mode:
+        outs.append(("zero_point", torch.int32, n_groups))
+    if cfg.mode in (CompressWeightsMode.MXFP4, CompressWeightsMode.MXFP8_E4M3):
+        outs.append(("scale_e8m0", torch.uint8, n_groups))
+    return outs
+
+
+def stored_bytes(outs: Sequence[tuple[str, torch.dtype, int]]) -> int:
+    """Bytes the outputs of one weight take in an arena (each padded to the arena alignment)."""
+    return sum(_pad(n * torch.empty(0, dtype=dt).element_size()) for _, dt, n in outs)
+
+
 def _split(shape: Sequence[int], axis: int) -> tuple[int, int, int]:
     outer = 1
     for d in shape[:axis]:
@@ -83,9 +125,16 @@ class CompressionPlan:
     offset), byte codes for 8-bit modes, fp32 scales [groups], int32 zero points for asymmetric modes,
     E8M0 exponent bytes for MX modes."""
 
-    def __init__(self, items: Sequence[tuple], device: Optional[torch.device] = None, fp16_scales: bool = False):
+    def __init__(self, items: Sequence[tuple], device: Optional[torch.device] = None, fp16_scales: bool = False,
+                 arena: Optional[torch.Tensor] = None, use_arena: bool = False):
+        """``use_arena``: put every output into one byte buffer (``self.arena``; ``arena`` supplies it), item after
+        item, each output on a 256-byte boundary - the results of any run of consecutive items are then one
+        contiguous range (``item_range``) that can be sent or copied with a single operation."""
         self.items: list[PlanItem] = []
         self.device = torch.device(device) if device is not None else None
+        self.arena = arena
+        self._use_arena = use_arena or arena is not None
+        self._arena_offsets: list[int] = []
         for it in items:
             name, weight, config = it[0], it[1], it[2]
             axis = it[3] if len(it) > 3 else -1
@@ -98,40 +147,50 @@ class CompressionPlan:
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._fp16_scales = fp16_scales
         self._arg_arrays: dict = {}
-        for item in self.items:
-            self._resolve(item)
+        self._layouts = [stored_outputs(it.name, it.weight.shape, it.reduction_axis, it.config, fp16_scales)
+                         for it in self.items]
+        if self._use_arena:
+            off = 0
+            for lay in self._layouts:
+                self._arena_offsets.append(off)
+                off += stored_bytes(lay)
+            self._arena_offsets.append(off)
+            if self.arena is None:
+                self.arena = torch.empty(off, dtype=torch.uint8, device=self.device)
+            elif self.arena.numel() < off or self.arena.dtype != torch.uint8 or not self.arena.is_contiguous():
+                msg = f"the arena must be a contiguous uint8 tensor of at least {off} bytes"
+                raise ValueError(msg)
+        for k, item in enumerate(self.items):
+            self._resolve(item, k)
 
-    def _resolve(self, item: PlanItem) -> None:
+    def item_range(self, first: int, last: int) -> tuple[int, int]:
+        """(offset, bytes) inside the arena of the outputs of items ``first`` .. ``last - 1``."""
+        return self._arena_offsets[first], self._arena_offsets[last] - self._arena_offsets[first]
+
+    def _resolve(self, item: PlanItem, k: int) -> None:
         w, cfg, dev = item.weight, item.config, self.device
         outer, reduce, inner = _split(tuple(w.shape), item.reduction_axis)
         gs = cfg.group_size if cfg.group_size != -1 else reduce
-        if reduce % gs != 0:
-            from .errors import InvalidGroupSizeError
-
-            msg = f"Channel size {reduce} should be divisible by size of group {gs}."
-            raise InvalidGroupSizeError(msg)
-        n, n_groups = w.numel(), outer * (reduce // gs) * inner
         four_bit = cfg.num_bits == 4
-        nibble_ok = four_bit and n % 2 == 0 and ((inner > 1 and inner % 2 == 0) or (inner == 1 and gs % 2 == 0))
-        if four_bit and not nibble_ok:
-            msg = f"{item.name}: shape {tuple(w.shape)} cannot be nibble-packed in one pass"
-            raise ValueError(msg)
-        signed8 = cfg.is_integer and not cfg.is_asym_mode and not four_bit  # FP8 bit patterns are unsigned bytes
-        item.packed = torch.empty(n // 2 if four_bit else n, dtype=torch.int8 if signed8 else torch.uint8, device=dev)
-        item.scale = torch.empty(n_groups, dtype=torch.float32, device=dev)
+        off = self._arena_offsets[k] if self._use_arena else 0
+        for field_name, dt, numel in self._layouts[k]:
+            if self._use_arena:
+                nb = numel * torch.empty(0, dtype=dt).element_size()
+                t = self.arena[off:off + nb].view(dt)
+                off += _pad(nb)
+            else:
+                t = torch.empty(numel, dtype=dt, device=dev)
+            setattr(item, field_name, t)
         a = _lib.QuantizeArgs()
         a.weight, a.weight_dtype, a.mode = w.data_ptr(), _lib.DTYPE_IDS[w.dtype], _lib.MODE_IDS[cfg.mode.value]
         a.outer, a.reduce, a.inner, a.group_size = outer, reduce, inner, gs
         a.codes_format = _lib.CODES_NIBBLE if four_bit else _lib.CODES_BYTE
         a.codes_out, a.scale_out = item.packed.data_ptr(), item.scale.data_ptr()
-        if self._fp16_scales:
-            item.scale_f16 = torch.empty(n_groups, dtype=torch.float16, device=dev)
+        if item.scale_f16 is not None:
             a.scale_f16_out = item.scale_f16.data_ptr()
-        if cfg.is_integer and cfg.is_asym_mode:
-            item.zero_point = torch.empty(n_groups, dtype=torch.int32, device=dev)
+        if item.zero_point is not None:
             a.zp_out = item.zero_point.data_ptr()
-        if cfg.mode in (CompressWeightsMode.MXFP4, CompressWeightsMode.MXFP8_E4M3):
-            item.scale_e8m0 = torch.empty(n_groups, dtype=torch.uint8, device=dev)
+        if item.scale_e8m0 is not None:
             a.scale_e8m0_out = item.scale_e8m0.data_ptr()
         item.args = a
 
@@ -180,16 +239,25 @@ class CompressionPlan:
         return sum(t.numel() * t.element_size() for i in self.items for t in i.output_tensors())
 
 
-def partition_by_bytes(sizes: Sequence[int], world_size: int) -> list[list[int]]:
-    """Longest-processing-time greedy split: indices sorted by size descending, each to the
-    currently lightest rank.  Deterministic, so every rank computes the same assignment.
+def partition_by_bytes(sizes: Sequence[int], world_size: int,
+                       capacity: Optional[Sequence[float]] = None) -> list[list[int]]:
+    """Longest-processing-time greedy split: indices sorted by size descending, each to the rank whose load,
+    relative to its capacity, is currently the lightest.  Deterministic, so every rank computes the same
+    assignment.  ``capacity`` (one positive weight per rank, default all equal) skews the split: a rank with
+    twice the capacity receives about twice the bytes - used to give the rank that collects the results more
+    of the compression work, since it need not send what it compresses itself.
     (The reference has no counterpart: it walks the weights sequentially,
     src/nncf/quantization/algorithms/weight_compression/algorithm.py:1198-1211.)"""
+    cap = [1.0] * world_size if capacity is None else [float(c) for c in capacity]
+    if len(cap) != world_size or any(c < 0 for c in cap) or not any(c > 0 for c in cap):
+        msg = f"capacity must hold {world_size} non-negative weights, not all zero"
+        raise ValueError(msg)
     order = sorted(range(len(sizes)), key=lambda i: (-sizes[i], i))
     loads = [0] * world_size
     parts: list[list[int]] = [[] for _ in range(world_size)]
+    usable = [k for k in range(world_size) if cap[k] > 0]
     for i in order:
-        r = min(range(world_size), key=lambda k: (loads[k], k))
+        r = min(usable, key=lambda k: ((loads[k] + sizes[i]) / cap[k], k))
         parts[r].append(i)
         loads[r] += sizes[i]
     for p in parts:

@@ -88,3 +88,115 @@ def test_gather_protocol_two_gloo_ranks(overlap):
         assert all(r[1] == "error" and "overlap" in r[2] for r in results), results
     else:
         assert all(r[1] == "ok" for r in results), results
+
+
+def test_weighted_partition_gives_the_collecting_rank_its_share():
+    sizes = [s[0] * s[1] * 2 for _, s in llama3_8b_weight_shapes()]
+    total = sum(sizes)
+    for world in (2, 4, 8):
+        share = 0.6
+        cap = [share] + [(1 - share) / (world - 1)] * (world - 1)
+        parts = partition_by_bytes(sizes, world, cap)
+        assert sorted(i for p in parts for i in p) == list(range(len(sizes)))
+        loads = [sum(sizes[i] for i in p) for p in parts]
+        assert abs(loads[0] / total - share) < 0.02
+        assert max(loads[1:]) - min(loads[1:]) <= max(sizes)
+    assert partition_by_bytes([4, 4, 4], 2, [1.0, 0.0]) == [[0, 1, 2], []]
+    with pytest.raises(ValueError):
+        partition_by_bytes([1], 2, [0.0, 0.0])
+
+
+class _HostPlan:
+    """Stand-in for CompressionPlan on CPU: same arena layout, and a "kernel" that fills every output of an item
+    with bytes that depend only on the item's name and the position, so any rank can predict any result."""
+
+    def __init__(self, items, arena):
+        from types import SimpleNamespace
+
+        from nncf_b200.pipeline import stored_bytes, stored_outputs
+
+        self.items = [SimpleNamespace(name=n, weight=w, config=c) for n, w, c in items]
+        self._layouts = [stored_outputs(n, w.shape, -1, c) for n, w, c in items]
+        offs = [0]
+        for lay in self._layouts:
+            offs.append(offs[-1] + stored_bytes(lay))
+        self._offs = offs
+        self.arena = arena if arena is not None else torch.zeros(offs[-1], dtype=torch.uint8)
+        for it, lay, off in zip(self.items, self._layouts, offs):
+            for field, dt, numel in lay:
+                nb = numel * torch.empty(0, dtype=dt).element_size()
+                setattr(it, field, self.arena[off:off + nb].view(dt))
+                off += (nb + 255) // 256 * 256
+
+    def item_range(self, first, last):
+        return self._offs[first], self._offs[last] - self._offs[first]
+
+    @staticmethod
+    def expected(name, field, numel, dt):
+        seed = sum(name.encode()) * 7 + len(field)
+        return ((torch.arange(numel, dtype=torch.int64) * 13 + seed) % 97).to(dt)
+
+    def launch(self, idx):
+        for k in idx:
+            for field, dt, numel in self._layouts[k]:
+                getattr(self.items[k], field).copy_(self.expected(self.items[k].name, field, numel, dt))
+
+
+def _sharded_worker(rank, world, port, dst_share, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nncf_b200 import CompressWeightsMode, WeightCompressionConfig
+        from nncf_b200.sharding import ShardedCompression
+
+        class HostSharded(ShardedCompression):
+            def _make_plan(self, items, arena):
+                return _HostPlan(items, arena)
+
+        i4 = WeightCompressionConfig(CompressWeightsMode.INT4_ASYM, 32)
+        i8 = WeightCompressionConfig(CompressWeightsMode.INT8_ASYM, -1)
+        mx = WeightCompressionConfig(CompressWeightsMode.MXFP4, 32)
+        specs = [(f"w{i}", shp, torch.bfloat16, cfg) for i, (shp, cfg) in enumerate(
+            [((64, 128), i8), ((16, 64), i4), ((48, 256), i4), ((8, 128), mx), ((32, 32), i4), ((24, 96), i4),
+             ((40, 64), mx), ((12, 160), i8), ((20, 32), i4)])]
+        sc = HostSharded(specs, "cpu", rank, world, dst=0, n_chunks=3, dst_share=dst_share)
+        # every rank derives the same assignment; the union of the shares is the model
+        assert sorted(i for a in sc.assignment for i in a) == list(range(len(specs)))
+        sc.bind({i: torch.zeros(specs[i][1], dtype=torch.bfloat16) for i in sc.local_indices})
+        for _ in range(2):   # a second pass reuses every buffer
+            sc.run()
+            sc.wait()
+        dist.barrier()
+        if rank == 0:
+            res = sc.results()
+            ok = sorted(res) == sorted(s[0] for s in specs)
+            for name, fields in res.items():
+                for field, t in fields.items():
+                    ok = ok and torch.equal(t, _HostPlan.expected(name, field, t.numel(), t.dtype))
+            received = sc.bytes_received_per_run
+            q.put((rank, "ok" if ok else "mismatch", received))
+        else:
+            q.put((rank, "ok", len(sc.local_indices)))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, "error", repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,dst_share", [(2, None), (2, 0.3), (3, 0.5)])
+def test_streamed_sharded_compression_collects_every_result_on_rank_0(world, dst_share):
+    """The streamed gather as gloo ranks on CPU with a host-side stand-in for the kernels: every rank lays out
+    every rank's results identically without exchanging a manifest, chunks are sent as they finish, and the
+    collecting rank ends up with every tensor of the model at its final position."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sharded_worker, args=(r, world, port, dst_share, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(r[1] == "ok" for r in results), results
+    assert [r for r in results if r[0] == 0][0][2] > 0   # something did cross between the ranks
