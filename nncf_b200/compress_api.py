@@ -62,6 +62,10 @@ class Dataset:
 # prefix for every layer.  False restores the plain form (one partial forward of the whole model per layer and
 # calibration item), which computes the same thing and is kept for models the block detection does not fit.
 LAYERWISE_REPLAY = True
+# With the block replay, run each block ONCE per micro-batch and pause it at every target layer until that layer
+# has been quantised, instead of re-running the block from its start for every layer (see _ResumableBlock).
+# False restores the re-running form; both give the same compressed model.
+RESUMABLE_REPLAY = True
 
 
 # Where the time of a model-level GPTQ run goes: seconds per phase ("hessians", "inverse_factors", "sweeps",
@@ -525,11 +529,14 @@ def compress_weights(
         timer = _PhaseTimer(COLLECT_TIMERS)
         t_total = timer.start("total")
 
-        def quantise_group(group, runners):
+        def quantise_group(group, runners=None, given=None):
             """One Hessian for layers fed by the very same tensor (q/k/v, gate/up), one factorisation, then
             every layer of the group; weights are replaced only after the whole group saw the same inputs."""
-            H, layer_stat = _layer_hessian(runners, group[0].module, g, want_statistics=cfg["scale_estimation"],
-                                           timer=timer)
+            if given is not None:
+                H, layer_stat = given
+            else:
+                H, layer_stat = _layer_hessian(runners, group[0].module, g, want_statistics=cfg["scale_estimation"],
+                                               timer=timer)
             hinv = None
             for p in group:
                 w = p.weight.data.float().contiguous()
@@ -557,10 +564,20 @@ def compress_weights(
             replay = _BlockReplay(model, blocks, cal)
             for bi, block in enumerate(blocks):
                 inside = {id(m) for m in block.modules()}
-                for group in groups:
-                    if id(group[0].module) in inside:
-                        quantise_group(group, replay.runners(bi))
-                        done.update(p.weight_name for p in group)
+                mine = [group for group in groups if id(group[0].module) in inside]
+                if RESUMABLE_REPLAY and mine:
+                    run = _ResumableBlock(replay, bi, [group[0].module for group in mine], g, cfg["scale_estimation"], timer)
+                    try:
+                        for gi, group in enumerate(mine):
+                            quantise_group(group, given=run.hessian(gi))
+                            done.update(p.weight_name for p in group)
+                        run.finish()
+                    finally:
+                        run.close()
+                    continue
+                for group in mine:
+                    quantise_group(group, replay.runners(bi))
+                    done.update(p.weight_name for p in group)
                 replay.advance(bi)
         for group in groups:  # layers outside the repeated blocks (or models without such blocks)
             if group[0].weight_name not in done:
@@ -624,7 +641,7 @@ def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: b
     C = module.in_features
     stat = WCTensorStatistic() if want_statistics else None
     H = torch.zeros(C, C, dtype=torch.float32, device=module.weight.device)
-    state = {"n": 0}
+    state = {"n": 0, "split": None}
 
     class _Stop(Exception):
         pass
@@ -636,15 +653,20 @@ def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: b
         state["n"] = g.accumulate_hessian(H, x, state["n"], batch)
         _PhaseTimer.stop(h)
         if stat is not None:
-            one = g.activations_to_wc_statistics([x])
-            stat.mean_values.append(one.mean_values[0])
-            stat.shape_values.append(one.shape_values[0])
+            # a micro-batch stacks several calibration items: statistics are per item
+            split = state["split"]
+            parts = x.split(split, 0) if split is not None and len(split) > 1 and sum(split) == x.shape[0] else [x]
+            for part in parts:
+                one = g.activations_to_wc_statistics([part])
+                stat.mean_values.append(one.mean_values[0])
+                stat.shape_values.append(one.shape_values[0])
         raise _Stop
 
     h = module.register_forward_pre_hook(hook)
     try:
         with torch.no_grad():
             for run in runners:
+                state["split"] = getattr(run, "split", None)
                 try:
                     run()
                 except _Stop:
@@ -675,40 +697,116 @@ def _decoder_blocks(model: nn.Module, targets: list) -> Optional[list]:
     return best[1] if best else None
 
 
-class _BlockReplay:
-    """Inputs of each repeated block for every calibration item, so that a block can be run on its own.
+def _same_value(a: Any, b: Any) -> bool:
+    """Whether two call arguments of different calibration items are interchangeable."""
+    if a is b:
+        return True
+    if isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor):
+        return a.shape == b.shape and a.dtype == b.dtype and bool(torch.equal(a, b))
+    if isinstance(a, (tuple, list)) and isinstance(b, (tuple, list)):
+        return len(a) == len(b) and all(_same_value(x, y) for x, y in zip(a, b))
+    if isinstance(a, torch.Tensor) or isinstance(b, torch.Tensor):
+        return False
+    try:
+        return bool(a == b)
+    except Exception:  # noqa: BLE001
+        return False
 
-    One forward pass per item records the positional and keyword arguments each block is called with.  The hidden
+
+class _BlockReplay:
+    """Inputs of each repeated block for the calibration items, so that a block can be run on its own.
+
+    The positional and keyword arguments each block is called with are recorded by forward pre-hooks.  The hidden
     state (first positional argument) is kept for the first block only; ``advance`` computes the next block's
     from the current block's output, i.e. through the weights the block holds at that moment.  Objects that
-    accumulate state across calls (key / value caches) are not replayed: they are replaced by None."""
+    accumulate state across calls (key / value caches) are not replayed: they are replaced by None.
 
-    def __init__(self, model: nn.Module, blocks: list, items: list):
+    Two things keep the cost of the replay near that of the arithmetic:
+    * Only the first item runs through the whole model.  If every block received the very same argument objects
+      as the first block (masks, position embeddings computed once and handed to every layer, as transformer
+      implementations do), the other items' forwards stop at the first block: its inputs are all that is needed.
+    * Items whose hidden states have one shape and whose other arguments are equal are stacked along the batch
+      axis into micro-batches of up to ``batch_tokens`` tokens, so a block runs a few large calls instead of one
+      small call per item.  A stacked activation [B, T, C] counts as B samples in the Hessian, exactly like a
+      batch in the reference (WC/gptq.py:229), and per-item statistics are taken from its B slices."""
+
+    class _Stop(Exception):
+        pass
+
+    def __init__(self, model: nn.Module, blocks: list, items: list, batch_tokens: int = 32768):
         self.blocks = blocks
-        self.calls: list = [[] for _ in blocks]   # per block, per item: (other positional args, kwargs, positional?)
-        first_hidden: list = []
+        per_item: list = []       # per item: (hidden of block 0, [per block: (rest, kwargs, positional?)])
+        state = {"stop_after_first": False, "record": None}
         handles = []
 
         def make(bi):
             def hook(mod, args, kwargs):
+                rec = state["record"]
                 if bi == 0:
-                    first_hidden.append((args[0] if args else kwargs["hidden_states"]).detach())
+                    rec["hidden"] = (args[0] if args else kwargs["hidden_states"]).detach()
                 kw = {k: (None if _is_stateful_cache(v) else v) for k, v in kwargs.items() if k != "hidden_states"}
                 if "use_cache" in kw:
                     kw["use_cache"] = False
-                self.calls[bi].append((tuple(args[1:]) if args else (), kw, bool(args)))
+                rec["calls"][bi] = (tuple(args[1:]) if args else (), kw, bool(args))
+                if bi == 0 and state["stop_after_first"]:
+                    raise _BlockReplay._Stop
             return hook
 
         for bi, b in enumerate(blocks):
             handles.append(b.register_forward_pre_hook(make(bi), with_kwargs=True))
         try:
             with torch.no_grad():
-                for item in items:
-                    _run(model, item)
+                for k, item in enumerate(items):
+                    state["record"] = {"hidden": None, "calls": [None] * len(blocks)}
+                    try:
+                        _run(model, item)
+                    except _BlockReplay._Stop:
+                        pass
+                    rec = state["record"]
+                    if state["stop_after_first"]:
+                        rec["calls"] = [rec["calls"][0]] * len(blocks)
+                    elif k == 0:
+                        first = rec["calls"][0]
+                        shared = all(c is not None and len(c[0]) == len(first[0]) and
+                                     all(x is y for x, y in zip(c[0], first[0])) and c[1].keys() == first[1].keys() and
+                                     all(c[1][n] is first[1][n] for n in first[1]) and c[2] == first[2]
+                                     for c in rec["calls"])
+                        state["stop_after_first"] = shared
+                    per_item.append(rec)
         finally:
             for h in handles:
                 h.remove()
-        self.hidden: list = first_hidden          # per item: input of the current block
+        # micro-batches of consecutive compatible items
+        self.hidden: list = []                    # per micro-batch: input of the current block
+        self.calls: list = [[] for _ in blocks]   # per block, per micro-batch
+        self.splits: list = []                    # per micro-batch: leading size of each stacked item
+        k = 0
+        while k < len(per_item):
+            group = [per_item[k]]
+            h0 = group[0]["hidden"]
+            limit = max(1, batch_tokens // max(1, h0.numel() // h0.shape[-1])) if h0.ndim == 3 else 1
+            while (k + len(group) < len(per_item) and len(group) < limit and
+                   self._stackable(group[0], per_item[k + len(group)])):
+                group.append(per_item[k + len(group)])
+            self.hidden.append(torch.cat([g["hidden"] for g in group], 0) if len(group) > 1 else h0)
+            self.splits.append([int(g["hidden"].shape[0]) for g in group])
+            for bi in range(len(blocks)):
+                self.calls[bi].append(group[0]["calls"][bi])
+            k += len(group)
+
+    @staticmethod
+    def _stackable(a: dict, b: dict) -> bool:
+        ha, hb = a["hidden"], b["hidden"]
+        if ha.ndim != 3 or ha.shape[1:] != hb.shape[1:] or ha.dtype != hb.dtype:
+            return False
+        for ca, cb in zip(a["calls"], b["calls"]):
+            if ca[2] != cb[2] or not _same_value(ca[0], cb[0]) or ca[1].keys() != cb[1].keys():
+                return False
+            if not all(_same_value(ca[1][n], cb[1][n]) for n in ca[1]):
+                return False
+            if ca is a["calls"][0] and all(c is ca for c in a["calls"]) and all(c is cb for c in b["calls"]):
+                break  # every block shares the first block's arguments: one comparison covers them all
+        return True
 
     def _call(self, bi: int, k: int):
         rest, kw, positional = self.calls[bi][k]
@@ -717,7 +815,12 @@ class _BlockReplay:
         return self.blocks[bi](hidden_states=self.hidden[k], **kw)
 
     def runners(self, bi: int) -> list:
-        return [lambda k=k: self._call(bi, k) for k in range(len(self.hidden))]
+        out = []
+        for k in range(len(self.hidden)):
+            fn = lambda k=k: self._call(bi, k)  # noqa: E731
+            fn.split = self.splits[k]
+            out.append(fn)
+        return out
 
     def advance(self, bi: int) -> None:
         """Replace the stored hidden states by block ``bi``'s outputs (the inputs of block ``bi + 1``)."""
@@ -725,6 +828,145 @@ class _BlockReplay:
             for k in range(len(self.hidden)):
                 out = self._call(bi, k)
                 self.hidden[k] = (out[0] if isinstance(out, (tuple, list)) else out).detach()
+
+
+class _ResumableBlock:
+    """One forward pass of a block per micro-batch, paused at the first layer of every target group.
+
+    Quantising the layers of a block one group after another (q/k/v, then o, then gate/up, then down) needs, for
+    each group, the group's input computed through the already quantised layers before it.  Re-running the block
+    from its start for every group repeats the work of the earlier layers (about 2.5 block passes per block
+    including the final pass that produces the next block's inputs).  Here every micro-batch's forward runs in a
+    thread of its own that is used as a coroutine: a forward pre-hook on the group's first layer accumulates
+    the Hessian from the layer's input and hands control back; when all micro-batches are waiting at that
+    layer, the caller quantises the group and resumes them, and the forwards continue through the new weights.
+    After the last group they run to the end, and their outputs are the next block's inputs: one block pass
+    per block in total.  Exactly one thread (or the caller) runs at any time, in a fixed order, so results do
+    not depend on thread scheduling.  The paused forwards keep their intermediate tensors alive: a few GB at
+    32 K tokens per micro-batch."""
+
+    class _Abort(Exception):
+        pass
+
+    def __init__(self, replay: "_BlockReplay", bi: int, leaders: list, g: GPTQ, want_statistics: bool,
+                 timer: Optional["_PhaseTimer"]):
+        import threading
+
+        self.replay, self.bi, self.g, self.timer = replay, bi, g, timer
+        self.leaders = leaders
+        self.K = len(replay.hidden)
+        dev = leaders[0].weight.device
+        self.H = [torch.zeros(m.in_features, m.in_features, dtype=torch.float32, device=dev) for m in leaders]
+        self.n = [0] * len(leaders)
+        self.stats = [WCTensorStatistic() if want_statistics else None for _ in leaders]
+        self.position = [-1] * self.K         # index of the group a micro-batch is paused at
+        self.outputs: list = [None] * self.K
+        self.errors: list = []
+        self.abort = False
+        self.current = threading.local()
+        self.go = [threading.Semaphore(0) for _ in range(self.K)]
+        self.back = threading.Semaphore(0)
+        self.stream = torch.cuda.current_stream(dev) if dev.type == "cuda" else None
+        self.device = dev
+        self.handles = [m.register_forward_pre_hook(self._make_hook(gi)) for gi, m in enumerate(leaders)]
+        self.threads = [threading.Thread(target=self._body, args=(k,), daemon=True) for k in range(self.K)]
+        for t in self.threads:
+            t.start()
+
+    def _make_hook(self, gi: int):
+        def hook(mod, args):
+            k = getattr(self.current, "k", None)
+            if k is None:      # a call from outside the replay (never happens while the block is being processed)
+                return
+            x = args[0]
+            batch = x.shape[0] if x.ndim == 3 else 1
+            h = self.timer.start("hessians") if self.timer is not None else None
+            self.n[gi] = self.g.accumulate_hessian(self.H[gi], x, self.n[gi], batch)
+            _PhaseTimer.stop(h)
+            if self.stats[gi] is not None:
+                split = self.replay.splits[k]
+                parts = x.split(split, 0) if len(split) > 1 and sum(split) == x.shape[0] else [x]
+                for part in parts:
+                    one = self.g.activations_to_wc_statistics([part])
+                    self.stats[gi].mean_values.append(one.mean_values[0])
+                    self.stats[gi].shape_values.append(one.shape_values[0])
+            self.position[k] = gi
+            self.back.release()        # control back to the caller ...
+            self.go[k].acquire()       # ... until it resumes this micro-batch
+            if self.abort:
+                raise _ResumableBlock._Abort
+        return hook
+
+    def _body(self, k: int) -> None:
+        self.go[k].acquire()
+        try:
+            if self.abort:
+                return
+            self.current.k = k
+            with torch.no_grad():
+                if self.stream is not None:
+                    with torch.cuda.device(self.device), torch.cuda.stream(self.stream):
+                        out = self.replay._call(self.bi, k)
+                else:
+                    out = self.replay._call(self.bi, k)
+            self.outputs[k] = (out[0] if isinstance(out, (tuple, list)) else out).detach()
+            self.position[k] = len(self.leaders)
+        except _ResumableBlock._Abort:
+            pass
+        except BaseException as exc:  # noqa: BLE001 - reported to the caller, which raises it
+            self.errors.append(exc)
+        finally:
+            self.back.release()
+
+    def _resume(self, k: int) -> None:
+        self.go[k].release()
+        if not self.back.acquire(timeout=600):
+            self.close()
+            msg = "a block forward did not come back within 10 minutes"
+            raise RuntimeError(msg)
+        if self.errors:
+            err = self.errors[0]
+            self.close()
+            raise err
+
+    def hessian(self, gi: int):
+        """Run every micro-batch up to group ``gi``'s first layer; returns (H, statistics or None)."""
+        for k in range(self.K):
+            self._resume(k)
+            if self.position[k] != gi:
+                self.close()
+                msg = (f"micro-batch {k} stopped at group {self.position[k]} instead of {gi}: the block does not call "
+                       "its layers in the order they were found")
+                raise RuntimeError(msg)
+        from . import _lib
+
+        if self.device.type == "cuda":
+            with torch.cuda.device(self.device):
+                _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(self.device)))
+        return self.H[gi], self.stats[gi]
+
+    def finish(self) -> None:
+        """Run every micro-batch to the end of the block and store the outputs as the next block's inputs."""
+        for k in range(self.K):
+            self._resume(k)
+            if self.position[k] != len(self.leaders):
+                self.close()
+                msg = f"micro-batch {k} reached a target layer a second time"
+                raise RuntimeError(msg)
+        self.close()
+        for k in range(self.K):
+            self.replay.hidden[k] = self.outputs[k]
+
+    def close(self) -> None:
+        self.abort = True
+        for h in self.handles:
+            h.remove()
+        self.handles = []
+        for k, t in enumerate(self.threads):
+            if t.is_alive():
+                self.go[k].release()
+        for t in self.threads:
+            t.join(timeout=60)
 
 
 def _is_stateful_cache(v: Any) -> bool:

@@ -144,9 +144,15 @@ def test_block_replay_reproduces_the_model_block_by_block():
     assert blocks is not None and [id(b) for b in blocks] == [id(b) for b in model.layers]
     assert api._decoder_blocks(model, [SimpleNamespace(module=model.out)]) is None
     items = [torch.randn(2, 4), torch.randn(3, 4)]
-    replay = api._BlockReplay(model, blocks, items)
-    calls_after_capture = model.cache.calls
+    with torch.no_grad():
+        for item in items:
+            model(item)
     want = [model.trace[0:3], model.trace[3:6]]
+    replay = api._BlockReplay(model, blocks, items)
+    # every block got the very same argument objects as the first one, so only the first item ran through the
+    # whole model; the second one stopped at the first block
+    assert len(model.trace) == 6 + 3
+    calls_after_capture = model.cache.calls
     for bi in range(3):
         outs = [run() for run in replay.runners(bi)]
         for k in range(2):
@@ -159,6 +165,19 @@ def test_block_replay_reproduces_the_model_block_by_block():
     replay2 = api._BlockReplay(model, blocks, items)
     out0 = replay2.runners(0)[0]()[0]
     assert not torch.allclose(out0, want[0][0])
+    # items of one shape [1, T, C] whose other arguments are equal are stacked into micro-batches of at most
+    # `batch_tokens` tokens; a stacked call equals the separate calls, and the runner says how to split it
+    seq = [torch.randn(1, 5, 4) for _ in range(5)]
+    single = api._BlockReplay(model, blocks, seq, batch_tokens=1)
+    stacked = api._BlockReplay(model, blocks, seq, batch_tokens=10)
+    assert [len(s) for s in single.splits] == [1] * 5 and [len(s) for s in stacked.splits] == [2, 2, 1]
+    for bi in range(3):
+        a = torch.cat([run()[0] for run in single.runners(bi)], 0)
+        b = torch.cat([run()[0] for run in stacked.runners(bi)], 0)
+        torch.testing.assert_close(a, b)
+        assert [r.split for r in stacked.runners(bi)] == [[1, 1], [1, 1], [1]]
+        single.advance(bi)
+        stacked.advance(bi)
 
 
 def test_tied_weights_are_listed_once_and_the_last_layer_counts_as_skipped():
