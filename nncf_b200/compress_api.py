@@ -80,23 +80,32 @@ class _PhaseTimer:
     def __init__(self, enabled: bool):
         self.enabled = enabled
         self.pairs: dict = {}
+        self.host: dict = {}
 
     def start(self, key: str):
         if not self.enabled:
             return None
+        import time
+
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         self.pairs.setdefault(key, []).append((a, b))
-        return b
+        return (b, self.host, key, time.perf_counter())
 
     @staticmethod
     def stop(handle) -> None:
         if handle is not None:
-            handle.record()
+            import time
+
+            b, host, key, t0 = handle
+            b.record()
+            host[key] = host.get(key, 0.0) + time.perf_counter() - t0   # time the host spent issuing the phase
 
     def resolve(self) -> dict:
         torch.cuda.synchronize()
-        return {k: sum(a.elapsed_time(b) for a, b in v) / 1e3 for k, v in self.pairs.items()}
+        out = {k: sum(a.elapsed_time(b) for a, b in v) / 1e3 for k, v in self.pairs.items()}
+        out.update({"host_" + k: v for k, v in self.host.items()})
+        return out
 
 
 def _run(model: nn.Module, item: Any) -> None:
@@ -561,24 +570,32 @@ def compress_weights(
             # inputs of the first repeated block are captured once; each block is then replayed on its own on the
             # outputs of the already-quantised block before it, instead of re-running the whole prefix of the
             # model for every layer.
+            h = timer.start("capture_block_inputs")
             replay = _BlockReplay(model, blocks, cal)
-            for bi, block in enumerate(blocks):
-                inside = {id(m) for m in block.modules()}
-                mine = [group for group in groups if id(group[0].module) in inside]
-                if RESUMABLE_REPLAY and mine:
-                    run = _ResumableBlock(replay, bi, [group[0].module for group in mine], g, cfg["scale_estimation"], timer)
-                    try:
-                        for gi, group in enumerate(mine):
-                            quantise_group(group, given=run.hessian(gi))
-                            done.update(p.weight_name for p in group)
-                        run.finish()
-                    finally:
-                        run.close()
-                    continue
-                for group in mine:
-                    quantise_group(group, replay.runners(bi))
-                    done.update(p.weight_name for p in group)
-                replay.advance(bi)
+            timer.stop(h)
+            workers = _ReplayWorkers(len(replay.hidden), targets[0].weight.device) if RESUMABLE_REPLAY else None
+            try:
+                for bi, block in enumerate(blocks):
+                    inside = {id(m) for m in block.modules()}
+                    mine = [group for group in groups if id(group[0].module) in inside]
+                    if workers is not None and mine:
+                        run = _ResumableBlock(workers, replay, bi, [group[0].module for group in mine], g,
+                                              cfg["scale_estimation"], timer)
+                        try:
+                            for gi, group in enumerate(mine):
+                                quantise_group(group, given=run.hessian(gi))
+                                done.update(p.weight_name for p in group)
+                            run.finish()
+                        finally:
+                            run.close()
+                        continue
+                    for group in mine:
+                        quantise_group(group, replay.runners(bi))
+                        done.update(p.weight_name for p in group)
+                    replay.advance(bi)
+            finally:
+                if workers is not None:
+                    workers.close()
         for group in groups:  # layers outside the repeated blocks (or models without such blocks)
             if group[0].weight_name not in done:
                 quantise_group(group, [lambda item=item: _run(model, item) for item in cal])
@@ -588,6 +605,8 @@ def compress_weights(
             TIMERS.update(timer.resolve())
             TIMERS["calibration_forward_and_host"] = TIMERS["total"] - sum(
                 TIMERS.get(k, 0.0) for k in ("hessians", "inverse_factors", "sweeps"))
+            if "block_segments" in TIMERS:
+                TIMERS["block_forward"] = TIMERS["block_segments"] - TIMERS.get("hessians", 0.0)
     elif cfg["scale_estimation"]:
         se = adv.scale_estimation_params
         algo = ScaleEstimation(se.subset_size, se.initial_steps, se.scale_steps, se.weight_penalty)
@@ -830,6 +849,59 @@ class _BlockReplay:
                 self.hidden[k] = (out[0] if isinstance(out, (tuple, list)) else out).detach()
 
 
+class _ReplayWorkers:
+    """A fixed set of threads that serve as coroutines for the paused block forwards, one per micro-batch, kept
+    for the whole compression call: libraries keep per-thread state (BLAS handles and their workspaces), which
+    is expensive to set up again for every block."""
+
+    def __init__(self, count: int, device: torch.device):
+        import threading
+
+        self.device = device
+        self.stream = torch.cuda.current_stream(device) if device.type == "cuda" else None
+        self.go = [threading.Semaphore(0) for _ in range(count)]
+        self.back = threading.Semaphore(0)
+        self.local = threading.local()
+        self.job = None          # the _ResumableBlock being served
+        self.closed = False
+        self.threads = [threading.Thread(target=self._serve, args=(k,), daemon=True) for k in range(count)]
+        for t in self.threads:
+            t.start()
+
+    def _serve(self, k: int) -> None:
+        self.local.k = k
+        while True:
+            self.go[k].acquire()
+            if self.closed:
+                return
+            job = self.job
+            try:
+                if not job.abort:
+                    with torch.no_grad():
+                        if self.stream is not None:
+                            with torch.cuda.device(self.device), torch.cuda.stream(self.stream):
+                                out = job.replay._call(job.bi, k)
+                        else:
+                            out = job.replay._call(job.bi, k)
+                    job.outputs[k] = (out[0] if isinstance(out, (tuple, list)) else out).detach()
+                    job.position[k] = len(job.leaders)
+            except _ResumableBlock._Abort:
+                pass
+            except BaseException as exc:  # noqa: BLE001 - reported to the caller, which raises it
+                job.errors.append(exc)
+            finally:
+                job.running[k] = False
+                self.back.release()
+
+    def close(self) -> None:
+        self.closed = True
+        for k, t in enumerate(self.threads):
+            if t.is_alive():
+                self.go[k].release()
+        for t in self.threads:
+            t.join(timeout=60)
+
+
 class _ResumableBlock:
     """One forward pass of a block per micro-batch, paused at the first layer of every target group.
 
@@ -848,35 +920,28 @@ class _ResumableBlock:
     class _Abort(Exception):
         pass
 
-    def __init__(self, replay: "_BlockReplay", bi: int, leaders: list, g: GPTQ, want_statistics: bool,
-                 timer: Optional["_PhaseTimer"]):
-        import threading
-
-        self.replay, self.bi, self.g, self.timer = replay, bi, g, timer
+    def __init__(self, workers: _ReplayWorkers, replay: "_BlockReplay", bi: int, leaders: list, g: GPTQ,
+                 want_statistics: bool, timer: Optional["_PhaseTimer"]):
+        self.workers, self.replay, self.bi, self.g, self.timer = workers, replay, bi, g, timer
         self.leaders = leaders
         self.K = len(replay.hidden)
         dev = leaders[0].weight.device
+        self.device = dev
         self.H = [torch.zeros(m.in_features, m.in_features, dtype=torch.float32, device=dev) for m in leaders]
         self.n = [0] * len(leaders)
         self.stats = [WCTensorStatistic() if want_statistics else None for _ in leaders]
         self.position = [-1] * self.K         # index of the group a micro-batch is paused at
+        self.running = [False] * self.K       # its forward has been started and has not ended
         self.outputs: list = [None] * self.K
         self.errors: list = []
         self.abort = False
-        self.current = threading.local()
-        self.go = [threading.Semaphore(0) for _ in range(self.K)]
-        self.back = threading.Semaphore(0)
-        self.stream = torch.cuda.current_stream(dev) if dev.type == "cuda" else None
-        self.device = dev
+        workers.job = self
         self.handles = [m.register_forward_pre_hook(self._make_hook(gi)) for gi, m in enumerate(leaders)]
-        self.threads = [threading.Thread(target=self._body, args=(k,), daemon=True) for k in range(self.K)]
-        for t in self.threads:
-            t.start()
 
     def _make_hook(self, gi: int):
         def hook(mod, args):
-            k = getattr(self.current, "k", None)
-            if k is None:      # a call from outside the replay (never happens while the block is being processed)
+            k = getattr(self.workers.local, "k", None)
+            if k is None or self.workers.job is not self:   # a call from outside the replay
                 return
             x = args[0]
             batch = x.shape[0] if x.ndim == 3 else 1
@@ -891,36 +956,19 @@ class _ResumableBlock:
                     self.stats[gi].mean_values.append(one.mean_values[0])
                     self.stats[gi].shape_values.append(one.shape_values[0])
             self.position[k] = gi
-            self.back.release()        # control back to the caller ...
-            self.go[k].acquire()       # ... until it resumes this micro-batch
+            self.workers.back.release()        # control back to the caller ...
+            self.workers.go[k].acquire()       # ... until it resumes this micro-batch
             if self.abort:
                 raise _ResumableBlock._Abort
         return hook
 
-    def _body(self, k: int) -> None:
-        self.go[k].acquire()
-        try:
-            if self.abort:
-                return
-            self.current.k = k
-            with torch.no_grad():
-                if self.stream is not None:
-                    with torch.cuda.device(self.device), torch.cuda.stream(self.stream):
-                        out = self.replay._call(self.bi, k)
-                else:
-                    out = self.replay._call(self.bi, k)
-            self.outputs[k] = (out[0] if isinstance(out, (tuple, list)) else out).detach()
-            self.position[k] = len(self.leaders)
-        except _ResumableBlock._Abort:
-            pass
-        except BaseException as exc:  # noqa: BLE001 - reported to the caller, which raises it
-            self.errors.append(exc)
-        finally:
-            self.back.release()
-
     def _resume(self, k: int) -> None:
-        self.go[k].release()
-        if not self.back.acquire(timeout=600):
+        h = self.timer.start("block_segments") if self.timer is not None else None   # includes the Hessian step
+        self.running[k] = True if self.position[k] == -1 else self.running[k]
+        self.workers.go[k].release()
+        ok = self.workers.back.acquire(timeout=600)
+        _PhaseTimer.stop(h)
+        if not ok:
             self.close()
             msg = "a block forward did not come back within 10 minutes"
             raise RuntimeError(msg)
@@ -958,15 +1006,15 @@ class _ResumableBlock:
             self.replay.hidden[k] = self.outputs[k]
 
     def close(self) -> None:
+        """Remove the hooks; forwards that are still paused are resumed with the abort flag and unwind."""
         self.abort = True
         for h in self.handles:
             h.remove()
         self.handles = []
-        for k, t in enumerate(self.threads):
-            if t.is_alive():
-                self.go[k].release()
-        for t in self.threads:
-            t.join(timeout=60)
+        for k in range(self.K):
+            if self.running[k]:
+                self.workers.go[k].release()
+                self.workers.back.acquire(timeout=60)
 
 
 def _is_stateful_cache(v: Any) -> bool:

@@ -214,3 +214,80 @@ def test_tied_weights_are_listed_once_and_the_last_layer_counts_as_skipped():
     assert not plain.is_last_layer_skipped
     assert [p.weight_name for p in _ratio_defining(plain, CompressWeightsMode.INT4_SYM, False)] == ["a", "b"]
     assert [p.weight_name for p in _ratio_defining(plain, CompressWeightsMode.INT4_SYM, True)] == ["a", "b", "head", "embed"]
+
+
+def test_resumable_block_pauses_at_every_target_and_continues_through_new_weights():
+    """One forward per micro-batch, paused at each target layer: the Hessians equal those of separate partial
+    runs, a weight replaced while the forwards are paused is the one they continue through, the outputs become
+    the next block's inputs, and an error inside a forward reaches the caller."""
+    try:
+        from nncf_b200 import compress_api as api
+    except Exception as exc:  # noqa: BLE001
+        pytest.skip(f"nncf_b200 cannot be imported here: {exc}")
+    from torch import nn
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(8, 8, bias=False)
+            self.b = nn.Linear(8, 8, bias=False)
+
+        def forward(self, hidden_states):
+            return hidden_states + self.b(torch.tanh(self.a(hidden_states)))
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Block(), Block()])
+
+        def forward(self, x):
+            for layer in self.layers:
+                x = layer(x)
+            return x
+
+    class StubGPTQ:   # the running Hessian of WC/gptq.py:229-236 in plain torch
+        def accumulate_hessian(self, H, x, n, batch):
+            x = x.reshape(-1, H.shape[-1]).float()
+            H.mul_(n / (n + batch)).add_((2.0 / (n + batch)) * (x.T @ x))
+            return n + batch
+
+    torch.manual_seed(0)
+    model = Model()
+    items = [torch.randn(1, 5, 8) for _ in range(5)]
+    replay = api._BlockReplay(model, list(model.layers), items, batch_tokens=10)   # micro-batches of 2, 2, 1 items
+    inputs = [h.clone() for h in replay.hidden]
+    workers = api._ReplayWorkers(len(replay.hidden), torch.device("cpu"))
+    try:
+        block = model.layers[0]
+        run = api._ResumableBlock(workers, replay, 0, [block.a, block.b], StubGPTQ(), False, None)
+        Ha, _ = run.hessian(0)
+        xa = torch.cat(inputs, 0).reshape(-1, 8)
+        torch.testing.assert_close(Ha, (2.0 / 5) * (xa.T @ xa))
+        with torch.no_grad():
+            block.a.weight.mul_(0.5)               # "quantise" the first layer while the forwards are paused
+        Hb, _ = run.hessian(1)
+        xb = torch.tanh(block.a(xa))
+        torch.testing.assert_close(Hb, (2.0 / 5) * (xb.T @ xb))
+        with torch.no_grad():
+            block.b.weight.mul_(2.0)
+        run.finish()
+        with torch.no_grad():
+            want = [block(h) for h in inputs]
+        for got, w in zip(replay.hidden, want):
+            torch.testing.assert_close(got, w)
+        # second block: an exception raised inside a paused forward surfaces in the caller, nothing is left hanging
+        block2 = model.layers[1]
+
+        def boom(mod, args):
+            raise ValueError("broken layer")
+
+        handle = block2.b.register_forward_pre_hook(boom)
+        run2 = api._ResumableBlock(workers, replay, 1, [block2.a], StubGPTQ(), False, None)
+        run2.hessian(0)
+        with pytest.raises(ValueError, match="broken layer"):
+            run2.finish()
+        handle.remove()
+        assert not any(run2.running)
+    finally:
+        workers.close()
+    assert not any(t.is_alive() for t in workers.threads)
