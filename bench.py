@@ -501,11 +501,17 @@ def run_gptq_model(args, device, rank, world, dist):
                                                                                 subset_size=args.gptq_samples))
     compress_api.COLLECT_TIMERS = True
     compress_api.TIMERS.clear()
+    group = dist.group.WORLD if world > 1 else None
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_SYM, group_size=128, ratio=1.0, gptq=True,
-                        dataset=nb.Dataset(items), subset_size=args.gptq_samples, advanced_parameters=adv)
+                        dataset=nb.Dataset(items), subset_size=args.gptq_samples, advanced_parameters=adv,
+                        process_group=group)
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     seconds = time.perf_counter() - t0
     with torch.no_grad():
         finite = bool(torch.isfinite(model(input_ids=items[0]["input_ids"][:, :128]).logits).all())
@@ -526,7 +532,10 @@ def run_gptq_model(args, device, rank, world, dist):
                                   "128), embed_tokens / lm_head on the INT8_ASYM backup",
                       "extrapolated": None if layers == 32 else f"value = measured x 32 / {layers} (per-layer work is identical)"},
            "split_seconds": split, "model_build_seconds": round(t_build, 2), "outputs_finite": finite,
-           "weights_in_model": n_params}
+           "weights_in_model": n_params, "n_gpus": world,
+           "sharing": None if world == 1 else "calibration items shared among the ranks (Hessians all-reduced), one inverse "
+                                              "factor (rank 0's), rows of every weight swept by different ranks and all-gathered; "
+                                              "split_seconds are rank 0's"}
     tokens = args.gptq_samples * args.gptq_tokens
     if split.get("hessians"):
         # per decoder layer 3 Hessians over 4096 channels and 1 over 14336; the kernel multiplies the 128 x 256
@@ -534,7 +543,7 @@ def run_gptq_model(args, device, rank, world, dist):
         def computed(C):
             tm, tn = (C + 127) // 128, (C + 255) // 256
             return 2.0 * tokens * sum(tn - mi // 2 for mi in range(tm)) * 128 * 256
-        flops = layers * (3 * computed(4096) + computed(14336))
+        flops = layers * (3 * computed(4096) + computed(14336)) / world   # this rank's share of the tokens
         tf = flops / split["hessians"] / 1e12
         out["roofline"] = {"bound": "tensor", "kernel": "tc_tn_kernel<4 stages, Hessian> (tcgen05 / TMEM / TMA), inside the model run",
                            "achieved": round(tf, 1), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(tf / peak_tf, 4),
@@ -759,7 +768,7 @@ def run_compress(args, device, rank, world, local_rank, dist):
 
     # ---- GPTQ seconds per 8B model (the second half of the metric) ---------------------------------------
     gptq = None
-    if not args.no_gptq and world == 1:
+    if not args.no_gptq:
         gptq = run_gptq_model(args, device, rank, world, dist)
     if rank != 0:
         if world > 1:
@@ -867,13 +876,19 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    if args.workload in ("gptq", "data_aware", "api", "gptq_model"):
+    if args.workload == "gptq_model":
+        if world > 1:
+            dist.init_process_group("nccl", device_id=device)
+        out = run_gptq_model(args, device, rank, world, dist)
         if rank == 0:
-            if args.workload == "gptq_model":
-                print(json.dumps(run_gptq_model(args, device, rank, 1, dist)), flush=True)
-            else:
-                {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload}[args.workload](
-                    args, device)
+            print(json.dumps(out), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload in ("gptq", "data_aware", "api"):
+        if rank == 0:
+            {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload}[args.workload](
+                args, device)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)

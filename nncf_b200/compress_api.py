@@ -393,6 +393,84 @@ def find_mul_merge_pairs(model: nn.Module, sample: Any, targets: dict) -> dict:
 
 
 # --------------------------------------------------------------------------------------------------
+# GPTQ over several ranks
+# --------------------------------------------------------------------------------------------------
+class _GptqRanks:
+    """The three exchange steps of distributed GPTQ.  With ``group`` None every method is the identity."""
+
+    def __init__(self, group: Any):
+        self.group = group
+        if group is None:
+            self.world, self.rank = 1, 0
+        else:
+            import torch.distributed as dist
+
+            self.dist = dist
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+
+    def share(self, items: list) -> list:
+        """This rank's calibration items: every world-th one."""
+        if self.world == 1:
+            return items
+        if len(items) < self.world:
+            msg = f"{len(items)} calibration items cannot be shared among {self.world} ranks"
+            raise ValidationError(msg)
+        return items[self.rank::self.world]
+
+    def combine(self, H: torch.Tensor, n_local: int, stat: Optional[WCTensorStatistic]):
+        """The Hessian over all ranks' items from the per-rank running averages: each is (2 / n_r) * sum X^T X over
+        the rank's n_r samples, the whole is (2 / n) * sum over everything = sum_r (n_r / n) * H_r."""
+        if self.world == 1:
+            return H, stat
+        n = torch.tensor([float(n_local)], dtype=torch.float64, device=H.device)
+        self.dist.all_reduce(n, group=self.group)
+        H.mul_(float(n_local) / float(n.item()))
+        self.dist.all_reduce(H, group=self.group)
+        if stat is not None:
+            # per-item channel means and shapes, back in the order of the calibration items (item i lives on
+            # rank i % world)
+            mine = ([m.cpu() for m in stat.mean_values], list(stat.shape_values))
+            everyone: list = [None] * self.world
+            self.dist.all_gather_object(everyone, mine, group=self.group)
+            merged = WCTensorStatistic()
+            for i in range(max(len(e[0]) for e in everyone)):
+                for means, shapes in everyone:
+                    if i < len(means):
+                        merged.mean_values.append(means[i].to(H.device))
+                        merged.shape_values.append(shapes[i])
+            stat = merged
+        return H, stat
+
+    def same_factor(self, hinv: torch.Tensor) -> torch.Tensor:
+        """Every rank computed the factor from the same Hessian; rank 0's copy is the one all of them use."""
+        if self.world > 1:
+            dead = getattr(hinv, "_dead_columns", None)
+            self.dist.broadcast(hinv, self.dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                                group=self.group)
+            hinv._dead_columns = dead
+        return hinv
+
+    def rows(self, n_rows: int) -> tuple[int, int, int]:
+        """(first row, end row, rows per rank) of this rank's slice: multiples of 128 rows, the sweep kernel's tile."""
+        if self.world == 1:
+            return 0, n_rows, n_rows
+        per = ((n_rows + self.world - 1) // self.world + 127) // 128 * 128
+        r0 = min(self.rank * per, n_rows)
+        return r0, min(r0 + per, n_rows), per
+
+    def gather_rows(self, part: Optional[torch.Tensor], per: int, n_rows: int, like: torch.Tensor) -> torch.Tensor:
+        """All ranks' row slices stacked back into [n_rows, ...]; ``like`` gives trailing shape, dtype and device."""
+        if self.world == 1:
+            return part
+        buf = torch.zeros((per, *like.shape[1:]), dtype=like.dtype, device=like.device)
+        if part is not None and part.shape[0] > 0:
+            buf[: part.shape[0]].copy_(part)
+        out = torch.empty((self.world * per, *like.shape[1:]), dtype=like.dtype, device=like.device)
+        self.dist.all_gather_into_tensor(out, buf, group=self.group)
+        return out[:n_rows]
+
+
+# --------------------------------------------------------------------------------------------------
 # the entry point
 # --------------------------------------------------------------------------------------------------
 def compress_weights(
@@ -413,9 +491,17 @@ def compress_weights(
     backup_mode: Optional[BackupMode] = None,
     compression_format: CompressionFormat = CompressionFormat.DQ,
     advanced_parameters: Optional[AdvancedCompressionParameters] = None,
+    process_group: Any = None,
 ) -> nn.Module:
     """Compress the weights of ``model`` (CUDA, modified in place and returned).  Same keyword API and
-    defaults as ``nncf.compress_weights``; ``ignored_scope`` is a collection of module names."""
+    defaults as ``nncf.compress_weights``; ``ignored_scope`` is a collection of module names.
+
+    ``process_group`` (an addition; the reference runs in one process): a ``torch.distributed`` group whose
+    ranks each hold a replica of ``model`` on their own GPU and call this function together with the same
+    arguments.  GPTQ is then shared out: every rank runs its share of the calibration items through the
+    blocks and the partial Hessians are summed with an all-reduce; the inverse factor is computed on every
+    rank and taken from rank 0 of the group; the rows of every weight are swept by different ranks and
+    all-gathered.  Every rank returns the same compressed model.  Other algorithms run replicated."""
     mode = CompressWeightsMode(mode)
     check_user_compression_configuration(mode, subset_size, dataset, ratio, group_size, all_layers, awq,
                                          scale_estimation, gptq, lora_correction, sensitivity_metric, backup_mode,
@@ -534,7 +620,8 @@ def compress_weights(
         g = GPTQ(adv.gptq_params.damp_percent, adv.gptq_params.block_size, adv.gptq_params.subset_size,
                  scale_estimation=cfg["scale_estimation"])
         targets = [p for p in active if not p.is_embedding and p.compression_config.mode not in INT8_MODES]
-        cal = items[: adv.gptq_params.subset_size]
+        ranks = _GptqRanks(process_group)
+        cal = ranks.share(items[: adv.gptq_params.subset_size])
         timer = _PhaseTimer(COLLECT_TIMERS)
         t_total = timer.start("total")
 
@@ -542,19 +629,33 @@ def compress_weights(
             """One Hessian for layers fed by the very same tensor (q/k/v, gate/up), one factorisation, then
             every layer of the group; weights are replaced only after the whole group saw the same inputs."""
             if given is not None:
-                H, layer_stat = given
+                H, layer_stat, n_local = given
             else:
-                H, layer_stat = _layer_hessian(runners, group[0].module, g, want_statistics=cfg["scale_estimation"],
-                                               timer=timer)
+                H, layer_stat, n_local = _layer_hessian(runners, group[0].module, g,
+                                                        want_statistics=cfg["scale_estimation"], timer=timer)
+            H, layer_stat = ranks.combine(H, n_local, layer_stat)
             hinv = None
             for p in group:
-                w = p.weight.data.float().contiguous()
+                n_rows = p.weight.shape[0]
+                r0, r1, per = ranks.rows(n_rows)
+                w = p.weight.data[r0:r1].float().contiguous()
                 if hinv is None:
                     h = timer.start("inverse_factors")
-                    hinv = g.prepare_hessian_inverse(H, w)
+                    hinv = ranks.same_factor(g.prepare_hessian_inverse(H, w))
                     timer.stop(h)
                 h = timer.start("sweeps")
-                q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat)
+                q = sc = zp = None
+                if r1 > r0:
+                    q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat)
+                    q = q.to(p.weight.dtype)
+                if ranks.world > 1:
+                    cols = p.weight.shape[1]
+                    gs = p.compression_config.group_size if p.compression_config.group_size != -1 else cols
+                    pshape = (1, cols // gs, 1) if p.compression_config.group_size != -1 else (1, 1)
+                    q = ranks.gather_rows(q, per, n_rows, p.weight.data)
+                    sc = ranks.gather_rows(sc, per, n_rows, torch.empty(pshape, dtype=torch.float32, device=q.device))
+                    if p.compression_config.is_asym_mode:
+                        zp = ranks.gather_rows(zp, per, n_rows, torch.empty(pshape, dtype=torch.int32, device=q.device))
                 timer.stop(h)
                 precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
                 p._gptq_weight = q
@@ -656,7 +757,7 @@ def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: b
     calibration item that runs the model (or the block that contains ``module``) on it.  Activations are
     consumed as they appear; nothing is stored but, when the sweep refines its scales with ScaleEstimation, the
     per-sample channel means and shapes (what GPTQ.activations_to_wc_statistics would reduce from stored
-    inputs).  Returns (H, statistics or None)."""
+    inputs).  Returns (H, statistics or None, number of samples seen)."""
     C = module.in_features
     stat = WCTensorStatistic() if want_statistics else None
     H = torch.zeros(C, C, dtype=torch.float32, device=module.weight.device)
@@ -697,7 +798,7 @@ def _layer_hessian(runners: list, module: nn.Linear, g: GPTQ, want_statistics: b
     with torch.cuda.device(H.device):
         # a bounded wait of the tensor-core kernel that ran out in ANY of the accumulation steps raises here
         _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(H.device)))
-    return H, stat
+    return H, stat, state["n"]
 
 
 def _decoder_blocks(model: nn.Module, targets: list) -> Optional[list]:
@@ -978,7 +1079,7 @@ class _ResumableBlock:
             raise err
 
     def hessian(self, gi: int):
-        """Run every micro-batch up to group ``gi``'s first layer; returns (H, statistics or None)."""
+        """Run every micro-batch up to group ``gi``'s first layer; returns (H, statistics or None, samples seen)."""
         for k in range(self.K):
             self._resume(k)
             if self.position[k] != gi:
@@ -991,7 +1092,7 @@ class _ResumableBlock:
         if self.device.type == "cuda":
             with torch.cuda.device(self.device):
                 _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(self.device)))
-        return self.H[gi], self.stats[gi]
+        return self.H[gi], self.stats[gi], self.n[gi]
 
     def finish(self) -> None:
         """Run every micro-batch to the end of the block and store the outputs as the next block's inputs."""

@@ -260,12 +260,13 @@ def test_resumable_block_pauses_at_every_target_and_continues_through_new_weight
     try:
         block = model.layers[0]
         run = api._ResumableBlock(workers, replay, 0, [block.a, block.b], StubGPTQ(), False, None)
-        Ha, _ = run.hessian(0)
+        Ha, _, n_a = run.hessian(0)
+        assert n_a == 5
         xa = torch.cat(inputs, 0).reshape(-1, 8)
         torch.testing.assert_close(Ha, (2.0 / 5) * (xa.T @ xa))
         with torch.no_grad():
             block.a.weight.mul_(0.5)               # "quantise" the first layer while the forwards are paused
-        Hb, _ = run.hessian(1)
+        Hb, _, _ = run.hessian(1)
         xb = torch.tanh(block.a(xa))
         torch.testing.assert_close(Hb, (2.0 / 5) * (xb.T @ xb))
         with torch.no_grad():
