@@ -16,6 +16,7 @@ from . import _lib  # noqa: F401  (fails loudly when the CUDA library is missing
 from . import weight_lowering
 from .weight_lowering import compress_weight
 from .compress_api import Dataset, compress_weights
-from .serialization import get_config, load_from_config, strip
+from .serialization import (from_reference_state_dict, get_config, gptq_layout, load_from_config, load_safetensors,
+                            reference_state_dict, save_safetensors, strip)
 
 __version__ = "0.1.0"

@@ -255,6 +255,12 @@ __device__ __forceinline__ void int_params(float mn, float mx, float& s, float& 
 // The cubic keeps k in {index - 1, index} for every real q in [-1, 1] with 0.034 to spare (fp32 evaluation
 // error is below 1e-5), so comparing against the single boundary bound[k] decides the index exactly; k = -1
 // reads lane 31, which holds -inf.  tests/test_kernel_constants.py re-derives that margin from these constants.
+// The comparison itself is done on the FMA pipe instead of a compare and a predicated add (the integer / compare
+// pipe issues at half rate and is this kernel's busiest): the lanes hold -bound * 2^40, and
+//   c = saturate(q * 2^40 + (-bound * 2^40))     -- one fused multiply-add, rounded once
+// is exactly 1.0f when q > bound and 0.0f otherwise: the scaled difference is exact up to its single rounding,
+// it is zero only for q == bound, and two distinct floats near a boundary (|bound| >= 0.039) differ by at least
+// 2^-28, i.e. by 2^12 after scaling.  c is then added to the float that carries k in its mantissa.
 constexpr float kNf4PolyC1 = 11.72690251f, kNf4PolyC2 = -0.51709913f, kNf4PolyC3 = -4.67530535f;
 constexpr float kLutNone = 3.0e38f;
 __device__ __constant__ const float kNf4LutBound[32] = {
@@ -264,6 +270,14 @@ __device__ __constant__ const float kNf4LutBound[32] = {
     0.5016633868217468f, 0.6427869200706482f, 0.8614783883094788f, kLutNone,
     kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone,
     kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, kLutNone, -kLutNone};
+constexpr float kNf4CmpScale = 1099511627776.0f;  // 2^40
+// what lane `l` holds for the comparison: -bound[l] * 2^40 (exact), +-1e30 for "no boundary" / "-inf"
+__device__ __forceinline__ float nf4_lane_operand(int l) {
+  const float b = kNf4LutBound[l];
+  if (b > 1.0e38f) return -1.0e30f;   // q > +inf is never true: c = 0
+  if (b < -1.0e38f) return 1.0e30f;   // q > -inf is always true: c = 1
+  return -b * kNf4CmpScale;
+}
 
 __host__ __device__ constexpr bool mode_is_fast_float(int m) {
   return m == NNCFB_NF4 || m == NNCFB_FP4 || m == NNCFB_MXFP4 || m == NNCFB_FP8_E4M3 || m == NNCFB_MXFP8_E4M3;
@@ -300,7 +314,7 @@ __device__ __forceinline__ float shfl_low5(float v, uint32_t index) {
 // E2M1 uses the hardware conversion cvt.rn.satfinite.e2m1x2.f32: round to nearest, ties to the even
 // mantissa, saturation at 6 - the rule WC/weight_lowering.py:577-583 implements on its 15-entry table.
 template <int MODE>
-__device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s, float r, float lut_bound) {
+__device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s, float r, float lut_operand) {
   const float2 r2 = f2(r, r), ns2 = f2(-s, -s);
   float2 q[4];
 #pragma unroll
@@ -326,12 +340,12 @@ __device__ __forceinline__ uint32_t encode8_float(const float2 (&v)[4], float s,
       // Opaque to the optimiser from here on: when it can see that kx and ky are the halves of one packed
       // result it was observed (nvcc 12.9, sm_100a) to place digits of the sum below in the wrong nibble.
       asm("" : "+r"(kx), "+r"(ky));
-      const float bx = shfl_low5(lut_bound, kx);
-      const float by = shfl_low5(lut_bound, ky);
-      acc = acc * 16u + ky;
-      if (q[i].y > by) acc += 1u;
-      acc = acc * 16u + kx;
-      if (q[i].x > bx) acc += 1u;
+      const float lx = shfl_low5(lut_operand, kx);
+      const float ly = shfl_low5(lut_operand, ky);
+      const float cx = __saturatef(__fmaf_rn(q[i].x, kNf4CmpScale, lx));   // 1.0f iff q > bound[k]
+      const float cy = __saturatef(__fmaf_rn(q[i].y, kNf4CmpScale, ly));
+      acc = acc * 16u + __float_as_uint(__fadd_rn(__uint_as_float(ky), cy));
+      acc = acc * 16u + __float_as_uint(__fadd_rn(__uint_as_float(kx), cx));
     }
     return acc - kMagicBits * 0x11111111u;
   } else {
@@ -582,7 +596,7 @@ __global__ void __launch_bounds__(256, NNCFB_ROWS_MINBLOCKS) quant_rows_batch_ke
   const int64_t total_iters = b.iter_start[b.n_tensors];
   int lo = 0;  // tensor of the current iteration; iterations only move forward
   float lut_bound = 0.0f;
-  if constexpr (MODE == NNCFB_NF4) lut_bound = kNf4LutBound[lane];
+  if constexpr (MODE == NNCFB_NF4) lut_bound = nf4_lane_operand(lane);
 
   for (int64_t it = warp; it < total_iters; it += n_warps) {
     while (b.iter_start[lo + 1] <= it) ++lo;

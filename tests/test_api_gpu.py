@@ -432,3 +432,56 @@ def test_gptq_shared_among_two_ranks_matches_one_rank():
     assert differing < 0.05, differing
     rel = float((one["__logits"] - a["__logits"]).norm() / one["__logits"].norm())
     assert rel < 0.05, rel
+
+
+def test_reference_key_names_and_safetensors_round_trip(tmp_path):
+    """The state dict under the reference's key names has exactly the keys, dtypes and shapes the reference's own
+    compressed model has (tests/golden/api.npz), and a safetensors file with the manifest in its metadata
+    rebuilds the compressed model in a fresh process-like setting (new dense model, no compression call)."""
+    import nncf_b200 as nb
+
+    name, kwargs, use_ds = API_CASES[3]   # int4_asym group 16, all layers
+    model, ids = _compress(kwargs, use_ds)
+    g = golden("api")
+    ref_keys = [str(k) for k in g[f"api/{name}/keys"]]
+    sd = nb.reference_state_dict(model)
+    assert sorted(sd) == sorted(ref_keys)
+    for k in ref_keys:
+        want = g[f"api/{name}/{k}"]
+        assert tuple(sd[k].shape) == want.shape and str(sd[k].dtype).replace("torch.", "") == str(want.dtype), k
+        np.testing.assert_array_equal(sd[k].cpu().numpy(), want)
+    path = str(tmp_path / "model.safetensors")
+    nb.save_safetensors(model, path)
+    fresh = nb.load_safetensors(TinyGatedLM().cuda(), path)
+    with torch.no_grad():
+        assert torch.equal(fresh(ids[0]), model(ids[0]))
+    for (ka, va), (kb, vb) in zip(model.state_dict().items(), fresh.state_dict().items()):
+        assert ka == kb and torch.equal(va, vb)
+
+
+@pytest.mark.parametrize("mode,gs", [("int4_asym", 32), ("int4_sym", 128), ("int8_asym", -1), ("int8_sym", -1)])
+def test_gptq_style_layout_decodes_to_the_decompressed_weight(mode, gs):
+    """qweight / qzeros / scales / g_idx of a compressed Linear, decoded with the GPTQ formula
+    W[o, i] = scales[g_idx[i], o] * (code[i, o] - zero[g_idx[i], o]), equal the decompressor's output (which
+    multiplies in fp16; the formula is evaluated in fp32 here, hence the 2^-10 tolerance)."""
+    import nncf_b200 as nb
+
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(256, 64, bias=False).cuda().half()
+    holder = torch.nn.Sequential(lin)
+    kw = {} if gs == -1 else dict(group_size=gs, all_layers=True)
+    nb.compress_weights(holder, mode=nb.CompressWeightsMode(mode), **kw)
+    lay = nb.gptq_layout(holder[0])
+    bits, pack = lay["bits"], 32 // lay["bits"]
+    assert lay["qweight"].shape == (256 // pack, 64) and lay["qweight"].dtype == torch.int32
+    groups = 256 // (gs if gs != -1 else 256)
+    assert lay["qzeros"].shape == (groups, 64 // pack) and lay["scales"].shape == (groups, 64)
+    shifts = torch.arange(pack, device="cuda", dtype=torch.int64) * bits
+    mask = (1 << bits) - 1
+    qw = lay["qweight"].to(torch.int64) & 0xFFFFFFFF
+    codes = ((qw.unsqueeze(1) >> shifts.view(1, pack, 1)) & mask).reshape(256, 64)             # [in, out]
+    qz = lay["qzeros"].to(torch.int64) & 0xFFFFFFFF
+    zeros = ((qz.unsqueeze(2) >> shifts.view(1, 1, pack)) & mask).reshape(groups, 64)         # [groups, out]
+    gi = lay["g_idx"].long()
+    w = lay["scales"].float()[gi] * (codes - zeros[gi]).float()                                 # [in, out]
+    torch.testing.assert_close(w.t(), holder[0].weight.float(), rtol=2 ** -10, atol=1e-7)

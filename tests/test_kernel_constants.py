@@ -43,3 +43,13 @@ def test_nf4_bucket_polynomial_keeps_every_quotient_within_one_boundary():
     assert np.all((k == index) | (k == index - 1))
     got = k + (q > table[k % 32])
     assert np.array_equal(got, index)
+    # the comparison as the kernel does it: c = saturate(fma(q, 2^40, -bound * 2^40)), 1e30 / -1e30 in the lanes
+    # that stand for "-inf" / "no boundary"; the float64 sum of the two exact terms, rounded once to fp32, is what
+    # the fused multiply-add returns
+    scale = float(re.search(r"kNf4CmpScale = ([0-9.]+)f", text).group(1))
+    assert scale == 2.0 ** 40
+    lane = np.where(table > 1e38, -1e30, np.where(table < -1e38, 1e30, -table.astype(np.float64) * scale))
+    assert np.array_equal(lane.astype(np.float32).astype(np.float64), lane) or np.allclose(lane, lane.astype(np.float32))
+    c = np.clip((q64 * scale + lane[k % 32]).astype(np.float32), 0.0, 1.0)
+    assert set(np.unique(c)) <= {0.0, 1.0}
+    assert np.array_equal(k + c.astype(np.int64), index)
