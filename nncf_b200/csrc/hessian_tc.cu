@@ -43,11 +43,17 @@ constexpr int kTileN = 256;
 constexpr int kBoxC = 64;    // channels per TMA box (128 bytes of bf16)
 constexpr int kBlockK = 64;  // tokens per pipeline stage
 constexpr int kStagesHessian = 4;
-constexpr int kStagesTrailing = 4;
+// The trailing update runs one tile per CTA (twelve K stages), so a CTA's life is a sequence of phases that do not
+// overlap: pipeline ramp-up, MMAs, drain, read-modify-write epilogue.  Two stages (96 KB) and one 256-column
+// accumulator let TWO such CTAs live on an SM and fill each other's gaps; four stages and a 512-column
+// allocation (what the persistent Hessian kernel wants) would admit one: the second CTA's tensor-memory
+// allocation waits until the first one frees its columns.
+constexpr int kStagesTrailing = 2;
 constexpr int kMaxStages = 4;
 constexpr int kBoxBytes = kBoxC * kBlockK * 2;                           // 8192
 constexpr int kStageBytes = (kTileM / kBoxC + kTileN / kBoxC) * kBoxBytes;  // 49152
-constexpr int kTmemCols = 512;  // two accumulators of kTileN fp32 columns
+constexpr int kTmemColsPersistent = 512;  // two accumulators of kTileN fp32 columns (tile t + 1 starts while t drains)
+constexpr int kTmemColsOneTile = 256;     // one accumulator: a CTA that computes a single tile
 constexpr uint64_t kWaitLimitNs = 4000000000ull;  // 4 s per wait: far beyond any legitimate wait of this kernel
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -101,6 +107,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+
+// D[y.., x..] += tile: a 2-D bulk tensor reduction from shared memory into global memory (fp32 add done by the
+// memory system next to L2, so the tile of D never travels to the SM).  Completion is tracked by the bulk async
+// group of the issuing thread.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, const void* src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y), "r"(smem_u32(src))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_generic_to_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // MN-major, 128-byte swizzle shared-memory operand descriptor:
 //   start address >> 4 | LBO (stride between 64-element atoms along M/N) >> 4 at bit 16 |
@@ -226,8 +246,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 //                   plane pair (pa, pb) x two halves of the 128-row block; A planes in `amap`, B planes in `bmap`,
 //                   each a 2-D tensor [3 * 128, extent] with plane p at rows [128 p, 128 p + 128).
 template <int kStages, bool TRAILING>
-__global__ void __launch_bounds__(192, 1)
-tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, float* __restrict__ H,
+__global__ void __launch_bounds__(192, TRAILING ? 2 : 1)
+tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
+             const __grid_constant__ CUtensorMap dmap, float* __restrict__ H,
              int64_t ld, int64_t m_bound, int64_t n_bound, int64_t tokens, float alpha, float beta, uint32_t idesc,
              int n_tiles_n, int n_tiles, int* __restrict__ status, uint64_t wait_ns, int producer_short) {
   extern __shared__ uint8_t smem_raw[];
@@ -235,6 +256,7 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Control* ctl = reinterpret_cast<Control*>(ring + kStages * kStageBytes);
 
+  constexpr int kTmemCols = TRAILING ? kTmemColsOneTile : kTmemColsPersistent;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = static_cast<int>((m_bound + kTileM - 1) / kTileM);
   const int k_iters = TRAILING ? 12 : static_cast<int>((tokens + kBlockK - 1) / kBlockK);
@@ -369,19 +391,56 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
         }
       }
     };
-    prefetch_tile(blockIdx.x);
+    if constexpr (!TRAILING) prefetch_tile(blockIdx.x);
     int t = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
       const int bf = t & 1;
       int m0, n0;
       tile_origin(tile, m0, n0);
       const int64_t r = static_cast<int64_t>(m0) + q * 32 + lane;
-      prefetch_tile(tile + gridDim.x);
+      if constexpr (!TRAILING) prefetch_tile(tile + gridDim.x);
       const bool ok = mbar_wait(&ctl->acc_full[bf], (t >> 1) & 1, wait_ns);
       if (!ok && lane == 0) give_up(status, 3);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (!ok || *reinterpret_cast<volatile int*>(status) != 0) break;  // warp-uniform: some role gave up
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(bf * kTileN);
+      if constexpr (TRAILING) {
+        // D += beta * acc without reading D into the SM: every 32 x 32 piece of the accumulator is written to
+        // shared memory (in the 128-byte swizzle the tensor map expects, which also keeps the 16-byte stores of a
+        // warp free of bank conflicts) and added to D by a bulk tensor reduction.  Every element of D receives
+        // exactly one add per launch, so the result is the correctly rounded D + beta * acc, as before; rows and
+        // columns beyond the bounds are clipped by the tensor map.  The staging buffers reuse the operand ring:
+        // the accumulator is complete, so every stage has been consumed and nothing else is loaded (one tile per
+        // CTA).  Four 4 KB buffers per warp: the reads of the first four reductions are awaited before the fifth.
+        uint8_t* stage = ring + static_cast<size_t>(q) * (4 * 4096);
+#pragma unroll 1
+        for (int c = 0; c < kTileN; c += 32) {
+          if (c == 128) {
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+          }
+          uint32_t acc[32];
+          tmem_ld32(tmem_acc + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c), acc);
+          uint8_t* buf = stage + ((c >> 5) & 3) * 4096;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 v;
+            v.x = __fmul_rn(beta, __uint_as_float(acc[4 * j]));
+            v.y = __fmul_rn(beta, __uint_as_float(acc[4 * j + 1]));
+            v.z = __fmul_rn(beta, __uint_as_float(acc[4 * j + 2]));
+            v.w = __fmul_rn(beta, __uint_as_float(acc[4 * j + 3]));
+            *reinterpret_cast<float4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_generic_to_async_smem();
+          __syncwarp();
+          if (lane == 0 && n0 + c < n_bound && m0 + q * 32 < m_bound) {
+            tma_reduce_add_2d(&dmap, n0 + c, m0 + q * 32, buf);
+            bulk_commit();
+          }
+        }
+        if (lane == 0) bulk_wait_all();
+        __syncwarp();
+      } else {
       // tcgen05.ld hands each lane one accumulator row, 32 columns (one 128-byte line of D) per step.  The
       // eight 16-byte loads of a step are issued together, before the first store, so that they overlap.
 #pragma unroll 1
@@ -408,6 +467,7 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
             }
           }
         }
+      }
       }
       // this warp has read its quarter of the buffer: hand it back to the MMA warp
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -506,6 +566,25 @@ int encode_map(CUtensorMap* map, const void* base, bool bf16, int64_t extent, in
   return NNCFB_OK;
 }
 
+// 2-D map over a row-major fp32 matrix [rows, extent] with `ld` floats between rows; boxes of 32 x 32 floats (one
+// 128-byte line per row) in the 128-byte swizzle the epilogue's staging buffers use.
+int encode_map_f32(CUtensorMap* map, const float* base, int64_t extent, int64_t rows, int64_t ld) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return NNCFB_E_UNSUPPORTED;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(extent), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult cr = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (fp32 output map) failed with code %d", static_cast<int>(cr));
+    return NNCFB_E_CUDA;
+  }
+  return NNCFB_OK;
+}
+
 template <int kStages>
 constexpr size_t tc_smem_bytes() { return static_cast<size_t>(kStages) * kStageBytes + sizeof(Control) + 1024; }
 
@@ -527,7 +606,7 @@ static int hessian_tc_launch(float* H, int64_t C, const void* x, int dtype, int6
   NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   int* status = nullptr;
   if (const int sr = next_launch_status(&status, st); sr != NNCFB_OK) return sr;
-  kernel<<<std::min(n_tiles, sm_count()), 192, smem, st>>>(map, map, H, C, C, C, tokens, alpha, beta,
+  kernel<<<std::min(n_tiles, sm_count()), 192, smem, st>>>(map, map, map, H, C, C, C, tokens, alpha, beta,
                                                             instr_desc(dtype == NNCFB_BF16), tiles_n, n_tiles, status,
                                                             wait_ns, producer_short);
   NNCFB_CUDA(cudaGetLastError());
@@ -575,10 +654,12 @@ int gptq_split_slab(const float* hinv, int64_t cols, int i1, int64_t c0, int64_t
 //   slab_c     : bf16 [3 * 128, slab_ld] planes of the slab, already offset to column c (16-byte aligned)
 int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv_bfloat16* err_planes, int64_t err_ld,
                      const __nv_bfloat16* slab_c, int64_t slab_ld, cudaStream_t st) {
-  CUtensorMap amap, bmap;
+  CUtensorMap amap, bmap, dmap;
   int rc = encode_map(&amap, err_planes, true, rows, 3 * 128, err_ld);
   if (rc != NNCFB_OK) return rc;
   rc = encode_map(&bmap, slab_c, true, n, 3 * 128, slab_ld);
+  if (rc != NNCFB_OK) return rc;
+  rc = encode_map_f32(&dmap, w_c, n, rows, ld);
   if (rc != NNCFB_OK) return rc;
   const int tiles_m = static_cast<int>((rows + kTileM - 1) / kTileM);
   const int tiles_n = static_cast<int>((n + kTileN - 1) / kTileN);
@@ -590,7 +671,7 @@ int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv
   // One CTA per tile here: this kernel shares the GPU with the next block's sweep (whose CTAs fill the shared
   // memory of the SMs they sit on), so a fixed set of persistent CTAs would leave tiles waiting behind it;
   // with a CTA per tile the hardware hands tiles to whichever SMs are free.
-  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, w_c, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
+  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, dmap, w_c, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
                                                tiles_m * tiles_n, status, kWaitLimitNs, 0);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
