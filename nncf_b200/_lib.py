@@ -71,6 +71,8 @@ def _load() -> C.CDLL:
         "nncfb_gptq_quantize_se": ([vp, i64, i64, vp, i32, i64, i32, vp, vp, i32, i32, i32, C.c_float, vp, vp, vp, vp,
                                     C.c_size_t, vp], C.c_int),
         "nncfb_gptq_quantize_noalloc": ([vp, i64, i64, vp, i32, i64, i32, vp, vp, vp, vp], C.c_int),
+        "nncfb_gemm_f32_workspace_bytes": ([i64, i64, i64], C.c_size_t),
+        "nncfb_gemm_f32": ([vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_float, i32, vp, C.c_size_t, vp], C.c_int),
         "nncfb_decompress": ([vp, i32, i64, i64, vp, vp, vp, i32, vp], C.c_int),
         "nncfb_pack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_unpack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
@@ -89,7 +91,8 @@ EXPORTED = ["nncfb_abi_version", "nncfb_last_error", "nncfb_quantize", "nncfb_qu
             "nncfb_scale_estimation", "nncfb_awq_workspace_bytes", "nncfb_awq_search", "nncfb_channel_stats",
             "nncfb_hessian_accumulate", "nncfb_hessian_status", "nncfb_gptq_workspace_bytes",
             "nncfb_gptq_workspace_bytes_tensor_cores", "nncfb_gptq_quantize",
-            "nncfb_gptq_quantize_se", "nncfb_gptq_quantize_noalloc", "nncfb_decompress",
+            "nncfb_gptq_quantize_se", "nncfb_gptq_quantize_noalloc", "nncfb_gemm_f32_workspace_bytes",
+            "nncfb_gemm_f32", "nncfb_decompress",
             "nncfb_pack_nibbles", "nncfb_unpack_nibbles",
             "nncfb_selftest_division", "nncfb_selftest_bounded_wait"]
 

@@ -242,9 +242,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // the producer prefetches the next tile's operands and the MMA warp starts it while the epilogue warps are still
 // writing the previous tile back.
 // TRAILING = false: D = H [C, C], upper-triangle tiles in banded order, K = tokens, both operands from `amap`.
-// TRAILING = true:  D = W + c0 [rows, n_bound] with leading dimension ld, all tiles, twelve K segments of 64:
-//                   plane pair (pa, pb) x two halves of the 128-row block; A planes in `amap`, B planes in `bmap`,
-//                   each a 2-D tensor [3 * 128, extent] with plane p at rows [128 p, 128 p + 128).
+// TRAILING = true:  D [m_bound, n_bound] += beta * A^T B for fp32 operands given as three bf16 planes each: all tiles,
+//                   6 * K / 64 pipeline stages (plane pair (pa, pb) x the K / 64 chunks of the contraction);
+//                   A planes in `amap`, B planes in `bmap`, each a 2-D tensor [3 * K, extent] with plane p at rows
+//                   [K p, K p + K); `tokens` carries K (128 for the GPTQ block update).  D is updated through `dmap`.
 template <int kStages, bool TRAILING>
 __global__ void __launch_bounds__(192, TRAILING ? 2 : 1)
 tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
@@ -259,7 +260,9 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
   constexpr int kTmemCols = TRAILING ? kTmemColsOneTile : kTmemColsPersistent;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = static_cast<int>((m_bound + kTileM - 1) / kTileM);
-  const int k_iters = TRAILING ? 12 : static_cast<int>((tokens + kBlockK - 1) / kBlockK);
+  // TRAILING: `tokens` is K, the number of rows of each operand plane (a multiple of 64): six plane pairs x K / 64
+  const int k_chunks = static_cast<int>((tokens + kBlockK - 1) / kBlockK);
+  const int k_iters = TRAILING ? 6 * k_chunks : k_chunks;
   auto tile_origin = [&](int tile, int& m0, int& n0) {
     int mi, nj;
     if constexpr (TRAILING) {
@@ -315,10 +318,12 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
           mbar_expect_tx(&ctl->full[s], kStageBytes);
           int ka = it * kBlockK, kb = ka;
           if constexpr (TRAILING) {
-            // plane pairs, smallest products first: (lo,hi) (hi,lo) (mid,mid) (mid,hi) (hi,mid) (hi,hi); hi = plane 0
-            const int combo = it >> 1, half = it & 1;
-            ka = static_cast<int>((0x001102u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
-            kb = static_cast<int>((0x010120u >> (4 * combo)) & 15u) * 128 + half * kBlockK;
+            // plane pairs, smallest products first: (lo,hi) (hi,lo) (mid,mid) (mid,hi) (hi,mid) (hi,hi); hi = plane 0;
+            // each pair runs over all of K before the next, so the small terms are summed before the large ones
+            const int combo = it / k_chunks, chunk = it - combo * k_chunks;
+            const int plane_rows = static_cast<int>(tokens);
+            ka = static_cast<int>((0x001102u >> (4 * combo)) & 15u) * plane_rows + chunk * kBlockK;
+            kb = static_cast<int>((0x010120u >> (4 * combo)) & 15u) * plane_rows + chunk * kBlockK;
           }
 #pragma unroll
           for (int b = 0; b < kTileM / kBoxC; ++b)
@@ -671,7 +676,98 @@ int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv
   // One CTA per tile here: this kernel shares the GPU with the next block's sweep (whose CTAs fill the shared
   // memory of the SMs they sit on), so a fixed set of persistent CTAs would leave tiles waiting behind it;
   // with a CTA per tile the hardware hands tiles to whichever SMs are free.
-  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, dmap, w_c, ld, rows, n, 0, 1.0f, -1.0f, instr_desc(true), tiles_n,
+  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, dmap, w_c, ld, rows, n, 128, 1.0f, -1.0f, instr_desc(true), tiles_n,
+                                               tiles_m * tiles_n, status, kWaitLimitNs, 0);
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+// ---- fp32-faithful GEMM on the tensor cores -----------------------------------------------------------
+// planes[p][k][j] = plane p of src[k][j] (src row-major [K, extent], `ld` floats between rows): B operands.
+__global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ src, int64_t ld, int64_t K,
+                                                         int64_t extent, int64_t plane_ld,
+                                                         __nv_bfloat16* __restrict__ planes) {
+  const int64_t k = blockIdx.y;
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (j >= extent) return;
+  __nv_bfloat16 h, m, l;
+  split_bf16x3(src[k * ld + j], h, m, l);
+  planes[(0 * K + k) * plane_ld + j] = h;
+  planes[(1 * K + k) * plane_ld + j] = m;
+  planes[(2 * K + k) * plane_ld + j] = l;
+}
+
+// planes[p][k][i] = plane p of src[i][k] (src row-major [extent, K]): A operands, transposed through a 32 x 32 tile.
+__global__ void __launch_bounds__(256) split_transposed_kernel(const float* __restrict__ src, int64_t ld, int64_t K,
+                                                               int64_t extent, int64_t plane_ld,
+                                                               __nv_bfloat16* __restrict__ planes) {
+  __shared__ float tile[32][33];
+  const int64_t i0 = static_cast<int64_t>(blockIdx.y) * 32, k0 = static_cast<int64_t>(blockIdx.x) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t i = i0 + r, k = k0 + tx;
+    tile[r][tx] = (i < extent && k < K) ? src[i * ld + k] : 0.0f;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t k = k0 + r, i = i0 + tx;
+    if (k < K && i < extent) {
+      __nv_bfloat16 h, m, l;
+      split_bf16x3(tile[tx][r], h, m, l);
+      planes[(0 * K + k) * plane_ld + i] = h;
+      planes[(1 * K + k) * plane_ld + i] = m;
+      planes[(2 * K + k) * plane_ld + i] = l;
+    }
+  }
+}
+
+namespace {
+int64_t round8_i64(int64_t v) { return (v + 7) & ~static_cast<int64_t>(7); }
+size_t planes_bytes_gemm(int64_t K, int64_t extent) {
+  return (static_cast<size_t>(3) * K * round8_i64(extent) * 2 + 1023) & ~static_cast<size_t>(1023);
+}
+}  // namespace
+
+size_t gemm_f32_workspace(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return planes_bytes_gemm(K, M) + planes_bytes_gemm(K, N);
+}
+
+// C[M, N] (row stride ldc) = C * (accumulate ? 1 : 0) + alpha * A[M, K] @ B[K, N]
+int gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc, int64_t M, int64_t N,
+             int64_t K, float alpha, bool accumulate, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (K % kBlockK != 0 || ldc % 4 != 0 || !aligned16(C) || !aligned16(workspace) || M > 0x7fffffff || N > 0x7fffffff ||
+      K > 0x7fffffff / 3 || encode_tiled_fn() == nullptr)
+    return NNCFB_E_UNSUPPORTED;
+  if (workspace_bytes < gemm_f32_workspace(M, N, K)) {
+    set_error("nncfb_gemm_f32: workspace of %zu bytes is smaller than nncfb_gemm_f32_workspace_bytes() = %zu",
+              workspace_bytes, gemm_f32_workspace(M, N, K));
+    return NNCFB_E_BAD_ARG;
+  }
+  __nv_bfloat16* a_planes = static_cast<__nv_bfloat16*>(workspace);
+  __nv_bfloat16* b_planes = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(workspace) + planes_bytes_gemm(K, M));
+  const int64_t a_ld = round8_i64(M), b_ld = round8_i64(N);
+  const dim3 ga(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((M + 31) / 32));
+  split_transposed_kernel<<<ga, 256, 0, st>>>(A, lda, K, M, a_ld, a_planes);
+  const dim3 gb(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(K));
+  split_rows_kernel<<<gb, 256, 0, st>>>(B, ldb, K, N, b_ld, b_planes);
+  NNCFB_CUDA(cudaGetLastError());
+  if (!accumulate) NNCFB_CUDA(cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, st));
+  CUtensorMap amap, bmap, dmap;
+  int rc = encode_map(&amap, a_planes, true, M, 3 * K, a_ld);
+  if (rc != NNCFB_OK) return rc;
+  rc = encode_map(&bmap, b_planes, true, N, 3 * K, b_ld);
+  if (rc != NNCFB_OK) return rc;
+  rc = encode_map_f32(&dmap, C, N, M, ldc);
+  if (rc != NNCFB_OK) return rc;
+  const int tiles_m = static_cast<int>((M + kTileM - 1) / kTileM);
+  const int tiles_n = static_cast<int>((N + kTileN - 1) / kTileN);
+  constexpr size_t smem = tc_smem_bytes<kStagesTrailing>();
+  auto kernel = tc_tn_kernel<kStagesTrailing, true>;
+  NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  int* status = nullptr;
+  if (const int sr = next_launch_status(&status, st); sr != NNCFB_OK) return sr;
+  kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, dmap, C, ldc, M, N, K, 1.0f, alpha, instr_desc(true), tiles_n,
                                                tiles_m * tiles_n, status, kWaitLimitNs, 0);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
@@ -705,6 +801,21 @@ extern "C" int nncfb_hessian_status(void* stream) {
     return NNCFB_E_TIMEOUT;
   }
   return NNCFB_OK;
+}
+
+extern "C" size_t nncfb_gemm_f32_workspace_bytes(int64_t m, int64_t n, int64_t k) { return nncfb::gemm_f32_workspace(m, n, k); }
+
+extern "C" int nncfb_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb, float* c, int64_t ldc, int64_t m,
+                              int64_t n, int64_t k, float alpha, int32_t accumulate, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  NNCFB_CHECK_ARG(a && b && c && workspace, NNCFB_E_BAD_ARG, "nncfb_gemm_f32: null pointer");
+  NNCFB_CHECK_ARG(m > 0 && n > 0 && k > 0 && lda >= k && ldb >= n && ldc >= n, NNCFB_E_BAD_ARG, "nncfb_gemm_f32: bad shape");
+  const int rc = nncfb::gemm_f32(a, lda, b, ldb, c, ldc, m, n, k, alpha, accumulate != 0, workspace, workspace_bytes,
+                                 static_cast<cudaStream_t>(stream));
+  if (rc == NNCFB_E_UNSUPPORTED)
+    nncfb::set_error("nncfb_gemm_f32: needs k %% 64 == 0, ldc %% 4 == 0, 16-byte aligned c and workspace, and a driver "
+                     "with tensor-map support");
+  return rc;
 }
 
 // Self test of the bounded waits: the Hessian kernel with a 1 ms limit per wait and a producer that leaves out the

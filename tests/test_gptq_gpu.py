@@ -441,3 +441,50 @@ def test_gptq_sweep_with_look_ahead_replays_from_a_cuda_graph():
         torch.cuda.synchronize()
         assert torch.equal(q, want[0]) and torch.equal(sc, want[1]) and torch.equal(w, want[2])
     _lib.check(_lib.lib.nncfb_hessian_status(None))
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (520, 1000, 192), (1024, 768, 1024), (2048, 2048, 2048)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_fp32_faithful_tensor_core_gemm_matches_fp64(m, n, k, accumulate):
+    """nncfb_gemm_f32 (bf16x3 operand planes on tcgen05, fp32 accumulation, bulk reduce-add into C) on strided
+    views of larger matrices, ragged M / N tiles included: as close to an fp64 product as torch's fp32 product."""
+    from nncf_b200 import gptq as G
+
+    gen = torch.Generator(device="cuda").manual_seed(m + n + k)
+    big_a = torch.randn(m + 8, k + 64, device="cuda", generator=gen)
+    big_b = torch.randn(k + 8, n + 128, device="cuda", generator=gen) * 3.0
+    big_c = torch.randn(m, n + 256, device="cuda", generator=gen)
+    a, b = big_a[8:, 64:], big_b[:k, 128:]
+    c = big_c[:, 128:128 + n]
+    guard_left, guard_right = big_c[:, :128].clone(), big_c[:, 128 + n:].clone()
+    want = a.double() @ b.double() + (c.double() if accumulate else 0)
+    ref32 = (a @ b + (c if accumulate else 0)).double()
+    G._gemm(a, b, c, accumulate=accumulate)
+    torch.cuda.synchronize()
+    scale = want.abs().max().item()
+    err = (c.double() - want).abs().max().item() / scale
+    err32 = (ref32 - want).abs().max().item() / scale
+    assert err < max(2e-6, 4 * err32), (err, err32)
+    # nothing outside the view was touched (ragged tiles are clipped by the tensor map)
+    assert torch.equal(big_c[:, :128], guard_left) and torch.equal(big_c[:, 128 + n:], guard_right)
+
+
+def test_triangular_inverse_with_tensor_core_products_matches_fp64(monkeypatch):
+    from nncf_b200 import gptq as G
+
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    n = 3072
+    x = torch.randn(2 * n, n, device="cuda", generator=gen)
+    H = (x.T @ x) / (2 * n)
+    H.diagonal().add_(0.01 * H.diagonal().mean())
+    L = torch.linalg.cholesky(H)
+    ref = torch.linalg.inv(L.double())
+    out = {}
+    for tc in (True, False):
+        monkeypatch.setattr(G, "TENSOR_CORE_PRODUCTS", tc)
+        out[tc] = G.lower_triangular_inverse(L)
+    err = {k: ((v.double() - ref).norm() / ref.norm()).item() for k, v in out.items()}
+    print(f"triangular inverse n={n}: relative error vs fp64 {err}")
+    assert err[True] < 2 * err[False] + 1e-7
+    assert torch.equal(out[True], torch.tril(out[True]))
+    assert not torch.equal(out[True], out[False])   # the tensor-core products were really used
