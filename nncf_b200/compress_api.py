@@ -210,12 +210,22 @@ def _backup_config(backup_mode: BackupMode, group_size: int = -1) -> Optional[We
 # weights of the model
 # --------------------------------------------------------------------------------------------------
 def _execution_order(model: nn.Module, sample: Any) -> dict:
-    """First-call order of the leaf modules during one forward pass."""
+    """First-call order of the leaf modules during one forward pass.  The same pass numbers the distinct input
+    tensors of the Linear layers (``_LAST_INPUTS``: module id -> number; a layer called with the very tensor the
+    Linear before it was called with gets the same number), so that layers fed by one tensor - q / k / v,
+    gate / up - can be grouped later without running the model again.  Only the latest input is kept alive."""
     order: dict = {}
     handles = []
+    _LAST_INPUTS.clear()
+    state = {"last": None, "number": 0}
 
     def hook(mod, args):
         order.setdefault(id(mod), len(order))
+        if isinstance(mod, nn.Linear) and args and isinstance(args[0], torch.Tensor) and id(mod) not in _LAST_INPUTS:
+            if args[0] is not state["last"]:
+                state["last"] = args[0]
+                state["number"] += 1
+            _LAST_INPUTS[id(mod)] = state["number"]
 
     for m in model.modules():
         if isinstance(m, (nn.Linear, nn.Embedding)):
@@ -226,7 +236,11 @@ def _execution_order(model: nn.Module, sample: Any) -> dict:
     finally:
         for h in handles:
             h.remove()
+        state["last"] = None
     return order
+
+
+_LAST_INPUTS: dict = {}
 
 
 def get_weight_compression_parameters(model: nn.Module, ignored_scope: Optional[Iterable[str]] = None,
@@ -502,6 +516,9 @@ def compress_weights(
     blocks and the partial Hessians are summed with an all-reduce; the inverse factor is computed on every
     rank and taken from rank 0 of the group; the rows of every weight are swept by different ranks and
     all-gathered.  Every rank returns the same compressed model.  Other algorithms run replicated."""
+    import time
+
+    t_call = time.perf_counter()
     mode = CompressWeightsMode(mode)
     check_user_compression_configuration(mode, subset_size, dataset, ratio, group_size, all_layers, awq,
                                          scale_estimation, gptq, lora_correction, sensitivity_metric, backup_mode,
@@ -622,6 +639,9 @@ def compress_weights(
         targets = [p for p in active if not p.is_embedding and p.compression_config.mode not in INT8_MODES]
         ranks = _GptqRanks(process_group)
         cal = ranks.share(items[: adv.gptq_params.subset_size])
+        if COLLECT_TIMERS:
+            torch.cuda.synchronize()
+            t_before = time.perf_counter() - t_call
         timer = _PhaseTimer(COLLECT_TIMERS)
         t_total = timer.start("total")
 
@@ -714,30 +734,42 @@ def compress_weights(
         precomputed.update({k: v for k, v in algo.apply([p for p in active if not p.is_embedding], stats).items()
                             if v.scale is not None})
 
+    if COLLECT_TIMERS and cfg["gptq"]:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        _transform_model(active, precomputed)
+        torch.cuda.synchronize()
+        TIMERS["find_layers_and_order"] = t_before
+        TIMERS["transform_model"] = time.perf_counter() - t0
+        return model
     _transform_model(active, precomputed)
     return model
 
 
 def _same_input_groups(model: nn.Module, sample: Any, targets: list) -> list:
-    """Consecutive target layers whose forward receives the identical input tensor."""
+    """Consecutive target layers whose forward receives the identical input tensor (taken from the pass that
+    established the execution order when there was one, else from a pass of its own)."""
     seen: dict = {}
-    keep = []
-    handles = []
+    if all(id(p.module) in _LAST_INPUTS for p in targets):
+        seen = {p.weight_name: _LAST_INPUTS[id(p.module)] for p in targets}
+    else:
+        keep = []
+        handles = []
 
-    def make(name):
-        def hook(mod, args):
-            seen.setdefault(name, id(args[0]))
-            keep.append(args[0])
-        return hook
+        def make(name):
+            def hook(mod, args):
+                seen.setdefault(name, id(args[0]))
+                keep.append(args[0])
+            return hook
 
-    for p in targets:
-        handles.append(p.module.register_forward_pre_hook(make(p.weight_name)))
-    try:
-        with torch.no_grad():
-            _run(model, sample)
-    finally:
-        for h in handles:
-            h.remove()
+        for p in targets:
+            handles.append(p.module.register_forward_pre_hook(make(p.weight_name)))
+        try:
+            with torch.no_grad():
+                _run(model, sample)
+        finally:
+            for h in handles:
+                h.remove()
     groups: list = []
     for p in targets:
         key = seen.get(p.weight_name)
@@ -746,6 +778,7 @@ def _same_input_groups(model: nn.Module, sample: Any, targets: list) -> list:
             groups[-1].append(p)
         else:
             groups.append([p])
+    _LAST_INPUTS.clear()
     return groups
 
 

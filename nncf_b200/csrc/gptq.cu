@@ -15,7 +15,6 @@
 // contraction accumulates in fp32 in ascending k; BLAS libraries use another order, and GPTQ
 // amplifies such last-bit differences into occasional flipped codes.
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 
 #include "quantize_kernels.cuh"
@@ -59,7 +58,7 @@ struct SweepSmem {
   static constexpr size_t bytes = (hs_floats + kSweepWarps * per_warp_floats) * sizeof(float);
 };
 
-template <int MODE, int SB>
+template <int MODE>
 __global__ void __launch_bounds__(kSweepWarps * kSweepRows) gptq_sweep_kernel(const GptqArgs a) {
   extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, t = threadIdx.x & 31;
@@ -158,6 +157,9 @@ __global__ void __launch_bounds__(kSweepWarps * kSweepRows) gptq_sweep_kernel(co
   int next_start = static_cast<int>(min(first_start - i1, static_cast<int64_t>(kGptqMaxBlock)));
   const int gs_step = static_cast<int>(min(a.gs, static_cast<int64_t>(kGptqMaxBlock)));
   int gl_next = 0;
+  // Sub-blocks of 8 and 16 columns (less unrolled code, more passes over the rest of the block) were measured at
+  // the same speed as 32: the kernel is a chain of dependent steps either way.
+  constexpr int SB = 32;
   for (int sb0 = 0; sb0 < count; sb0 += SB) {
     const int cb = min(SB, count - sb0);
     float w[SB], e[SB];
@@ -356,12 +358,7 @@ int scale_estimation_launch(const void* weight, int32_t weight_dtype, int64_t ro
 template <int MODE>
 int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, const GptqSe& se, cudaStream_t st) {
   const size_t smem = SweepSmem::bytes;
-  static const int sweep_sb = [] {
-    const char* e = std::getenv("NNCFB_SWEEP_SB");
-    const int v = e ? std::atoi(e) : 32;
-    return (v == 8 || v == 16) ? v : 32;
-  }();
-  auto sweep = sweep_sb == 8 ? gptq_sweep_kernel<MODE, 8> : sweep_sb == 16 ? gptq_sweep_kernel<MODE, 16> : gptq_sweep_kernel<MODE, 32>;
+  auto sweep = gptq_sweep_kernel<MODE>;
   NNCFB_CUDA(cudaFuncSetAttribute(sweep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const unsigned row_blocks = static_cast<unsigned>((a.rows + kSweepWarps * kSweepRows - 1) / (kSweepWarps * kSweepRows));
   const bool use_tc = tc.slab_planes[0] != nullptr;
