@@ -556,6 +556,48 @@ def run_gptq_model(args, device, rank, world, dist):
     return out
 
 
+def run_data_aware_model(args, device):
+    """Benchmark configuration 3 as written: INT4_ASYM group 128 with awq=True and scale_estimation=True on the
+    random-init Llama-3-8B-architecture bf16 model; calibration is 128 sequences of 512 token ids uniform in
+    [0, 128256) from seed 2 run through the model, with 1 % of the hidden channels of the embedding table scaled
+    by 20 to create activation outliers.  Wall time of the whole nncf_b200.compress_weights call."""
+    import transformers
+
+    import nncf_b200 as nb
+
+    layers = args.gptq_layers
+    cfg = transformers.LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=layers,
+                                   num_attention_heads=32, num_key_value_heads=8, max_position_embeddings=8192,
+                                   rope_theta=500000.0, tie_word_embeddings=False, initializer_range=0.02)
+    torch.manual_seed(1)
+    with torch.device(device):
+        model = transformers.LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    gen = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 128256, (128, 512), generator=gen)
+    outliers = torch.randperm(4096, generator=gen)[:41].to(device)      # 1 % of the hidden channels
+    with torch.no_grad():
+        model.model.embed_tokens.weight[:, outliers] *= 20.0
+        model(input_ids=ids[:1, :16].to(device))                         # process warm-up (kernel loading)
+    items = [{"input_ids": ids[k:k + 1].to(device)} for k in range(128)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_ASYM, group_size=128, ratio=1.0, awq=True,
+                        scale_estimation=True, dataset=nb.Dataset(items), subset_size=128)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    with torch.no_grad():
+        finite = bool(torch.isfinite(model(input_ids=items[0]["input_ids"][:, :64]).logits).all())
+    print(json.dumps({
+        "metric": "awq_scale_estimation_seconds_per_8b_model", "value": round(seconds * 32 / layers, 2), "unit": "s",
+        "higher_is_better": False, "n_gpus": 1, "measured_seconds": round(seconds, 2), "decoder_layers_run": layers,
+        "data": "synthetic", "dtype": "f32", "outputs_finite": finite,
+        "config": {"workload": f"LlamaForCausalLM random init, Llama-3-8B architecture ({layers} of 32 decoder layers), bf16; "
+                               "compress_weights(INT4_ASYM, group 128, awq=True, scale_estimation=True), 128 x 512 calibration "
+                               "token ids (seed 2) through the model, 41 of 4096 embedding channels x 20; whole call incl. "
+                               "statistics collection, AWQ on the down_proj / up_proj pairs, ScaleEstimation on every 4-bit "
+                               "matrix, packing and installing the decompressors"}}), flush=True)
+
+
 def run_compress(args, device, rank, world, local_rank, dist):
     from nncf_b200.pipeline import CompressionPlan, HostStreamingCompressor, bind_host_thread_near, partition_by_bytes
     from nncf_b200.sharding import ShardedCompression
@@ -840,7 +882,7 @@ def main():
     ap.add_argument("--dst-share", type=float, default=None,
                     help="N > 1: share of the source bytes the collecting rank compresses itself (default: balanced "
                          "against its NVLink ingest)")
-    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "gptq_model", "data_aware", "moe", "api"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "gptq_model", "data_aware", "data_aware_model", "moe", "api"],
                     help="compress: the headline line (default); gptq: per-kernel GPTQ timings; gptq_model: only the "
                          "GPTQ model run of the headline line")
     ap.add_argument("--mode", default="nf4", choices=["nf4", "mxfp4", "fp4"], help="mode of the moe workload")
@@ -888,10 +930,10 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    if args.workload in ("gptq", "data_aware", "api"):
+    if args.workload in ("gptq", "data_aware", "api", "data_aware_model"):
         if rank == 0:
-            {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload}[args.workload](
-                args, device)
+            {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload,
+             "data_aware_model": run_data_aware_model}[args.workload](args, device)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
