@@ -609,7 +609,8 @@ def run_compress(args, device, rank, world, local_rank, dist):
     if args.profile_case:
         specs = specs[1:8]  # one decoder layer: 436 MB of weights, larger than L2
         args.steps, args.no_e2e, args.no_cpu_baseline, args.no_gptq, args.no_parity = 1, True, True, True, True
-    sc = ShardedCompression(specs, device, rank, world, dst=0, n_chunks=args.chunks, dst_share=args.dst_share)
+    sc = ShardedCompression(specs, device, rank, world, dst=0, n_chunks=args.chunks, dst_share=args.dst_share,
+                            registered_buffers=args.registered_buffers)
     index_of = {s[0]: i for i, s in enumerate(specs)}
     weights = {i: make_weight(specs[i][1], i if not args.profile_case else i + 1, device) for i in sc.local_indices}
     sc.bind(weights)
@@ -882,6 +883,8 @@ def main():
     ap.add_argument("--dst-share", type=float, default=None,
                     help="N > 1: share of the source bytes the collecting rank compresses itself (default: balanced "
                          "against its NVLink ingest)")
+    ap.add_argument("--registered-buffers", action="store_true",
+                    help="N > 1: arenas from NCCL's allocator, registered with the communicator (zero-copy transfers)")
     ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "gptq_model", "data_aware", "data_aware_model", "moe", "api"],
                     help="compress: the headline line (default); gptq: per-kernel GPTQ timings; gptq_model: only the "
                          "GPTQ model run of the headline line")

@@ -71,7 +71,10 @@ class ShardedCompression:
 
     def __init__(self, specs: Sequence[tuple], device, rank: Optional[int] = None, world_size: Optional[int] = None,
                  dst: int = 0, n_chunks: int = 4, dst_share: Optional[float] = None,
-                 group: Optional[dist.ProcessGroup] = None):
+                 group: Optional[dist.ProcessGroup] = None, registered_buffers: bool = False):
+        """``registered_buffers``: allocate the arenas from NCCL's own allocator and register them with the
+        communicator (NCCL user-buffer registration), which lets NCCL move point-to-point data without its
+        staging copies where the transport supports it.  CUDA + NCCL only."""
         self.specs = list(specs)
         self.device = torch.device(device)
         self.group = group
@@ -124,6 +127,8 @@ class ShardedCompression:
         self._arena_bytes = off
         self.plan: Optional[CompressionPlan] = None
         self.arena: Optional[torch.Tensor] = None
+        self.registered_buffers = bool(registered_buffers) and self.world > 1 and self.device.type == "cuda"
+        self._pool = None
         self._chunk_items: list[list[int]] = []
         self._pending: list = []
         self._comm_stream = None
@@ -137,14 +142,24 @@ class ShardedCompression:
             msg = f"rank {self.rank} was not given the weights {missing[:5]}{'...' if len(missing) > 5 else ''}"
             raise ValueError(msg)
         items = [(self.specs[i][0], weights[i], self.specs[i][3]) for i in self.local_indices]
+        own_bytes = sum(self.out_sizes[i] for i in self.local_indices)
+        n_arena = self._arena_bytes if self.rank == self.dst else own_bytes
+        arena = None
+        if self.registered_buffers:
+            pg = self.group if self.group is not None else dist.distributed_c10d._get_default_group()
+            backend = pg._get_backend(self.device)
+            self._pool = torch.cuda.MemPool(backend.mem_allocator)
+            with torch.cuda.use_mem_pool(self._pool):
+                arena = torch.empty(max(n_arena, 1), dtype=torch.uint8, device=self.device)
+            backend.register_mem_pool(self._pool)
         if self.rank == self.dst:
             # one arena for the whole model; this rank's own region is where its kernels write
-            self.arena = torch.empty(self._arena_bytes, dtype=torch.uint8, device=self.device)
+            self.arena = arena if arena is not None else torch.empty(self._arena_bytes, dtype=torch.uint8, device=self.device)
             start = self._region[(self.rank, 0)][0] if self.chunks[self.rank] else 0
             own = sum(self.out_sizes[i] for i in self.local_indices)
             self.plan = self._make_plan(items, self.arena[start:start + own]) if items else None
         else:
-            self.plan = self._make_plan(items, None) if items else None
+            self.plan = self._make_plan(items, arena[:own_bytes] if arena is not None else None) if items else None
             self.arena = self.plan.arena if self.plan is not None else None
         self._chunk_items, k = [], 0
         for chunk in self.chunks[self.rank]:
