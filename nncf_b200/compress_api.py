@@ -406,6 +406,18 @@ def find_mul_merge_pairs(model: nn.Module, sample: Any, targets: dict) -> dict:
     return pairs
 
 
+_SWEEP_STREAMS: dict = {}
+
+
+def _sweep_streams(device: torch.device, count: int) -> list:
+    """Side streams for the sweeps of layers that share one inverse factor (kept per device)."""
+    have = _SWEEP_STREAMS.setdefault(device, [])
+    with torch.cuda.device(device):
+        while len(have) < count:
+            have.append(torch.cuda.Stream())
+    return have[:count]
+
+
 # --------------------------------------------------------------------------------------------------
 # GPTQ over several ranks
 # --------------------------------------------------------------------------------------------------
@@ -655,7 +667,14 @@ def compress_weights(
                                                         want_statistics=cfg["scale_estimation"], timer=timer)
             H, layer_stat = ranks.combine(H, n_local, layer_stat)
             hinv = None
-            for p in group:
+            # Layers that share the factor are independent from here on.  In one process their sweeps - chains of
+            # small dependent launches that occupy a fraction of the GPU each - are enqueued on streams of their own
+            # and run side by side; with several ranks every layer's rows are split instead and the layers go one
+            # after the other (the gathers are collectives).
+            dev = group[0].weight.device
+            main = torch.cuda.current_stream(dev)
+            side = _sweep_streams(dev, len(group) - 1) if ranks.world == 1 else []
+            for idx, p in enumerate(group):
                 n_rows = p.weight.shape[0]
                 r0, r1, per = ranks.rows(n_rows)
                 w = p.weight.data[r0:r1].float().contiguous()
@@ -663,11 +682,20 @@ def compress_weights(
                     h = timer.start("inverse_factors")
                     hinv = ranks.same_factor(g.prepare_hessian_inverse(H, w))
                     timer.stop(h)
-                h = timer.start("sweeps")
+                    h_sweeps = timer.start("sweeps")
                 q = sc = zp = None
                 if r1 > r0:
-                    q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat)
-                    q = q.to(p.weight.dtype)
+                    stream = side[idx - 1] if side and idx > 0 else main
+                    if stream is not main:
+                        stream.wait_stream(main)
+                        w.record_stream(stream)     # allocated on the main stream, consumed on the side stream
+                    with torch.cuda.stream(stream):
+                        q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat, check_status=False)
+                        q = q.to(p.weight.dtype)
+                    if stream is not main:
+                        for t in (q, sc, zp):
+                            if t is not None:
+                                t.record_stream(main)   # read on the main stream after the join below
                 if ranks.world > 1:
                     cols = p.weight.shape[1]
                     gs = p.compression_config.group_size if p.compression_config.group_size != -1 else cols
@@ -676,9 +704,12 @@ def compress_weights(
                     sc = ranks.gather_rows(sc, per, n_rows, torch.empty(pshape, dtype=torch.float32, device=q.device))
                     if p.compression_config.is_asym_mode:
                         zp = ranks.gather_rows(zp, per, n_rows, torch.empty(pshape, dtype=torch.int32, device=q.device))
-                timer.stop(h)
                 precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
                 p._gptq_weight = q
+            for stream in side:
+                main.wait_stream(stream)
+            timer.stop(h_sweeps)
+            g.check_tensor_core_status(dev)
             for p in group:
                 p.module.weight.data = p._gptq_weight.to(p.weight.dtype)
                 del p._gptq_weight

@@ -221,7 +221,7 @@ class GPTQ:
 
     def _quantize_weights(self, wc_params, hessian: torch.Tensor, weight_tensor: torch.Tensor,
                           inputs: Optional[Sequence[torch.Tensor]] = None, hinv: Optional[torch.Tensor] = None,
-                          statistics: Optional[WCTensorStatistic] = None):
+                          statistics: Optional[WCTensorStatistic] = None, check_status: bool = True):
         """gptq.py:244-379.  ``weight_tensor`` [out, C] fp32 is modified in place (trailing updates) like the
         reference's; returns (dequantised weight [out, C] fp32, scales [out, G, 1], zero points or None).
         ``hinv``: the factor returned by ``prepare_hessian_inverse`` for this Hessian, when several weights
@@ -229,7 +229,9 @@ class GPTQ:
         are then zeroed from ``hessian``'s diagonal as usual.  With ``scale_estimation=True`` (4-bit integer
         modes) every group's parameters come from ScaleEstimation on the group's current weight, as in
         gptq.py:319-327; the layer statistics are taken from ``statistics`` (per-sample means and shapes, for
-        callers that do not keep the activations) or reduced from ``inputs``."""
+        callers that do not keep the activations) or reduced from ``inputs``.  ``check_status=False`` leaves out the
+        (synchronising) read of the tensor-core kernels' status flag, for callers that enqueue several sweeps and
+        check once afterwards (``check_tensor_core_status``)."""
         config: WeightCompressionConfig = wc_params.compression_config
         assert hessian.ndim == 2, "Hessian should be 2D"
         if weight_tensor.dtype != torch.float32 or not weight_tensor.is_contiguous():
@@ -273,7 +275,7 @@ class GPTQ:
                     _lib.ptr(weight_tensor), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[config.mode.value], gs,
                     self._block_size, _lib.ptr(q), _lib.ptr(scale), _lib.ptr(zp), _lib.ptr(workspace), ws_bytes,
                     _lib.stream_handle(dev)))
-            if self._tensor_cores:
+            if self._tensor_cores and check_status:
                 _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(dev)))  # bounded waits of the TC kernels
         scales = scale.reshape(rows, G, 1)
         zero_points = zp.reshape(rows, G, 1) if zp is not None else None
@@ -283,6 +285,13 @@ class GPTQ:
         if config.mode not in (CompressWeightsMode.INT8_ASYM, CompressWeightsMode.INT4_ASYM):
             zero_points = None
         return q, scales, zero_points
+
+    @staticmethod
+    def check_tensor_core_status(device: torch.device) -> None:
+        """Raises if a bounded wait of a tensor-core kernel ran out in any call on ``device`` since the last check
+        (synchronises the current stream)."""
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(device)))
 
     def quantize_stacked(self, wc_params, hessian: torch.Tensor, weight_tensor: torch.Tensor,
                          inputs: Optional[Sequence[torch.Tensor]] = None):
