@@ -537,8 +537,8 @@ def run_gptq_model(args, device, rank, world, dist):
            "split_seconds": split, "model_build_seconds": round(t_build, 2), "outputs_finite": finite,
            "weights_in_model": n_params, "n_gpus": world,
            "sharing": None if world == 1 else "calibration items shared among the ranks (Hessians all-reduced), one inverse "
-                                              "factor (rank 0's), rows of every weight swept by different ranks and all-gathered; "
-                                              "split_seconds are rank 0's"}
+                                              "factor (rank 0's), layers that share a factor swept by different ranks and "
+                                              "broadcast; split_seconds are rank 0's"}
     tokens = args.gptq_samples * args.gptq_tokens
     if split.get("hessians"):
         # per decoder layer 3 Hessians over 4096 channels and 1 over 14336; the kernel multiplies the 128 x 256

@@ -476,24 +476,23 @@ class _GptqRanks:
             hinv._dead_columns = dead
         return hinv
 
-    def rows(self, n_rows: int) -> tuple[int, int, int]:
-        """(first row, end row, rows per rank) of this rank's slice: multiples of 128 rows, the sweep kernel's tile."""
-        if self.world == 1:
-            return 0, n_rows, n_rows
-        per = ((n_rows + self.world - 1) // self.world + 127) // 128 * 128
-        r0 = min(self.rank * per, n_rows)
-        return r0, min(r0 + per, n_rows), per
-
-    def gather_rows(self, part: Optional[torch.Tensor], per: int, n_rows: int, like: torch.Tensor) -> torch.Tensor:
-        """All ranks' row slices stacked back into [n_rows, ...]; ``like`` gives trailing shape, dtype and device."""
-        if self.world == 1:
-            return part
-        buf = torch.zeros((per, *like.shape[1:]), dtype=like.dtype, device=like.device)
-        if part is not None and part.shape[0] > 0:
-            buf[: part.shape[0]].copy_(part)
-        out = torch.empty((self.world * per, *like.shape[1:]), dtype=like.dtype, device=like.device)
-        self.dist.all_gather_into_tensor(out, buf, group=self.group)
-        return out[:n_rows]
+    def from_owner(self, owner: int, p: WeightCompressionParameters, q, scale, zero_point):
+        """Results of one layer's sweep from the rank that ran it: dequantised weight (in the weight's dtype),
+        scales and (asymmetric modes) zero points, allocated here on the other ranks."""
+        cfg = p.compression_config
+        rows, cols = p.weight.shape
+        gs = cfg.group_size if cfg.group_size != -1 else cols
+        pshape = (rows, cols // gs, 1) if cfg.group_size != -1 else (rows, 1)
+        dev = p.weight.device
+        if self.rank != owner:
+            q = torch.empty((rows, cols), dtype=p.weight.dtype, device=dev)
+            scale = torch.empty(pshape, dtype=torch.float32, device=dev)
+            zero_point = torch.empty(pshape, dtype=torch.int32, device=dev) if cfg.is_asym_mode else None
+        src = self.dist.get_global_rank(self.group, owner)
+        for t in (q, scale, zero_point):
+            if t is not None:
+                self.dist.broadcast(t, src, group=self.group)
+        return q, scale, zero_point
 
 
 # --------------------------------------------------------------------------------------------------
@@ -526,8 +525,9 @@ def compress_weights(
     ranks each hold a replica of ``model`` on their own GPU and call this function together with the same
     arguments.  GPTQ is then shared out: every rank runs its share of the calibration items through the
     blocks and the partial Hessians are summed with an all-reduce; the inverse factor is computed on every
-    rank and taken from rank 0 of the group; the rows of every weight are swept by different ranks and
-    all-gathered.  Every rank returns the same compressed model.  Other algorithms run replicated."""
+    rank and taken from rank 0 of the group; layers that share a factor (q / k / v, gate / up) are swept by
+    different ranks and broadcast.  Every rank returns the same compressed model.  Other algorithms run
+    replicated."""
     import time
 
     t_call = time.perf_counter()
@@ -667,24 +667,24 @@ def compress_weights(
                                                         want_statistics=cfg["scale_estimation"], timer=timer)
             H, layer_stat = ranks.combine(H, n_local, layer_stat)
             hinv = None
-            # Layers that share the factor are independent from here on.  In one process their sweeps - chains of
-            # small dependent launches that occupy a fraction of the GPU each - are enqueued on streams of their own
-            # and run side by side; with several ranks every layer's rows are split instead and the layers go one
-            # after the other (the gathers are collectives).
+            # Layers that share the factor are independent from here on, and a sweep is a chain of small dependent
+            # launches whose duration hardly depends on the number of rows.  In one process the layers' sweeps are
+            # enqueued on streams of their own and run side by side.  With several ranks each layer of the group
+            # is swept by one rank (layer i by rank i mod world) and broadcast; a layer that is alone in its group
+            # is swept by every rank for itself, which gives identical bits everywhere without any exchange.
             dev = group[0].weight.device
             main = torch.cuda.current_stream(dev)
             side = _sweep_streams(dev, len(group) - 1) if ranks.world == 1 else []
+            shared_out = ranks.world > 1 and len(group) > 1
             for idx, p in enumerate(group):
-                n_rows = p.weight.shape[0]
-                r0, r1, per = ranks.rows(n_rows)
-                w = p.weight.data[r0:r1].float().contiguous()
+                w = p.weight.data.float().contiguous()
                 if hinv is None:
                     h = timer.start("inverse_factors")
                     hinv = ranks.same_factor(g.prepare_hessian_inverse(H, w))
                     timer.stop(h)
                     h_sweeps = timer.start("sweeps")
                 q = sc = zp = None
-                if r1 > r0:
+                if not shared_out or idx % ranks.world == ranks.rank:
                     stream = side[idx - 1] if side and idx > 0 else main
                     if stream is not main:
                         stream.wait_stream(main)
@@ -696,14 +696,8 @@ def compress_weights(
                         for t in (q, sc, zp):
                             if t is not None:
                                 t.record_stream(main)   # read on the main stream after the join below
-                if ranks.world > 1:
-                    cols = p.weight.shape[1]
-                    gs = p.compression_config.group_size if p.compression_config.group_size != -1 else cols
-                    pshape = (1, cols // gs, 1) if p.compression_config.group_size != -1 else (1, 1)
-                    q = ranks.gather_rows(q, per, n_rows, p.weight.data)
-                    sc = ranks.gather_rows(sc, per, n_rows, torch.empty(pshape, dtype=torch.float32, device=q.device))
-                    if p.compression_config.is_asym_mode:
-                        zp = ranks.gather_rows(zp, per, n_rows, torch.empty(pshape, dtype=torch.int32, device=q.device))
+                if shared_out:
+                    q, sc, zp = ranks.from_owner(idx % ranks.world, p, q, sc, zp)
                 precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
                 p._gptq_weight = q
             for stream in side:
