@@ -191,9 +191,10 @@ int nncfb_hessian_status(void* stream);
  * (agrees with the fp32 contraction to ~1e-7 relative).  That kernel bounds every wait like the Hessian kernel;
  * nncfb_hessian_status() reports a wait that gave up.  On this path the part of a block's update that the next
  * block does not need yet runs on a stream of the library's own (one non-blocking stream and two events per
- * device, created on first use; no device memory), ordered against `stream` by events in both directions: all
- * work is complete, in stream order, when `stream` reaches the end of the call, and the sequence may be captured
- * into a CUDA graph like any fork / join.  Calls on one device are serialised by a mutex while they enqueue.
+ * device and caller stream, created on first use and kept; no device memory), ordered against `stream` by events
+ * in both directions: all work is complete, in stream order, when `stream` reaches the end of the call, and the
+ * sequence may be captured into a CUDA graph like any fork / join.  Calls on different streams of one device run
+ * side by side; calls on the same stream are serialised by a mutex while they enqueue.
  * Replaces WC/gptq.py:297-379 (the loop of GPTQ._quantize_weights).
  */
 size_t nncfb_gptq_workspace_bytes(int64_t rows);

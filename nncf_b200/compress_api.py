@@ -406,16 +406,13 @@ def find_mul_merge_pairs(model: nn.Module, sample: Any, targets: dict) -> dict:
     return pairs
 
 
-_SWEEP_STREAMS: dict = {}
+_SM_COUNT: dict = {}
 
 
-def _sweep_streams(device: torch.device, count: int) -> list:
-    """Side streams for the sweeps of layers that share one inverse factor (kept per device)."""
-    have = _SWEEP_STREAMS.setdefault(device, [])
-    with torch.cuda.device(device):
-        while len(have) < count:
-            have.append(torch.cuda.Stream())
-    return have[:count]
+def _sm_count(device: torch.device) -> int:
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[device]
 
 
 # --------------------------------------------------------------------------------------------------
@@ -668,16 +665,21 @@ def compress_weights(
             H, layer_stat = ranks.combine(H, n_local, layer_stat)
             hinv = None
             # Layers that share the factor are independent from here on, and a sweep is a chain of small dependent
-            # launches whose duration hardly depends on the number of rows.  In one process the layers' sweeps are
-            # enqueued on streams of their own and run side by side.  With several ranks each layer of the group
-            # is swept by one rank (layer i by rank i mod world) and broadcast; a layer that is alone in its group
-            # is swept by every rank for itself, which gives identical bits everywhere without any exchange.
+            # launches whose duration hardly depends on the number of rows (up to one 128-row tile per SM).  In one
+            # process the layers of a group with the same configuration are therefore stacked row-wise and swept as
+            # ONE weight (q / k / v: one chain of 32 blocks instead of three; rows are independent, so the result is
+            # the same).  With several ranks each layer of the group is swept by one rank (layer i by rank
+            # i mod world) and broadcast; a layer that is alone in its group is swept by every rank for itself, which
+            # gives identical bits everywhere without any exchange.
             dev = group[0].weight.device
-            main = torch.cuda.current_stream(dev)
-            side = _sweep_streams(dev, len(group) - 1) if ranks.world == 1 else []
             shared_out = ranks.world > 1 and len(group) > 1
-            for idx, p in enumerate(group):
-                w = p.weight.data.float().contiguous()
+            stack = (ranks.world == 1 and len(group) > 1 and
+                     all(p.compression_config == group[0].compression_config for p in group) and
+                     sum(p.weight.shape[0] for p in group) <= 128 * _sm_count(dev))
+            units = [group] if stack else [[p] for p in group]
+            for idx, unit in enumerate(units):
+                w = torch.cat([p.weight.data.float() for p in unit], 0).contiguous() if len(unit) > 1 else \
+                    unit[0].weight.data.float().contiguous()
                 if hinv is None:
                     h = timer.start("inverse_factors")
                     hinv = ranks.same_factor(g.prepare_hessian_inverse(H, w))
@@ -685,23 +687,16 @@ def compress_weights(
                     h_sweeps = timer.start("sweeps")
                 q = sc = zp = None
                 if not shared_out or idx % ranks.world == ranks.rank:
-                    stream = side[idx - 1] if side and idx > 0 else main
-                    if stream is not main:
-                        stream.wait_stream(main)
-                        w.record_stream(stream)     # allocated on the main stream, consumed on the side stream
-                    with torch.cuda.stream(stream):
-                        q, sc, zp = g._quantize_weights(p, H, w, hinv=hinv, statistics=layer_stat, check_status=False)
-                        q = q.to(p.weight.dtype)
-                    if stream is not main:
-                        for t in (q, sc, zp):
-                            if t is not None:
-                                t.record_stream(main)   # read on the main stream after the join below
+                    q, sc, zp = g._quantize_weights(unit[0], H, w, hinv=hinv, statistics=layer_stat, check_status=False)
+                    q = q.to(unit[0].weight.dtype)
                 if shared_out:
-                    q, sc, zp = ranks.from_owner(idx % ranks.world, p, q, sc, zp)
-                precomputed[p.weight_name] = CompressedWeight(None, sc, zp)
-                p._gptq_weight = q
-            for stream in side:
-                main.wait_stream(stream)
+                    q, sc, zp = ranks.from_owner(idx % ranks.world, unit[0], q, sc, zp)
+                r0 = 0
+                for p in unit:
+                    r1 = r0 + p.weight.shape[0]
+                    precomputed[p.weight_name] = CompressedWeight(None, sc[r0:r1], zp[r0:r1] if zp is not None else None)
+                    p._gptq_weight = q[r0:r1]
+                    r0 = r1
             timer.stop(h_sweeps)
             g.check_tensor_core_status(dev)
             for p in group:

@@ -15,7 +15,10 @@
 // contraction accumulates in fp32 in ascending k; BLAS libraries use another order, and GPTQ
 // amplifies such last-bit differences into occasional flipped codes.
 #include <algorithm>
+#include <map>
+#include <memory>
 #include <mutex>
+#include <utility>
 
 #include "quantize_kernels.cuh"
 
@@ -313,25 +316,30 @@ struct GptqTcScratch {
   int64_t slab_ld = 0;
 };
 
-// Side stream and events of the look-ahead schedule, one set per device, created on first use.
+// Side stream and events of the look-ahead schedule: one set per (device, caller stream), created on first use and
+// kept for the life of the process, so that calls enqueued on different streams of one device (the sweeps of layers
+// that share a factor) do not queue behind one another on a common side stream.
 struct Lookahead {
   cudaStream_t side = nullptr;
   cudaEvent_t panel_done = nullptr, rest_done = nullptr;
+  std::mutex in_use;  // held while a call enqueues: two host threads may target the same stream
 };
 std::mutex g_lookahead_mutex;
-Lookahead g_lookahead[64];
+std::map<std::pair<int, cudaStream_t>, std::unique_ptr<Lookahead>> g_lookahead;
 
-int lookahead_for_current_device(Lookahead** out) {
+int lookahead_for(cudaStream_t st, Lookahead** out) {
   int dev = 0;
   NNCFB_CUDA(cudaGetDevice(&dev));
-  NNCFB_CHECK_ARG(dev >= 0 && dev < 64, NNCFB_E_UNSUPPORTED, "nncfb_gptq_quantize: device ordinal %d >= 64", dev);
-  Lookahead& l = g_lookahead[dev];
-  if (l.side == nullptr) {
-    NNCFB_CUDA(cudaStreamCreateWithFlags(&l.side, cudaStreamNonBlocking));
-    NNCFB_CUDA(cudaEventCreateWithFlags(&l.panel_done, cudaEventDisableTiming));
-    NNCFB_CUDA(cudaEventCreateWithFlags(&l.rest_done, cudaEventDisableTiming));
+  std::lock_guard<std::mutex> lock(g_lookahead_mutex);
+  auto& slot = g_lookahead[std::make_pair(dev, st)];
+  if (!slot) {
+    std::unique_ptr<Lookahead> l(new Lookahead());
+    NNCFB_CUDA(cudaStreamCreateWithFlags(&l->side, cudaStreamNonBlocking));
+    NNCFB_CUDA(cudaEventCreateWithFlags(&l->panel_done, cudaEventDisableTiming));
+    NNCFB_CUDA(cudaEventCreateWithFlags(&l->rest_done, cudaEventDisableTiming));
+    slot = std::move(l);
   }
-  *out = &l;
+  *out = slot.get();
   return NNCFB_OK;
 }
 
@@ -363,11 +371,11 @@ int run_gptq(GptqArgs a, int block, const GptqTcScratch& tc, const GptqSe& se, c
   const unsigned row_blocks = static_cast<unsigned>((a.rows + kSweepWarps * kSweepRows - 1) / (kSweepWarps * kSweepRows));
   const bool use_tc = tc.slab_planes[0] != nullptr;
   Lookahead* la = nullptr;
-  std::unique_lock<std::mutex> lock(g_lookahead_mutex, std::defer_lock);
+  std::unique_lock<std::mutex> lock;
   if (use_tc) {
-    lock.lock();  // the side stream and its two events are shared by every call on this device
-    const int rc = lookahead_for_current_device(&la);
+    const int rc = lookahead_for(st, &la);
     if (rc != NNCFB_OK) return rc;
+    lock = std::unique_lock<std::mutex>(la->in_use);  // the side stream and its events belong to one call at a time
   }
   // A group that reaches beyond its block makes the sweep read columns the previous block's rest update is
   // still writing, so the two may only overlap when every group lies inside one block.
