@@ -500,7 +500,7 @@ def run_gptq_model(args, device, rank, world, dist):
     adv = nb.AdvancedCompressionParameters(gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.01, block_size=128,
                                                                                 subset_size=args.gptq_samples))
     with torch.no_grad():
-        model(input_ids=items[0]["input_ids"][:, :16])   # process warm-up: loads the GEMM / attention kernels once
+        model(input_ids=items[0]["input_ids"])   # process warm-up: one forward pass of one calibration item
     compress_api.COLLECT_TIMERS = True
     compress_api.TIMERS.clear()
     group = dist.group.WORLD if world > 1 else None
@@ -531,8 +531,8 @@ def run_gptq_model(args, device, rank, world, dist):
            "config": {"workload": f"LlamaForCausalLM random init, Llama-3-8B architecture with {layers} of 32 decoder "
                                   f"layers, bf16; {args.gptq_samples} x {args.gptq_tokens} calibration token ids (seed 3) "
                                   "through the model; compress_weights(INT4_SYM, group 128, gptq=True, damp 0.01, block "
-                                  "128), embed_tokens / lm_head on the INT8_ASYM backup; one 16-token forward pass before "
-                                  "the timed call loads the model's kernels",
+                                  "128), embed_tokens / lm_head on the INT8_ASYM backup; one forward pass of one calibration item "
+                                  "before the timed call (kernel loading, allocator warm-up)",
                       "extrapolated": None if layers == 32 else f"value = measured x 32 / {layers} (per-layer work is identical)"},
            "split_seconds": split, "model_build_seconds": round(t_build, 2), "outputs_finite": finite,
            "weights_in_model": n_params, "n_gpus": world,
