@@ -777,8 +777,8 @@ def run_compress(args, device, rank, world, local_rank, dist):
         torch.cuda.synchronize()
         e2e_specs = [(specs[i][0], specs[i][1], specs[i][2], specs[i][3]) for i in mine]
         del plan, weights
-        sc.plan, sc.arena = None, None
-        del sc
+        sc.close()
+        sc = None
         torch.cuda.empty_cache()
         if e2e_specs:
             hsc = HostStreamingCompressor(e2e_specs, device)
@@ -810,6 +810,12 @@ def run_compress(args, device, rank, world, local_rank, dist):
             del hsc, host_w
         else:
             e2e = {"value": None, "unit": UNIT, "skipped": "not enough free host memory to pin even one tensor"}
+        torch.cuda.empty_cache()
+
+    if sc is not None:
+        plan = weights = None
+        sc.close()
+        sc = None
         torch.cuda.empty_cache()
 
     # ---- GPTQ seconds per 8B model (the second half of the metric) ---------------------------------------

@@ -236,6 +236,19 @@ class ShardedCompression:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
         self._pending = []
 
+    def close(self) -> None:
+        """Release the arenas.  With ``registered_buffers`` this must run before the process group is destroyed:
+        the pool is deregistered from the communicator first, then its memory is returned."""
+        self._pending = []
+        self.plan = None
+        self.arena = None
+        if self._pool is not None:
+            pg = self.group if self.group is not None else dist.distributed_c10d._get_default_group()
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            pg._get_backend(self.device).deregister_mem_pool(self._pool)
+            self._pool = None
+
     # ------------------------------------------------------------------------------------------------
     def results(self) -> dict:
         """On the collecting rank: {name: {field: tensor}} for every weight of the model (views into the arena).
