@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define NNCFB_ABI_VERSION 1
+#define NNCFB_ABI_VERSION 2
 
 /* status codes */
 #define NNCFB_OK 0
@@ -83,6 +83,10 @@ typedef struct nncfb_quantize_args {
   float* values_out;      /* float modes: decoded fp32 grid value per element (the reference's `tensor`); may be NULL */
   float* dq_out;          /* dequantised fp32 weight per element; may be NULL */
   float* sqerr_out;       /* fp32 [outer, G, inner]: sum over the group of (dq - w)^2; may be NULL */
+  uint8_t* zp_packed_out; /* asym modes: the zero points as the decompressor stores them (layers.py:1318,1390): one
+                             uint8 per group for 8-bit modes; for 4-bit modes two groups per byte in flat group
+                             order, even group in the low nibble (pack_uint4 of the zero-point tensor).  4-byte
+                             aligned, ((n_groups + 7) / 8) * 4 bytes for 4-bit modes; may be NULL */
 } nncfb_quantize_args;
 
 /*

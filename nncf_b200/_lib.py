@@ -40,6 +40,7 @@ class QuantizeArgs(C.Structure):
         ("pre_scale", C.c_void_p), ("pre_zp", C.c_void_p), ("pre_zp_dtype", C.c_int32), ("codes_format", C.c_int32),
         ("codes_out", C.c_void_p), ("scale_out", C.c_void_p), ("zp_out", C.c_void_p), ("scale_f16_out", C.c_void_p),
         ("scale_e8m0_out", C.c_void_p), ("values_out", C.c_void_p), ("dq_out", C.c_void_p), ("sqerr_out", C.c_void_p),
+        ("zp_packed_out", C.c_void_p),
     ]
 
 

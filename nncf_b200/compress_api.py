@@ -1190,6 +1190,10 @@ def _make_decompressor(p: WeightCompressionParameters, item) -> nn.Module:
     if cfg.num_bits == 8:
         pshape = (out_ch, 1)
         if cfg.mode == _M.INT8_ASYM:
+            stored = getattr(item, "zero_point_packed", None)
+            if stored is not None:   # written by the kernel in its stored form: no range check, no cast
+                return INT8AsymmetricWeightsDecompressor(item.scale.reshape(pshape), stored.reshape(pshape), w.dtype,
+                                                         zero_point_is_stored=True)
             return INT8AsymmetricWeightsDecompressor(item.scale.reshape(pshape), item.zero_point.reshape(pshape), w.dtype)
         return INT8SymmetricWeightsDecompressor(item.scale.reshape(pshape), w.dtype)
     grouped = (out_ch, G, gs) if cfg.group_size != -1 else (out_ch, in_ch)
@@ -1197,6 +1201,12 @@ def _make_decompressor(p: WeightCompressionParameters, item) -> nn.Module:
     if cfg.mode == _M.INT4_SYM:
         return INT4SymmetricWeightsDecompressor(item.scale.reshape(pshape), grouped, tuple(w.shape), w.dtype)
     if cfg.mode == _M.INT4_ASYM:
+        stored = getattr(item, "zero_point_packed", None)
+        if stored is not None:       # nibble-packed by the kernel (two groups per byte, flat group order)
+            n_groups = out_ch * G
+            return INT4AsymmetricWeightsDecompressor(item.scale.reshape(pshape), stored.reshape(-1)[: (n_groups + 1) // 2]
+                                                     .reshape(-1, 1), grouped, tuple(w.shape), w.dtype,
+                                                     zero_point_shape=pshape)
         return INT4AsymmetricWeightsDecompressor(item.scale.reshape(pshape), item.zero_point.reshape(pshape), grouped,
                                                  tuple(w.shape), w.dtype)
     scale = item.scale_e8m0.reshape(pshape) if cfg.mode == _M.MXFP4 else item.scale.reshape(pshape)
@@ -1211,7 +1221,8 @@ def _transform_model(active: list, precomputed: dict) -> None:
     plain = [p for p in active if p.weight_name not in precomputed]
     results = {}
     if plain:
-        plan = CompressionPlan([(p.weight_name, p.weight.data.contiguous(), p.compression_config) for p in plain])
+        plan = CompressionPlan([(p.weight_name, p.weight.data.contiguous(), p.compression_config) for p in plain],
+                               packed_zero_points=True)
         plan.run(use_graph=False)
         for p, it in zip(plain, plan.items):
             results[p.weight_name] = it

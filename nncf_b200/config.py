@@ -60,7 +60,8 @@ class CompressedWeight:
     float modes - the same content the reference's torch path returns.  The remaining fields are
     additions of this build: ``packed`` (nibble-packed / byte codes as stored in a model),
     ``scale_e8m0`` (exponent byte of MX scales), ``scale_f16`` (the decompressor's fp16 scale
-    buffer) and ``grouped_shape`` (shape of the codes before packing)."""
+    buffer), ``zero_point_packed`` (the decompressor's zero-point buffer: uint8, nibble-packed for 4-bit modes) and
+    ``grouped_shape`` (shape of the codes before packing)."""
 
     tensor: Optional[torch.Tensor] = None
     scale: Optional[torch.Tensor] = None
@@ -70,6 +71,7 @@ class CompressedWeight:
     packed: Optional[torch.Tensor] = None
     scale_e8m0: Optional[torch.Tensor] = None
     scale_f16: Optional[torch.Tensor] = None
+    zero_point_packed: Optional[torch.Tensor] = None
     grouped_shape: Optional[tuple] = None
 
     def get_unscaled_tensor(self) -> Optional[torch.Tensor]:

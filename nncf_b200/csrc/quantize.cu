@@ -22,6 +22,7 @@ int launch_fast_run(const nncfb_quantize_args* items, int n, FastClass cls, cuda
     t.codes = static_cast<uint8_t*>(p.codes_out);
     t.scale = p.scale_out;
     t.zp = p.zp_out;
+    t.zp_packed = p.zp_packed_out;
     t.scale_f16 = p.scale_f16_out;
     t.e8m0 = p.scale_e8m0_out;
     t.n_groups = p.outer * (p.reduce / p.group_size);
@@ -133,6 +134,7 @@ int launch_general(const nncfb_quantize_args* p, cudaStream_t st) {
   a.codes_format = p->codes_format;
   a.scale_out = p->scale_out;
   a.zp_out = p->zp_out;
+  a.zp_packed = asym ? p->zp_packed_out : nullptr;
   a.scale_f16 = p->scale_f16_out;
   a.scale_e8m0 = p->scale_e8m0_out;
   a.values = p->values_out;
@@ -143,6 +145,12 @@ int launch_general(const nncfb_quantize_args* p, cudaStream_t st) {
   a.inner = p->inner;
   a.n_groups = p->outer * a.groups_per_row * p->inner;
   a.lanes_per_group = static_cast<int>(p->group_size / 8);
+  if (a.zp_packed != nullptr && mode_bits(p->mode) == 4) {
+    // nibbles are ORed into place by whichever thread owns the group: the words start at zero
+    NNCFB_CHECK_ARG((reinterpret_cast<uintptr_t>(a.zp_packed) & 3u) == 0, NNCFB_E_ALIGNMENT,
+                    "nncfb_quantize: zp_packed_out must be 4-byte aligned");
+    NNCFB_CUDA(cudaMemsetAsync(a.zp_packed, 0, static_cast<size_t>((a.n_groups + 7) / 8) * 4, st));
+  }
 
   const bool aligned = aligned16(p->weight) && aligned16(p->codes_out) && aligned16(p->values_out) &&
                        aligned16(p->dq_out);

@@ -39,6 +39,7 @@ struct FastTensor {
   uint16_t* scale_f16;
   uint8_t* e8m0;
   int64_t n_groups;
+  uint8_t* zp_packed;  // stored form of the zero points: u8 per group (8-bit modes) or two groups per byte (4-bit)
 };
 
 struct FastBatch {
@@ -462,6 +463,10 @@ __device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_
     }
     bool clamp = false;
     if constexpr (mode_is_asym(MODE)) clamp = __any_sync(0xffffffffu, need_clamp && owner);
+    // zero point of the next group (lane + 1): the two nibbles of a byte of the packed zero points; `first` and
+    // the number of owner lanes are even, so an even lane always owns an even group
+    float zp_next = 0.0f;
+    if constexpr (mode_is_asym(MODE) && mode_bits(MODE) == 4) zp_next = __shfl_down_sync(0xffffffffu, zp, 1);
     if (owner) {
       const int64_t g = first + lane;
       if constexpr (mode_is_fast_float(MODE)) {
@@ -470,7 +475,20 @@ __device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_
         T.scale[g] = s;
       }
       if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
-      if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+      if constexpr (mode_is_asym(MODE)) {
+        if (T.zp) T.zp[g] = static_cast<int32_t>(zp);
+        if (T.zp_packed) {
+          if constexpr (mode_bits(MODE) == 4) {
+            if ((lane & 1) == 0) {
+              const bool has_next = FULL || g + 1 < n_groups;
+              const uint32_t hi = has_next ? static_cast<uint32_t>(static_cast<int32_t>(zp_next)) : 0u;
+              T.zp_packed[g >> 1] = static_cast<uint8_t>(static_cast<uint32_t>(static_cast<int32_t>(zp)) | (hi << 4));
+            }
+          } else {
+            T.zp_packed[g] = static_cast<uint8_t>(static_cast<int32_t>(zp));
+          }
+        }
+      }
       if constexpr (mode_is_mx(MODE)) {
         if (T.e8m0) T.e8m0[g] = static_cast<uint8_t>(e8 + 127);
       }
@@ -576,10 +594,26 @@ __device__ __forceinline__ void rows_iteration(const FastTensor& T, const int64_
           }
         }
       }
+      const int sub = (threadIdx.x & 31) / L;
+      float zp_next = 0.0f;   // zero point of group g + 1, owned by the next sub-warp (g is even iff `sub` is)
+      if constexpr (mode_is_asym(MODE) && mode_bits(MODE) == 4) zp_next = __shfl_sync(0xffffffffu, zp, (sub | 1) * L);
       if (valid && lig == 0) {
         T.scale[g] = s;
         if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
-        if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+        if constexpr (mode_is_asym(MODE)) {
+          if (T.zp) T.zp[g] = static_cast<int32_t>(zp);
+          if (T.zp_packed) {
+            if constexpr (mode_bits(MODE) == 4) {
+              if ((sub & 1) == 0) {
+                const bool has_next = FULL || g + 1 < n_groups;
+                const uint32_t hi = has_next ? static_cast<uint32_t>(static_cast<int32_t>(zp_next)) : 0u;
+                T.zp_packed[g >> 1] = static_cast<uint8_t>(static_cast<uint32_t>(static_cast<int32_t>(zp)) | (hi << 4));
+              }
+            } else {
+              T.zp_packed[g] = static_cast<uint8_t>(static_cast<int32_t>(zp));
+            }
+          }
+        }
       }
     }
   }
@@ -734,7 +768,12 @@ __device__ __forceinline__ void channel_iteration(const FastTensor& T, const int
   if (valid && tir == 0) {
     T.scale[g] = s;
     if (T.scale_f16) T.scale_f16[g] = __half_as_ushort(__float2half_rn(s));
-    if constexpr (mode_is_asym(MODE)) T.zp[g] = static_cast<int32_t>(zp);
+    if constexpr (mode_is_asym(MODE)) {
+      if (T.zp) T.zp[g] = static_cast<int32_t>(zp);
+      if constexpr (mode_bits(MODE) == 8) {
+        if (T.zp_packed) T.zp_packed[g] = static_cast<uint8_t>(static_cast<int32_t>(zp));
+      }
+    }
   }
 }
 

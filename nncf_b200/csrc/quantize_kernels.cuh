@@ -26,6 +26,7 @@ struct QArgs {
   int codes_format;
   float* scale_out;
   int32_t* zp_out;
+  uint8_t* zp_packed;  // stored form of the zero points (u8 per group, or two 4-bit groups per byte); zeroed by the host
   uint16_t* scale_f16;
   uint8_t* scale_e8m0;
   float* values;
@@ -215,6 +216,15 @@ __device__ __forceinline__ void store_group_params(const QArgs& a, int64_t g, co
   if (a.scale_f16) a.scale_f16[g] = __half_as_ushort(__float2half_rn(c.scale));
   if constexpr (mode_is_asym(MODE)) {
     if (a.zp_out) a.zp_out[g] = static_cast<int32_t>(c.zp);
+    if (a.zp_packed) {
+      const uint32_t z = static_cast<uint32_t>(static_cast<int32_t>(c.zp));
+      if constexpr (mode_bits(MODE) == 4) {
+        // groups are owned by unrelated threads here: each ORs its nibble into the (zeroed) word that holds it
+        atomicOr(reinterpret_cast<unsigned int*>(a.zp_packed) + (g >> 3), (z & 15u) << (4 * static_cast<int>(g & 7)));
+      } else {
+        a.zp_packed[g] = static_cast<uint8_t>(z);
+      }
+    }
   }
   if constexpr (mode_is_mx(MODE)) {
     if (a.scale_e8m0) a.scale_e8m0[g] = static_cast<uint8_t>(c.e8m0 + 127);

@@ -108,12 +108,15 @@ inline FastClass fast_class(const nncfb_quantize_args& p) {
     return none;
   if (p.scale_e8m0_out && !mode_is_mx(p.mode)) return none;
   if (!p.scale_out && !(mode_is_mx(p.mode) && p.scale_e8m0_out)) return none;
-  if (mode_is_asym(p.mode) && !p.zp_out) return none;
+  if (mode_is_asym(p.mode) && !p.zp_out && !p.zp_packed_out) return none;
   const bool four = mode_bits(p.mode) == 4;
   if (p.codes_format != (four ? NNCFB_CODES_NIBBLE : NNCFB_CODES_BYTE)) return none;
   if (!aligned16(p.weight) || !aligned16(p.codes_out)) return none;
   if (p.group_size == 128 || p.group_size == 64 || p.group_size == 32) return FastClass{1, p.group_size};
   if (fast_float) return none;  // per-channel float modes use the general kernels
+  // the per-channel kernel writes packed zero points one byte per row only: two rows per byte (4-bit) is left
+  // to the general kernels
+  if (p.zp_packed_out && four) return none;
   if (p.group_size == p.reduce && p.reduce % 8 == 0 && p.reduce >= 512) return FastClass{2, p.reduce};
   return none;
 }

@@ -101,10 +101,13 @@ class INT8AsymmetricWeightsDecompressor(BaseWeightsDecompressor):
 
     mode = CompressWeightsMode.INT8_ASYM
 
-    def __init__(self, scale: torch.Tensor, zero_point: torch.Tensor, result_dtype: Optional[torch.dtype] = None):
+    def __init__(self, scale: torch.Tensor, zero_point: torch.Tensor, result_dtype: Optional[torch.dtype] = None,
+                 zero_point_is_stored: bool = False):
+        """``zero_point_is_stored``: ``zero_point`` is already the uint8 buffer (written by the compression kernel),
+        so the range check and cast of ``pack_weight`` are not repeated."""
         super().__init__(None, None, result_dtype)
         self.register_buffer("_scale", scale.to(torch.float16))
-        self.register_buffer("_zero_point", self.pack_weight(zero_point))
+        self.register_buffer("_zero_point", zero_point if zero_point_is_stored else self.pack_weight(zero_point))
 
     def pack_weight(self, weight: torch.Tensor) -> torch.Tensor:
         if torch.is_floating_point(weight):
@@ -145,11 +148,18 @@ class INT4AsymmetricWeightsDecompressor(BaseWeightsDecompressor):
 
     mode = CompressWeightsMode.INT4_ASYM
 
-    def __init__(self, scale, zero_point, compressed_weight_shape, result_shape=None, result_dtype=None):
+    def __init__(self, scale, zero_point, compressed_weight_shape, result_shape=None, result_dtype=None,
+                 zero_point_shape=None):
+        """``zero_point_shape``: given when ``zero_point`` is already nibble-packed ([n / 2, 1] uint8, written by the
+        compression kernel); it is then the shape of the unpacked zero points."""
         super().__init__(compressed_weight_shape, result_shape, result_dtype)
         self.register_buffer("_scale", scale.to(torch.float16))
-        self.zero_point_shape = tuple(zero_point.shape)
-        self.register_buffer("_zero_point", self.pack_weight(zero_point))
+        if zero_point_shape is not None:
+            self.zero_point_shape = tuple(zero_point_shape)
+            self.register_buffer("_zero_point", zero_point)
+        else:
+            self.zero_point_shape = tuple(zero_point.shape)
+            self.register_buffer("_zero_point", self.pack_weight(zero_point))
 
     def pack_weight(self, weight: torch.Tensor) -> torch.Tensor:
         if torch.any((weight < 0) | (weight > 15)):

@@ -60,6 +60,8 @@ class PlanItem:
         n += self.scale.numel() * 4
         if self.zero_point is not None:
             n += self.zero_point.numel() * 4
+        if self.zero_point_packed is not None:
+            n += self.zero_point_packed.numel()
         if self.scale_e8m0 is not None:
             n += self.scale_e8m0.numel()
         return n
@@ -73,7 +75,7 @@ def _pad(n: int) -> int:
 
 
 def stored_outputs(name: str, shape: Sequence[int], axis: int, cfg: WeightCompressionConfig,
-                   fp16_scales: bool = False) -> list[tuple[str, torch.dtype, int]]:
+                   fp16_scales: bool = False, packed_zero_points: bool = False) -> list[tuple[str, torch.dtype, int]]:
     """(field, dtype, element count) of everything the stored form of one weight consists of, in the order the
     plan allocates them.  Depends only on shape and configuration, so a rank can lay out another rank's results
     without asking it."""
@@ -96,7 +98,11 @@ def stored_outputs(name: str, shape: Sequence[int], axis: int, cfg: WeightCompre
     if fp16_scales:
         outs.append(("scale_f16", torch.float16, n_groups))
     if cfg.is_integer and cfg.is_asym_mode:
-        outs.append(("zero_point", torch.int32, n_groups))
+        if packed_zero_points:
+            # the decompressor's buffer: a byte per group, or two 4-bit groups per byte (whole 32-bit words)
+            outs.append(("zero_point_packed", torch.uint8, (n_groups + 7) // 8 * 4 if four_bit else n_groups))
+        else:
+            outs.append(("zero_point", torch.int32, n_groups))
     if cfg.mode in (CompressWeightsMode.MXFP4, CompressWeightsMode.MXFP8_E4M3):
         outs.append(("scale_e8m0", torch.uint8, n_groups))
     return outs
@@ -126,10 +132,12 @@ class CompressionPlan:
     E8M0 exponent bytes for MX modes."""
 
     def __init__(self, items: Sequence[tuple], device: Optional[torch.device] = None, fp16_scales: bool = False,
-                 arena: Optional[torch.Tensor] = None, use_arena: bool = False):
+                 arena: Optional[torch.Tensor] = None, use_arena: bool = False, packed_zero_points: bool = False):
         """``use_arena``: put every output into one byte buffer (``self.arena``; ``arena`` supplies it), item after
         item, each output on a 256-byte boundary - the results of any run of consecutive items are then one
-        contiguous range (``item_range``) that can be sent or copied with a single operation."""
+        contiguous range (``item_range``) that can be sent or copied with a single operation.
+        ``packed_zero_points``: asymmetric modes write their zero points as the decompressor stores them (uint8 per
+        group, or two 4-bit groups per byte) instead of int32 (``PlanItem.zero_point_packed``)."""
         self.items: list[PlanItem] = []
         self.device = torch.device(device) if device is not None else None
         self.arena = arena
@@ -147,8 +155,8 @@ class CompressionPlan:
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._fp16_scales = fp16_scales
         self._arg_arrays: dict = {}
-        self._layouts = [stored_outputs(it.name, it.weight.shape, it.reduction_axis, it.config, fp16_scales)
-                         for it in self.items]
+        self._layouts = [stored_outputs(it.name, it.weight.shape, it.reduction_axis, it.config, fp16_scales,
+                                        packed_zero_points) for it in self.items]
         if self._use_arena:
             off = 0
             for lay in self._layouts:
@@ -190,6 +198,8 @@ class CompressionPlan:
             a.scale_f16_out = item.scale_f16.data_ptr()
         if item.zero_point is not None:
             a.zp_out = item.zero_point.data_ptr()
+        if item.zero_point_packed is not None:
+            a.zp_packed_out = item.zero_point_packed.data_ptr()
         if item.scale_e8m0 is not None:
             a.scale_e8m0_out = item.scale_e8m0.data_ptr()
         item.args = a

@@ -114,6 +114,7 @@ def quantize_launch(
     want_sqerr: bool = False,
     want_scale_f16: bool = False,
     want_params: bool = True,
+    want_zp_packed: bool = False,
 ) -> dict:
     """One ``nncfb_quantize`` launch on ``weight`` viewed as [outer, reduce, inner] around
     ``reduction_axis`` with groups of ``group_size`` (must divide the axis).
@@ -189,6 +190,11 @@ def quantize_launch(
     if want_scale_f16:
         out["scale_f16"] = torch.empty(n_groups, dtype=torch.float16, device=dev)
         args.scale_f16_out = _lib.ptr(out["scale_f16"])
+    if want_zp_packed and config.is_integer and config.is_asym_mode:
+        # the decompressor's `_zero_point` buffer: uint8 per group, or two 4-bit groups per byte
+        nbytes = (n_groups + 7) // 8 * 4 if four_bit else n_groups
+        out["zp_packed"] = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        args.zp_packed_out = _lib.ptr(out["zp_packed"])
     if want_values:
         out["values"] = torch.empty(n, dtype=torch.float32, device=dev)
         args.values_out = _lib.ptr(out["values"])
@@ -508,7 +514,7 @@ def compress_weight(weight: torch.Tensor, reduction_axes: ReductionAxes, config:
     w, axis, gs = _grouped(weight, config, reduction_axes, ps)
     four_bit = config.num_bits == 4
     o = quantize_launch(w, config, axis, gs, ps, pz, want_codes="nibble" if four_bit else "byte",
-                        want_scale_f16=True)
+                        want_scale_f16=True, want_zp_packed=True)
     pshape = _keepdims_shape(w.shape, axis)
     scale = ps if ps is not None else o["scale"].reshape(pshape)
     zp = None
@@ -517,6 +523,10 @@ def compress_weight(weight: torch.Tensor, reduction_axes: ReductionAxes, config:
     cw = CompressedWeight(None, scale, zp)
     cw.packed = o["packed"].reshape(-1, 1) if four_bit else o["codes"].reshape(w.shape)
     cw.scale_f16 = o["scale_f16"].reshape(pshape)
+    if "zp_packed" in o:
+        n_groups = o["scale_f16"].numel()
+        cw.zero_point_packed = (o["zp_packed"][: (n_groups + 1) // 2].reshape(-1, 1) if four_bit
+                                else o["zp_packed"].reshape(pshape))
     cw.grouped_shape = tuple(w.shape)
     if "scale_e8m0" in o:
         cw.scale_e8m0 = o["scale_e8m0"].reshape(pshape)

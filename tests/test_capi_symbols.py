@@ -37,7 +37,7 @@ def test_binding_covers_every_declared_symbol():
 def test_abi_version_and_host_side_validation():
     from nncf_b200 import _lib
 
-    assert _lib.lib.nncfb_abi_version() == 1
+    assert _lib.lib.nncfb_abi_version() == 2
     args = _lib.QuantizeArgs()
     assert _lib.lib.nncfb_quantize(ctypes.byref(args), None) == _lib.E_BAD_ARG
     assert b"weight is null" in _lib.lib.nncfb_last_error()
