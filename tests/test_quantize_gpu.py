@@ -463,3 +463,60 @@ def test_convolution_weights_reduce_over_every_axis_but_the_channel(shape, axes,
             _eq(st.scale_f16, ref.scale.astype(np.float16), "fp16 scale")
     with pytest.raises(UnsupportedModelError):
         wl.compress_weight(w.cuda(), axes, _cfg(mode, 4))
+
+
+@pytest.mark.parametrize("mode", ["int4_asym", "int8_asym"])
+@pytest.mark.parametrize("shape,axis,gs", [((96, 4096), 1, 128), ((33, 1024), 1, 32), ((7, 192), 1, 64), ((5, 384), 1, 128),
+                                           ((64, 2048), 1, -1), ((9, 1000), 1, 8), ((256, 48), 0, 32), ((3, 64, 20), 1, 16)])
+def test_zero_points_leave_the_kernel_in_their_stored_form(shape, axis, gs, mode):
+    """`zp_packed_out`: the decompressor's zero-point buffer written by the compression kernel itself - uint8 per
+    group, or two 4-bit groups per byte in flat group order with the even group in the low nibble (pack_uint4 of
+    the reference's zero-point tensor, layers.py:1390) - on the batched row kernel (even and odd numbers of
+    groups, groups of 32 / 64 / 128), the per-channel kernel and the general kernels (atomic OR into zeroed words)."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import weight_lowering as wl
+
+    gen = torch.Generator().manual_seed(sum(shape) + len(mode))
+    w = (torch.randn(*shape, generator=gen) * 0.05).to(torch.bfloat16)
+    ref = O.compress_weight(w.float().numpy(), axis, mode, gs)
+    zp = ref.zero_point.reshape(-1).astype(np.uint8)
+    if mode == "int4_asym":
+        padded = np.concatenate([zp, np.zeros(len(zp) % 2, dtype=np.uint8)])
+        want = O.pack_uint4(padded).reshape(-1)
+    else:
+        want = zp
+    st = wl.compress_weight(w.cuda(), axis, _cfg(mode, gs), pack=True)
+    got = st.zero_point_packed.cpu().numpy().reshape(-1)
+    assert got.dtype == np.uint8
+    np.testing.assert_array_equal(got[: len(want)], want)
+    _eq(st.zero_point, ref.zero_point, "int32 zero point still written")
+
+
+def test_plan_with_packed_zero_points_matches_oracle_and_installs_decompressors():
+    """CompressionPlan(packed_zero_points=True) on the batched kernels (INT4_ASYM g128 incl. an odd number of
+    groups per tensor, INT8_ASYM per channel), and the model-level call, which installs the kernel-written buffers
+    without the torch-side pack: state dict equal to the reference's golden (api case int4_asym_g16_all)."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import CompressWeightsMode, WeightCompressionConfig
+    from nncf_b200.pipeline import CompressionPlan
+
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    items = []
+    for k, (shape, mode, gs) in enumerate([((512, 4096), "int4_asym", 128), ((3, 384), "int4_asym", 128),
+                                           ((1024, 1024), "int8_asym", -1), ((640, 4096), "int4_asym", 32)]):
+        w = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
+        w.normal_(0.0, 0.02, generator=gen)
+        items.append((f"t{k}", w, WeightCompressionConfig(CompressWeightsMode(mode), gs)))
+    plan = CompressionPlan(items, packed_zero_points=True)
+    plan.run(use_graph=False)
+    torch.cuda.synchronize()
+    for (name, w, cfg), it in zip(items, plan.items):
+        ref = O.stored_form(w.float().cpu().numpy(), cfg.mode.value, cfg.group_size)
+        zp = ref["zero_point"].astype(np.uint8)
+        want = O.pack_uint4(np.concatenate([zp, np.zeros(len(zp) % 2, dtype=np.uint8)])).reshape(-1) if cfg.num_bits == 4 else zp
+        got = it.zero_point_packed.cpu().numpy()
+        np.testing.assert_array_equal(got[: len(want)], want, err_msg=name)
+        np.testing.assert_array_equal(it.packed.cpu().numpy().reshape(-1).view(np.uint8), ref["packed"], err_msg=name)
+        assert it.zero_point is None
