@@ -253,19 +253,22 @@ int nncfb_channel_stats(const void* x, int32_t dtype, int64_t tokens, int64_t ch
 
 /*
  * fp32-faithful matrix product on the tcgen05 tensor cores:
- *   c[m, n] (row stride ldc) = (accumulate ? c : 0) + alpha * a[m, k] @ b[k, n]      (all fp32, row-major, device)
+ *   c[m, n] (row stride ldc) = (accumulate ? c : 0) + alpha * a[m, k] @ b      (all fp32, row-major, device)
+ * with b given as [k, n] or, with transpose_b != 0, as [n, k] (c = a b^T).
  * Both operands are split into three bf16 planes (hi + mid + lo = the fp32 value to 2^-27) and the six plane
  * products down to 2^-24 are accumulated in fp32 in tensor memory, smallest first, by the kernel that also does
  * the GPTQ trailing update; c is updated by a bulk tensor reduction (never read into the SM).  Agrees with an
  * fp32 product to about 1e-6 relative.  Needs k % 64 == 0, ldc % 4 == 0, c and workspace 16-byte aligned;
  * workspace >= nncfb_gemm_f32_workspace_bytes(m, n, k) holds the operand planes.  Returns NNCFB_E_UNSUPPORTED
  * (nothing launched) when the shape does not qualify.
- * Used for the dense products inside the inverse factor of the GPTQ Hessian, which the reference obtains from
- * fns.linalg.cholesky_inverse / cholesky (WC/gptq.py:293-295).
+ * Used for the dense products inside the inverse factor of the GPTQ Hessian (the trailing updates of a blocked
+ * Cholesky factorisation and the triangular inverse), which the reference obtains from fns.linalg.cholesky /
+ * cholesky_inverse (WC/gptq.py:293-295).
  */
 size_t nncfb_gemm_f32_workspace_bytes(int64_t m, int64_t n, int64_t k);
-int nncfb_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb, float* c, int64_t ldc, int64_t m, int64_t n,
-                   int64_t k, float alpha, int32_t accumulate, void* workspace, size_t workspace_bytes, void* stream);
+int nncfb_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb, int32_t transpose_b, float* c, int64_t ldc,
+                   int64_t m, int64_t n, int64_t k, float alpha, int32_t accumulate, void* workspace,
+                   size_t workspace_bytes, void* stream);
 
 /*
  * Decompression of stored weights in one pass: codes (nibble-packed for 4-bit modes, bytes for 8-bit) +

@@ -73,7 +73,7 @@ def _load() -> C.CDLL:
                                     C.c_size_t, vp], C.c_int),
         "nncfb_gptq_quantize_noalloc": ([vp, i64, i64, vp, i32, i64, i32, vp, vp, vp, vp], C.c_int),
         "nncfb_gemm_f32_workspace_bytes": ([i64, i64, i64], C.c_size_t),
-        "nncfb_gemm_f32": ([vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_float, i32, vp, C.c_size_t, vp], C.c_int),
+        "nncfb_gemm_f32": ([vp, i64, vp, i64, i32, vp, i64, i64, i64, i64, C.c_float, i32, vp, C.c_size_t, vp], C.c_int),
         "nncfb_decompress": ([vp, i32, i64, i64, vp, vp, vp, i32, vp], C.c_int),
         "nncfb_pack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),
         "nncfb_unpack_nibbles": ([vp, i64, i32, vp, vp], C.c_int),

@@ -733,9 +733,11 @@ size_t gemm_f32_workspace(int64_t M, int64_t N, int64_t K) {
   return planes_bytes_gemm(K, M) + planes_bytes_gemm(K, N);
 }
 
-// C[M, N] (row stride ldc) = C * (accumulate ? 1 : 0) + alpha * A[M, K] @ B[K, N]
-int gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc, int64_t M, int64_t N,
-             int64_t K, float alpha, bool accumulate, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+// C[M, N] (row stride ldc) = C * (accumulate ? 1 : 0) + alpha * A[M, K] @ B, with B given as [K, N] (row stride ldb)
+// or, with transpose_b, as [N, K] (C = A B^T)
+int gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, bool transpose_b, float* C, int64_t ldc, int64_t M,
+             int64_t N, int64_t K, float alpha, bool accumulate, void* workspace, size_t workspace_bytes,
+             cudaStream_t st) {
   if (K % kBlockK != 0 || ldc % 4 != 0 || !aligned16(C) || !aligned16(workspace) || M > 0x7fffffff || N > 0x7fffffff ||
       K > 0x7fffffff / 3 || encode_tiled_fn() == nullptr)
     return NNCFB_E_UNSUPPORTED;
@@ -749,8 +751,13 @@ int gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, float* C,
   const int64_t a_ld = round8_i64(M), b_ld = round8_i64(N);
   const dim3 ga(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((M + 31) / 32));
   split_transposed_kernel<<<ga, 256, 0, st>>>(A, lda, K, M, a_ld, a_planes);
-  const dim3 gb(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(K));
-  split_rows_kernel<<<gb, 256, 0, st>>>(B, ldb, K, N, b_ld, b_planes);
+  if (transpose_b) {
+    const dim3 gb(static_cast<unsigned>((K + 31) / 32), static_cast<unsigned>((N + 31) / 32));
+    split_transposed_kernel<<<gb, 256, 0, st>>>(B, ldb, K, N, b_ld, b_planes);
+  } else {
+    const dim3 gb(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(K));
+    split_rows_kernel<<<gb, 256, 0, st>>>(B, ldb, K, N, b_ld, b_planes);
+  }
   NNCFB_CUDA(cudaGetLastError());
   if (!accumulate) NNCFB_CUDA(cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, st));
   CUtensorMap amap, bmap, dmap;
@@ -805,13 +812,14 @@ extern "C" int nncfb_hessian_status(void* stream) {
 
 extern "C" size_t nncfb_gemm_f32_workspace_bytes(int64_t m, int64_t n, int64_t k) { return nncfb::gemm_f32_workspace(m, n, k); }
 
-extern "C" int nncfb_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb, float* c, int64_t ldc, int64_t m,
-                              int64_t n, int64_t k, float alpha, int32_t accumulate, void* workspace,
-                              size_t workspace_bytes, void* stream) {
+extern "C" int nncfb_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb, int32_t transpose_b, float* c,
+                              int64_t ldc, int64_t m, int64_t n, int64_t k, float alpha, int32_t accumulate,
+                              void* workspace, size_t workspace_bytes, void* stream) {
   NNCFB_CHECK_ARG(a && b && c && workspace, NNCFB_E_BAD_ARG, "nncfb_gemm_f32: null pointer");
-  NNCFB_CHECK_ARG(m > 0 && n > 0 && k > 0 && lda >= k && ldb >= n && ldc >= n, NNCFB_E_BAD_ARG, "nncfb_gemm_f32: bad shape");
-  const int rc = nncfb::gemm_f32(a, lda, b, ldb, c, ldc, m, n, k, alpha, accumulate != 0, workspace, workspace_bytes,
-                                 static_cast<cudaStream_t>(stream));
+  NNCFB_CHECK_ARG(m > 0 && n > 0 && k > 0 && lda >= k && ldb >= (transpose_b ? k : n) && ldc >= n, NNCFB_E_BAD_ARG,
+                  "nncfb_gemm_f32: bad shape");
+  const int rc = nncfb::gemm_f32(a, lda, b, ldb, transpose_b != 0, c, ldc, m, n, k, alpha, accumulate != 0, workspace,
+                                 workspace_bytes, static_cast<cudaStream_t>(stream));
   if (rc == NNCFB_E_UNSUPPORTED)
     nncfb::set_error("nncfb_gemm_f32: needs k %% 64 == 0, ldc %% 4 == 0, 16-byte aligned c and workspace, and a driver "
                      "with tensor-map support");

@@ -490,3 +490,24 @@ def test_triangular_inverse_with_tensor_core_products_matches_fp64(monkeypatch):
     assert err[True] < 1.5e-6 and err[False] < 1.5e-6
     assert torch.equal(out[True], torch.tril(out[True]))
     assert not torch.equal(out[True], out[False])   # the tensor-core products were really used
+
+
+def test_fp32_faithful_gemm_with_transposed_and_column_major_operands():
+    """C = A B^T with B given as [n, k] (a column-major [k, n] view), accumulate with alpha = -1 (the form of a
+    symmetric rank-k update), and the all-column-major case (operands as torch.linalg.cholesky returns them)."""
+    from nncf_b200 import gptq as G
+
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    a = torch.randn(768, 512, device="cuda", generator=gen)
+    bt = torch.randn(640, 512, device="cuda", generator=gen)          # B^T, row-major
+    c0 = torch.randn(768, 640, device="cuda", generator=gen)
+    c = c0.clone()
+    G._gemm(a, bt.T, c, accumulate=True, alpha=-1.0)
+    want = c0.double() - a.double() @ bt.double().T
+    assert ((c.double() - want).abs().max() / want.abs().max()).item() < 2e-6
+    # column-major everything: views of transposed row-major storage
+    a_cm, b_cm = torch.randn(512, 768, device="cuda", generator=gen).T, torch.randn(640, 512, device="cuda", generator=gen).T
+    out_cm = torch.empty(640, 768, device="cuda").T
+    G._gemm(a_cm, b_cm, out_cm)
+    want = a_cm.double() @ b_cm.double()
+    assert ((out_cm.double() - want).abs().max() / want.abs().max()).item() < 2e-6
