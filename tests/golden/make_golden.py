@@ -448,6 +448,81 @@ def gen_gptq_large(out: dict):
     out["gptq_large/damp"] = np.float64(c["damp"])
 
 
+def gen_layerwise(out: dict):
+    """Model-level GPTQ on a toy decoder, layer by layer: the reference's own schedule
+    (quantization/algorithms/layerwise/scheduler.py:92, on the graph the reference traces from the torch model)
+    decides which target layers share a step; every step's inputs are collected from the model as it stands at
+    that point (earlier steps' weights already replaced by their quantised values, the contract of
+    layerwise/openvino_iterator.py and WC/gptq.py:157), and the reference's GPTQ computes the Hessian and the
+    quantised weight of each layer (WC/gptq.py:201, :230).  Only the collection of a step's inputs is done here,
+    with forward hooks on the torch model, because the reference ships that piece for OpenVINO models only."""
+    import torch
+
+    import nncf
+    from models import LAYERWISE, TinyGatedLM, layerwise_ids
+    from nncf.parameters import CompressWeightsMode
+    from nncf.quantization.algorithms.layerwise.scheduler import LayerwiseScheduler
+    from nncf.quantization.algorithms.weight_compression.config import WeightCompressionConfig
+    from nncf.quantization.algorithms.weight_compression.gptq import GPTQ
+    from nncf.tensor import Tensor
+    from nncf.torch.graph.operator_metatypes import PTLinearMetatype
+
+    c = LAYERWISE
+    ids = layerwise_ids()
+    names = []
+    for mode in c["modes"]:
+        torch.manual_seed(0)
+        model = TinyGatedLM(**c["model"]).eval()
+        wrapped = nncf.torch.wrap_model(model, example_input=ids[0], trace_parameters=True)
+        graph = wrapped.get_graph()
+        linear = [n for n in graph.get_all_nodes() if n.metatype is PTLinearMetatype]
+        weight_of = {}
+        for n in linear:
+            const = [p for p in graph.get_previous_nodes(n) if p.node_name.endswith(".weight")]
+            weight_of[n.node_name] = const[0].node_name
+        targets = [n for n in linear if weight_of[n.node_name] != "head.weight"]
+        steps = LayerwiseScheduler().schedule(graph, targets, True)
+        modules = dict(model.named_modules())
+        be = SimpleNamespace(matmul_metatypes=[PTLinearMetatype], convolution_metatypes=[])
+        g = GPTQ(damp_percent=c["damp"], block_size=c["block"], subset_size=len(ids))
+        g._backend_entity = be
+        cfg = WeightCompressionConfig(CompressWeightsMode(mode), c["group_size"])
+        key = f"layerwise/{mode}"
+        names.append(key)
+        step_names = []
+        for step in steps:
+            mods = [weight_of[n.node_name][: -len(".weight")] for n in step.target_node_map]
+            step_names.append(",".join(mods))
+            seen = {m: [] for m in mods}
+            handles = [modules[m].register_forward_pre_hook(lambda mod, args, m=m: seen[m].append(args[0].detach().clone()))
+                       for m in mods]
+            with torch.no_grad():
+                for item in ids:
+                    model(item)
+            for h in handles:
+                h.remove()
+            for node, m in zip(step.target_node_map, mods):
+                node_ns = SimpleNamespace(metatype=PTLinearMetatype, node_name=node.node_name,
+                                          layer_attributes=SimpleNamespace(input_attributes={"transpose": False},
+                                                                           constant_attributes={1: {"transpose": True}}))
+                inputs = [Tensor(x) for x in seen[m]]
+                H = g._calculate_hessian(node_ns, inputs)
+                wp = SimpleNamespace(node_with_weight=node_ns, weight_port_id=1, compression_config=cfg,
+                                     reduction_axes=(1,))
+                w = modules[m].weight.detach().clone()
+                q, s, z = g._quantize_weights(wp, Tensor(H.data[0].clone()), Tensor(w), inputs)
+                with torch.no_grad():
+                    modules[m].weight.copy_(q.data)
+                out[f"{key}/{m}/weight"] = _np(q)
+                out[f"{key}/{m}/scale"] = _np(s)
+                if z is not None:
+                    out[f"{key}/{m}/zp"] = _np(z)
+        out[key + "/steps"] = np.array(step_names)
+        with torch.no_grad():
+            out[key + "/logits"] = _np(model(ids[0]))
+    out["layerwise/index"] = np.array(names)
+
+
 def gen_config1(out: dict):
     """SHA-256 digests of every tensor of the state dict the reference's ``nncf.compress_weights`` produces for
     8 stacked Linear(4096 -> 4096) fp32 layers (INT4_SYM, group 128, ratio 1.0, CPU): a few hundred bytes that
@@ -488,6 +563,7 @@ def main():
         "gptq_se": gen_gptq_se,
         "gptq_large": gen_gptq_large,
         "config1": gen_config1,
+        "layerwise": gen_layerwise,
         "api": gen_api,
     }
     only = [a for a in sys.argv[1:] if a in groups]

@@ -72,3 +72,12 @@ API_CASES = [
     ("int4_sym_g16_awq", dict(mode="int4_sym", group_size=16, awq=True), True),
     ("int4_asym_g16_awq_se", dict(mode="int4_asym", group_size=16, awq=True, scale_estimation=True), True),
 ]
+
+
+# model-level GPTQ fixture: a toy decoder wide enough that every Hessian has more tokens than channels
+LAYERWISE = dict(model=dict(vocab=64, hidden=128, inter=256, layers=2, seed=3), group_size=32, block=128, damp=0.1,
+                 modes=("int4_sym", "int4_asym"), n=8, seq=64)
+
+
+def layerwise_ids():
+    return calibration_ids(n=LAYERWISE["n"], seq=LAYERWISE["seq"], vocab=LAYERWISE["model"]["vocab"], seed=7)

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 from conftest import golden
-from models import API_CASES, TinyGatedLM, calibration_ids
+from models import API_CASES, LAYERWISE, TinyGatedLM, calibration_ids, layerwise_ids
 
 pytestmark = pytest.mark.gpu
 
@@ -485,3 +485,47 @@ def test_gptq_style_layout_decodes_to_the_decompressed_weight(mode, gs):
     gi = lay["g_idx"].long()
     w = lay["scales"].float()[gi] * (codes - zeros[gi]).float()                                 # [in, out]
     torch.testing.assert_close(w.t(), holder[0].weight.float(), rtol=2 ** -10, atol=1e-7)
+
+
+@pytest.mark.parametrize("mode", LAYERWISE["modes"])
+def test_model_level_gptq_follows_the_reference_schedule_and_reference_gptq(mode):
+    """Model-level GPTQ against tests/golden/layerwise.npz: the reference's own schedule on the graph it traced
+    from this model, its Hessian and its quantiser per layer, every step fed by the model with the earlier
+    steps' weights already quantised (embedding and head left in floating point on both sides).  Later layers see
+    inputs that passed through earlier quantised layers, so a rounding flip early on would perturb everything
+    after it: the integer codes of all eight layers must still agree with the reference's except for a handful,
+    and the stored fp16 scale is the reference's fp32 scale rounded once."""
+    import nncf_b200 as nb
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    c = LAYERWISE
+    gs = c["group_size"]
+    g = golden("layerwise")
+    key = f"layerwise/{mode}"
+    ids = [i.cuda() for i in layerwise_ids()]
+    model = TinyGatedLM(**c["model"]).eval().cuda()
+    cm = nb.compress_weights(model, mode=nb.CompressWeightsMode(mode), group_size=gs, dataset=nb.Dataset(ids),
+                             gptq=True, subset_size=len(ids), all_layers=True, ignored_scope=["embed", "head"],
+                             advanced_parameters=nb.AdvancedCompressionParameters(
+                                 gptq_params=nb.AdvancedGPTQParameters(damp_percent=c["damp"], subset_size=len(ids))))
+    mods = dict(cm.named_modules())
+    flips = total = 0
+    for step in g[key + "/steps"]:
+        for m in str(step).split(","):
+            want = torch.from_numpy(g[f"{key}/{m}/weight"]).cuda()
+            s_want = torch.from_numpy(g[f"{key}/{m}/scale"]).cuda().reshape(want.shape[0], -1)
+            have = mods[m].weight.detach().float()
+            buffers = mods[m].parametrizations.weight[0].state_dict()
+            s_have = [v for k, v in buffers.items() if k.endswith("scale")][0].float().reshape(want.shape[0], -1)
+            assert torch.equal(s_have, s_want.half().float()), m     # same fp32 scale, stored in half precision
+            # signed distance from the zero point in quantisation steps: identical integers when no code flipped
+            k_want = torch.round(want.reshape(want.shape[0], -1, gs) / s_want[..., None])
+            k_have = torch.round(have.reshape(want.shape[0], -1, gs) / s_have[..., None])
+            flips += int((k_want != k_have).sum())
+            total += want.numel()
+            assert float((have - want).norm() / want.norm()) < 1e-3, m
+    assert flips <= total * 1e-3, (flips, total)
+    with torch.no_grad():
+        logits = cm(ids[0]).float().cpu()
+    want = torch.from_numpy(g[key + "/logits"])
+    assert float((logits - want).norm() / want.norm()) < 2e-3

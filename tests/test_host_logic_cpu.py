@@ -292,3 +292,22 @@ def test_resumable_block_pauses_at_every_target_and_continues_through_new_weight
     finally:
         workers.close()
     assert not any(t.is_alive() for t in workers.threads)
+
+
+def test_same_input_groups_equal_the_reference_schedule():
+    """The steps the reference's layer-wise scheduler produced for the toy decoder (stored with the model-level
+    GPTQ fixture) are the groups of target layers that receive the identical input tensor."""
+    from types import SimpleNamespace
+
+    from conftest import golden
+    from models import LAYERWISE, TinyGatedLM, layerwise_ids
+
+    from nncf_b200.compress_api import _same_input_groups
+
+    model = TinyGatedLM(**LAYERWISE["model"]).eval()
+    names = [n for n, m in model.named_modules() if isinstance(m, torch.nn.Linear) and n != "head"]
+    mods = dict(model.named_modules())
+    targets = [SimpleNamespace(weight_name=n, module=mods[n], weight_shape=tuple(mods[n].weight.shape)) for n in names]
+    groups = _same_input_groups(model, layerwise_ids()[0], targets)
+    got = [",".join(p.weight_name for p in grp) for grp in groups]
+    assert got == [str(s) for s in golden("layerwise")["layerwise/int4_sym/steps"]]
