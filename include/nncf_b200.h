@@ -182,8 +182,10 @@ int nncfb_hessian_accumulate(float* hessian, int64_t channels, const void* x, in
 int nncfb_hessian_status(void* stream);
 
 /*
- * GPTQ blocked column sweep.  weight [rows, cols] fp32 is the tensor-level weight: it is UPDATED IN PLACE by
- * the trailing updates, as in the reference (pass a clone).  hinv [cols, cols] fp32 is the upper Cholesky
+ * GPTQ blocked column sweep.  weight [rows, cols] fp32 is the tensor-level weight: it is the call's WORKING COPY,
+ * updated in place by the trailing updates (pass a clone; its contents after the call are unspecified: on the
+ * tensor-core path a block's update of the next block's columns is applied inside that block's sweep and never
+ * written back).  hinv [cols, cols] fp32 is the upper Cholesky
  * factor of the inverse damped Hessian.  For every block of `block_size` (<= 128) columns: group parameters
  * at each group start from the tensor-level weight, quantise-dequantise column by column with error feedback
  * inside the block, then weight[:, i2:] -= Err @ hinv[i1:i2, i2:].  Outputs: q_out [rows, cols] fp32
@@ -194,7 +196,7 @@ int nncfb_hessian_status(void* stream);
  * operands are split into three bf16 planes and six plane products are accumulated in fp32 in tensor memory
  * (agrees with the fp32 contraction to ~1e-7 relative).  That kernel bounds every wait like the Hessian kernel;
  * nncfb_hessian_status() reports a wait that gave up.  On this path the part of a block's update that the next
- * block does not need yet runs on a stream of the library's own (one non-blocking stream and two events per
+ * block does not need yet runs on a stream of the library's own (one non-blocking stream and three events per
  * device and caller stream, created on first use and kept; no device memory), ordered against `stream` by events
  * in both directions: all work is complete, in stream order, when `stream` reaches the end of the call, and the
  * sequence may be captured into a CUDA graph like any fork / join.  Calls on different streams of one device run

@@ -31,6 +31,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <memory>
 
 #include "nncfb_common.cuh"
 
@@ -251,7 +252,10 @@ __global__ void __launch_bounds__(192, TRAILING ? 2 : 1)
 tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
              const __grid_constant__ CUtensorMap dmap, float* __restrict__ H,
              int64_t ld, int64_t m_bound, int64_t n_bound, int64_t tokens, float alpha, float beta, uint32_t idesc,
-             int n_tiles_n, int n_tiles, int* __restrict__ status, uint64_t wait_ns, int producer_short) {
+             int n_tiles_n, int n_tiles, int* __restrict__ status, uint64_t wait_ns, int producer_short,
+             int b_col0, int d_col0) {
+  // b_col0 / d_col0: column of `bmap` / `dmap` at which this launch's column 0 lies (maps that cover a whole buffer
+  // are encoded once and reused by launches on different column ranges); both multiples of 8
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte aligned operand ring (swizzle-128B atoms must start on 1 KiB), control block behind it
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -330,7 +334,7 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
             tma_load_2d(stage + b * kBoxBytes, &amap, m0 + b * kBoxC, ka, &ctl->full[s]);
 #pragma unroll
           for (int b = 0; b < kTileN / kBoxC; ++b)
-            tma_load_2d(stage + (kTileM / kBoxC + b) * kBoxBytes, &bmap, n0 + b * kBoxC, kb, &ctl->full[s]);
+            tma_load_2d(stage + (kTileM / kBoxC + b) * kBoxBytes, &bmap, b_col0 + n0 + b * kBoxC, kb, &ctl->full[s]);
         }
       }
       // do not leave while a copy into this CTA's shared memory may still be in flight: wait (bounded)
@@ -439,7 +443,7 @@ tc_tn_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ C
           fence_generic_to_async_smem();
           __syncwarp();
           if (lane == 0 && n0 + c < n_bound && m0 + q * 32 < m_bound) {
-            tma_reduce_add_2d(&dmap, n0 + c, m0 + q * 32, buf);
+            tma_reduce_add_2d(&dmap, d_col0 + n0 + c, m0 + q * 32, buf);
             bulk_commit();
           }
         }
@@ -535,12 +539,14 @@ __device__ int g_launch_status[kStatusSlots];
 
 namespace {
 
-int next_launch_status(int** status, cudaStream_t st) {
+// The slot of a launch: a word that is zero unless a role of some launch that used it gave up.  Slots start as
+// zeros and are only ever set by give_up(); the host clears the whole ring when it reads a raised status
+// (hessian_tc_status), so no launch has to be preceded by a memset.
+int next_launch_status(int** status, cudaStream_t /*st*/) {
   static std::atomic<unsigned> counter{0};
   int* base = nullptr;
   NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_launch_status));
   *status = base + (counter.fetch_add(1) % kStatusSlots);
-  NNCFB_CUDA(cudaMemsetAsync(*status, 0, sizeof(int), st));
   return NNCFB_OK;
 }
 
@@ -613,7 +619,7 @@ static int hessian_tc_launch(float* H, int64_t C, const void* x, int dtype, int6
   if (const int sr = next_launch_status(&status, st); sr != NNCFB_OK) return sr;
   kernel<<<std::min(n_tiles, sm_count()), 192, smem, st>>>(map, map, map, H, C, C, C, tokens, alpha, beta,
                                                             instr_desc(dtype == NNCFB_BF16), tiles_n, n_tiles, status,
-                                                            wait_ns, producer_short);
+                                                            wait_ns, producer_short, 0, 0);
   NNCFB_CUDA(cudaGetLastError());
   const dim3 mgrid(static_cast<unsigned>((C + 31) / 32), static_cast<unsigned>((C + 31) / 32));
   mirror_upper_tc_kernel<<<mgrid, 256, 0, st>>>(H, C);
@@ -677,7 +683,60 @@ int gptq_trailing_tc(float* w_c, int64_t ld, int64_t rows, int64_t n, const __nv
   // memory of the SMs they sit on), so a fixed set of persistent CTAs would leave tiles waiting behind it;
   // with a CTA per tile the hardware hands tiles to whichever SMs are free.
   kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, dmap, w_c, ld, rows, n, 128, 1.0f, -1.0f, instr_desc(true), tiles_n,
-                                               tiles_m * tiles_n, status, kWaitLimitNs, 0);
+                                               tiles_m * tiles_n, status, kWaitLimitNs, 0, 0, 0);
+  NNCFB_CUDA(cudaGetLastError());
+  return NNCFB_OK;
+}
+
+// The rest updates of one GPTQ call: every block launches the same product on a column range that shrinks by 128,
+// so the tensor maps are encoded once for the whole buffers (error planes and slab planes alternate between two
+// buffers each) and a launch only passes its column offsets.  The range of a launch must end at the last column
+// of W: a tile that reaches beyond the range is clipped by the map of W, not by the launch.
+struct GptqTrailingPlan {
+  CUtensorMap amap[2], bmap[2], dmap;
+  float* w;
+  int64_t ld, rows, cols;
+  int* status_base;
+};
+
+int gptq_trailing_plan_create(GptqTrailingPlan** out, float* w, int64_t ld, int64_t rows, int64_t cols,
+                              const __nv_bfloat16* const err_planes[2], int64_t err_ld,
+                              const __nv_bfloat16* const slab_planes[2], int64_t slab_ld) {
+  std::unique_ptr<GptqTrailingPlan> p(new GptqTrailingPlan());
+  for (int i = 0; i < 2; ++i) {
+    int rc = encode_map(&p->amap[i], err_planes[i], true, rows, 3 * 128, err_ld);
+    if (rc != NNCFB_OK) return rc;
+    rc = encode_map(&p->bmap[i], slab_planes[i], true, cols, 3 * 128, slab_ld);
+    if (rc != NNCFB_OK) return rc;
+  }
+  const int rc = encode_map_f32(&p->dmap, w, cols, rows, ld);
+  if (rc != NNCFB_OK) return rc;
+  p->w = w;
+  p->ld = ld;
+  p->rows = rows;
+  p->cols = cols;
+  NNCFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p->status_base), g_launch_status));
+  auto kernel = tc_tn_kernel<kStagesTrailing, true>;
+  NNCFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(tc_smem_bytes<kStagesTrailing>())));
+  *out = p.release();
+  return NNCFB_OK;
+}
+
+void gptq_trailing_plan_destroy(GptqTrailingPlan* p) { delete p; }
+
+// W[:, c : cols] -= Err @ Hinv[i1 : i1 + 128, c : cols] with the operands of parity `which`; the slab planes hold
+// column c at their column `slab_col`.
+int gptq_trailing_plan_run(const GptqTrailingPlan* p, int which, int64_t c, int64_t slab_col, cudaStream_t st) {
+  const int64_t n = p->cols - c;
+  const int tiles_m = static_cast<int>((p->rows + kTileM - 1) / kTileM);
+  const int tiles_n = static_cast<int>((n + kTileN - 1) / kTileN);
+  static std::atomic<unsigned> counter{0};
+  int* status = p->status_base + (counter.fetch_add(1) % kStatusSlots);
+  auto kernel = tc_tn_kernel<kStagesTrailing, true>;
+  kernel<<<tiles_m * tiles_n, 192, tc_smem_bytes<kStagesTrailing>(), st>>>(
+      p->amap[which], p->bmap[which], p->dmap, p->w + c, p->ld, p->rows, n, 128, 1.0f, -1.0f, instr_desc(true), tiles_n,
+      tiles_m * tiles_n, status, kWaitLimitNs, 0, static_cast<int>(slab_col), static_cast<int>(c));
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
 }
@@ -775,7 +834,7 @@ int gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, bool tran
   int* status = nullptr;
   if (const int sr = next_launch_status(&status, st); sr != NNCFB_OK) return sr;
   kernel<<<tiles_m * tiles_n, 192, smem, st>>>(amap, bmap, dmap, C, ldc, M, N, K, 1.0f, alpha, instr_desc(true), tiles_n,
-                                               tiles_m * tiles_n, status, kWaitLimitNs, 0);
+                                               tiles_m * tiles_n, status, kWaitLimitNs, 0, 0, 0);
   NNCFB_CUDA(cudaGetLastError());
   return NNCFB_OK;
 }
@@ -788,7 +847,10 @@ int hessian_tc_status(cudaStream_t st) {
   if (cudaMemcpyAsync(&h, status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
   if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
   if (h != 0) {
+    int* ring = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ring), g_launch_status) != cudaSuccess) return -1;
     if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return -1;
+    if (cudaMemsetAsync(ring, 0, sizeof(int) * kStatusSlots, st) != cudaSuccess) return -1;  // the launches' own words
     if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
   }
   return h;

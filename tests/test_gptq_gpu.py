@@ -248,23 +248,27 @@ def test_gptq_512x1024_against_reference_torch_golden(mode):
 
 
 def test_trailing_update_on_tensor_cores_agrees_with_fp32_kernel():
-    """The bf16x3 tensor-core trailing update against the fp32 CUDA-core one on the same problem: the tensor-level
-    weight after the FIRST block (one trailing update, no error feedback through it yet) agrees to fp32
-    rounding, and the complete sweep differs only by the flips GPTQ makes out of last-bit differences."""
+    """The tensor-core schedule against the fp32 CUDA-core one on the same problem.  The update of the NEXT block's
+    columns is done by that block's sweep in fp32 with the arithmetic of the CUDA-core kernel, so two blocks give
+    identical results on both routes; the columns after that receive the bf16x3 tensor-core update, which agrees
+    with the fp32 kernel to fp32 rounding (checked on the first block's update, before any error feedback went
+    through it); the complete sweep differs only by the flips GPTQ makes out of last-bit differences."""
     from nncf_b200 import _lib
     from nncf_b200.gptq import GPTQ
 
     gen = torch.Generator().manual_seed(5)
-    rows, C = 520, 1024      # rows % 128 != 0: partial M tile; four N tiles with a ragged last one after block 0
+    rows, C = 520, 1024      # rows % 128 != 0: partial M tile; ragged N tiles after block 0
     w = (torch.randn(rows, C, generator=gen) * 0.02).cuda()
     x = torch.randn(4096, C, generator=gen)
     x[:, :16] *= 8.0
     H = ((2.0 / 8) * (x.double().T @ x.double()).float()).cuda()
     hinv = GPTQ(0.01).prepare_hessian_inverse(H.clone(), w.clone())
 
-    def run(ws_bytes, cols):
-        wt = w.clone()[:, :cols].contiguous()
-        hv = hinv[:cols, :cols].contiguous()
+    def run(ws_bytes, columns):
+        idx = torch.as_tensor(columns, device="cuda")
+        cols = len(columns)
+        wt = w[:, idx].contiguous()
+        hv = hinv[idx][:, idx].contiguous()
         q = torch.empty_like(wt)
         sc = torch.empty(rows, cols // 128, device="cuda")
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
@@ -276,17 +280,24 @@ def test_trailing_update_on_tensor_cores_agrees_with_fp32_kernel():
     small = int(_lib.lib.nncfb_gptq_workspace_bytes(rows))
     big = int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, C))
     assert big > small
-    # two blocks only: the second block's input is the first block's trailing update, its output is not fed back
-    w_simt, q_simt, _ = run(small, 256)
-    w_tc, q_tc, _ = run(int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, 256)), 256)
-    assert torch.equal(q_simt[:, :128], q_tc[:, :128])
-    upd = (w[:, 128:256] - w_simt[:, 128:256]).abs().max().item()
-    diff = (w_simt[:, 128:256] - w_tc[:, 128:256]).abs().max().item()
+    # two blocks: the second block's input is the first block's update, applied in fp32 on both routes
+    _, q_simt, _ = run(small, range(256))
+    _, q_tc, _ = run(int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, 256)), range(256))
+    assert torch.equal(q_simt, q_tc)
+    # block 0's update of columns 256.. on the tensor cores (the tensor-level weight of a complete run keeps it
+    # for the LAST block's columns only as long as no later block touched them: take three blocks and look at
+    # the third, which received block 0's update through the tensor cores and block 1's inside its own sweep)
+    # against the fp32 kernel run on blocks 0 and 2 alone, where the same update is the only one
+    far = list(range(128)) + list(range(256, 384))
+    w_simt, _, _ = run(small, far)
+    w_tc, _, _ = run(int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, 384)), range(384))
+    upd = (w[:, 256:384] - w_simt[:, 128:256]).abs().max().item()
+    diff = (w_simt[:, 128:256] - w_tc[:, 256:384]).abs().max().item()
     print(f"trailing update: max |update| {upd:.3e}, tensor cores vs fp32 kernel max diff {diff:.3e}")
     assert upd > 0 and diff <= 2e-6 * max(upd, 1e-3)
     # whole sweep
-    _, q1, s1 = run(small, C)
-    _, q2, s2 = run(big, C)
+    _, q1, s1 = run(small, range(C))
+    _, q2, s2 = run(big, range(C))
     flipped = ((q1 - q2).abs() > 1e-6).float().mean().item()   # a last-bit change of a scale is not a flip
     rel = ((q1 - q2).norm() / q1.norm()).item()
     print(f"whole sweep: tensor cores vs fp32 kernel differing elements {flipped:.5f}, relative Frobenius {rel:.2e}")
@@ -398,6 +409,67 @@ def test_gptq_odd_shapes_match_oracle(rows, cols, gs, block, mode):
         assert np.mean(z.cpu().numpy() != Z) < 0.05
     else:
         assert z is None
+
+
+def _special_rows(w):
+    """Rows that leave the exponent range in which the sweep may divide by multiplying with a reciprocal."""
+    w[0] = 0.0                                   # all zeros: scale = eps, every numerator +0
+    w[1] *= 1e-28                                # scale = eps, numerators far below 2^-60
+    w[2] *= 1e24                                 # scale above 2^40
+    w[3, ::3] = -0.0                             # negative zeros among ordinary weights
+    w[4, 1::2] *= 1e-26                          # tiny weights inside ordinary groups
+    w[5, :] = w[5, :].abs().max()                # constant row: every element is the group's extreme
+    return w
+
+
+@pytest.mark.parametrize("rows,cols,gs,mode,special", [
+    (13, 256, 128, "int4_sym", False),       # rows % 4 != 0: lanes without a row
+    (64, 384, 8, "int4_asym", False),        # sixteen groups start inside every block
+    (32, 640, 10, "int4_sym", False),        # groups that start off the quads of columns and straddle blocks
+    (40, 256, 128, "int4_sym", True),        # rows that must take the IEEE-division pass
+    (40, 256, 64, "int4_asym", True),
+    (15000, 256, 128, "int4_sym", False),    # more groups of rows than one round of warps covers
+])
+def test_lane_split_sweep_is_bit_exact_against_oracle(rows, cols, gs, mode, special):
+    """The sweep kernel that spreads a row over eight lanes, run with the fp32 trailing update, against the CPU
+    oracle from the same inverse factor: every dequantised weight, scale and zero point equal.  With the
+    tensor-core workspace and two blocks (the second block's input is then computed inside its own sweep) the
+    result is the same again."""
+    from oracle import wc_oracle as O
+
+    from nncf_b200 import _lib
+    from nncf_b200.gptq import GPTQ
+
+    gen = torch.Generator().manual_seed(rows + cols + gs)
+    w = torch.randn(rows, cols, generator=gen) * 0.05
+    if special:
+        w = _special_rows(w)
+    x = torch.randn(4 * cols, cols, generator=gen)
+    H = ((2.0 / 8) * (x.double().T @ x.double()).float()).cuda()
+    hinv = GPTQ(0.05).prepare_hessian_inverse(H.clone(), torch.randn(8, cols).cuda())
+    asym = mode.endswith("asym")
+
+    def run(ws_bytes):
+        wt = w.clone().cuda()
+        q = torch.empty_like(wt)
+        sc = torch.empty(rows, cols // gs, device="cuda")
+        zp = torch.empty(rows, cols // gs, dtype=torch.int32, device="cuda") if asym else None
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        _lib.check(_lib.lib.nncfb_gptq_quantize(_lib.ptr(wt), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[mode], gs, 128,
+                                                _lib.ptr(q), _lib.ptr(sc), _lib.ptr(zp) if asym else None, _lib.ptr(ws),
+                                                ws_bytes, None))
+        _lib.check(_lib.lib.nncfb_hessian_status(None))
+        return q.cpu().numpy(), sc.cpu().numpy(), (zp.cpu().numpy() if asym else None)
+
+    q, sc, zp = run(int(_lib.lib.nncfb_gptq_workspace_bytes(rows)))
+    Q, S, Z = O.gptq_quantize(w.numpy().copy(), hinv.cpu().numpy(), mode, gs, 128)
+    assert np.array_equal(q, Q), f"{np.count_nonzero(q != Q)} of {q.size} dequantised weights differ"
+    assert np.array_equal(sc, S.reshape(sc.shape))
+    if asym:
+        assert np.array_equal(zp, Z.reshape(zp.shape).astype(np.int32))
+    if cols == 256 and rows % 8 == 0:
+        q2, sc2, zp2 = run(int(_lib.lib.nncfb_gptq_workspace_bytes_tensor_cores(rows, cols)))
+        assert np.array_equal(q2, q) and np.array_equal(sc2, sc)
 
 
 def test_gptq_sweep_with_look_ahead_replays_from_a_cuda_graph():
