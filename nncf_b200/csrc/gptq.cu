@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(kSweepWarps * kSweepRows) gptq_sweep_kernel(co
 constexpr int kFsLanes = 8;
 constexpr int kFsRows = 32 / kFsLanes;             // rows per warp
 constexpr int kFsQuads = kGptqMaxBlock / 4 / kFsLanes;  // quads per lane
-constexpr int kFsMaxWarps = 25;
+constexpr int kFsMaxWarps = 16;  // 512 threads: the compiler may use 128 registers (fewer made the update loops spill)
 
 // start of quad q of rows in the packed triangle, and the length of its rows
 __host__ __device__ constexpr int tri_base(int q) { return 512 * q - 8 * q * (q - 1); }
@@ -285,7 +285,7 @@ static_assert(tri_base(32) == 8448, "packed triangle size");
 struct FastSweepSmem {
   static constexpr size_t hs_floats = static_cast<size_t>(kGptqMaxBlock) * kGptqMaxBlock;
   static constexpr size_t diag_floats = 2 * kGptqMaxBlock;
-  static constexpr size_t per_warp_floats = 2 * kSweepMaxGroups * kFsRows;
+  static constexpr size_t per_warp_floats = 3 * kSweepMaxGroups * kFsRows;  // scale, zero point, reciprocal
   // The upper triangle only, rows padded to whole quads of columns: row i keeps columns 4 * (i / 4) .. 127.
   static constexpr size_t tri_floats = 8448;  // sum over the 32 quads of rows of 4 * (128 - 4 q)
   static constexpr size_t bytes(int warps, bool with_previous) {
@@ -310,7 +310,7 @@ __device__ __forceinline__ void store_bf16_if(__nv_bfloat16* p, __nv_bfloat16 v,
 // output.  QUAD_GROUPS: group starts fall on multiples of four columns, so they are looked for once per quad.
 template <int MODE, bool QUAD_GROUPS, bool SLOW>
 __device__ __forceinline__ bool sweep_row_group(const GptqArgs& a, const float* hs, const float* hp, const float2* diag,
-                                                float* ps, float* pz, const int64_t row, const bool valid, const int lane,
+                                                float* ps, float* pz, float* pr, const int64_t row, const bool valid, const int lane,
                                                 const int64_t first_start, const int gs_step) {
   constexpr int L = kFsLanes, M = kFsQuads, B = kGptqMaxBlock;
   const int l = lane & (L - 1), rloc = lane / L;
@@ -327,24 +327,31 @@ __device__ __forceinline__ bool sweep_row_group(const GptqArgs& a, const float* 
     // The previous block's trailing update for this block's columns, which that block's launch left out so that
     // no kernel stands between two sweeps: fp32 accumulation in ascending k, one subtraction (the arithmetic of
     // gptq_trailing_kernel).  hp is Hinv[previous block's rows, this block's columns].
-    float acc[M][4];
+    float acc[M][4], ep[M][4];
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f;
-    const float4* ep = reinterpret_cast<const float4*>(a.err_prev + (valid ? row : 0) * B);
+    for (int m = 0; m < M; ++m) {
+      acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f;
+      // this lane's share of the row's previous errors (the same quads as its weights); the others come by shuffle
+      const float4 v = *reinterpret_cast<const float4*>(a.err_prev + (valid ? row : 0) * B + 4 * (l + L * m));
+      ep[m][0] = v.x; ep[m][1] = v.y; ep[m][2] = v.z; ep[m][3] = v.w;
+    }
+    const int src0 = lane & ~(L - 1);
+#pragma unroll
+    for (int mk = 0; mk < M; ++mk) {
 #pragma unroll 2
-    for (int k0 = 0; k0 < B / 4; ++k0) {
-      const float4 ev = ep[k0];
-      const float e4[4] = {ev.x, ev.y, ev.z, ev.w};
+      for (int lk = 0; lk < L; ++lk) {
+        const float* hq = hp + 4 * (lk + L * mk) * B + 4 * l;  // rows k = 4 (lk + L mk) .. + 3, ascending over the loops
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const float* hrow = hp + (4 * k0 + kk) * B + 4 * l;
+        for (int kk = 0; kk < 4; ++kk) {
+          const float e = __shfl_sync(0xffffffffu, ep[mk][kk], src0 | lk);
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const float4 h = *reinterpret_cast<const float4*>(hrow + 4 * L * m);
-          acc[m][0] = __fmaf_rn(e4[kk], h.x, acc[m][0]);
-          acc[m][1] = __fmaf_rn(e4[kk], h.y, acc[m][1]);
-          acc[m][2] = __fmaf_rn(e4[kk], h.z, acc[m][2]);
-          acc[m][3] = __fmaf_rn(e4[kk], h.w, acc[m][3]);
+          for (int m = 0; m < M; ++m) {
+            const float4 h = *reinterpret_cast<const float4*>(hq + kk * B + 4 * L * m);
+            acc[m][0] = __fmaf_rn(e, h.x, acc[m][0]);
+            acc[m][1] = __fmaf_rn(e, h.y, acc[m][1]);
+            acc[m][2] = __fmaf_rn(e, h.z, acc[m][2]);
+            acc[m][3] = __fmaf_rn(e, h.w, acc[m][3]);
+          }
         }
       }
     }
@@ -411,6 +418,7 @@ __device__ __forceinline__ bool sweep_row_group(const GptqArgs& a, const float* 
       if (l == 0) {  // at most kSweepMaxGroups groups start inside a block (the launcher checks the group size)
         ps[gl * kFsRows + rloc] = cg.scale;
         pz[gl * kFsRows + rloc] = cg.zp;
+        pr[gl * kFsRows + rloc] = cg.div.fast ? cg.div.r : 0.0f;  // 0: this scale needs the IEEE division
       }
     }
   }
@@ -442,14 +450,17 @@ __device__ __forceinline__ bool sweep_row_group(const GptqArgs& a, const float* 
           // a group starts at this column (the same for the whole warp): its parameters replace the current ones
           const bool start = i == next_start;
           const int gi = min(gl_next, kSweepMaxGroups - 1);
-          Codec<MODE> n;
-          n.from_given(ps[gi * kFsRows + rloc], pz[gi * kFsRows + rloc]);
-          bad = bad || (start && !n.div.fast);
-          c.scale = start ? n.scale : c.scale;
-          c.zp = start ? n.zp : c.zp;
-          c.e8m0 = start ? n.e8m0 : c.e8m0;
-          c.div.s = start ? n.div.s : c.div.s;
-          c.div.r = start ? n.div.r : c.div.r;
+          const float ns = ps[gi * kFsRows + rloc], nz = pz[gi * kFsRows + rloc], nr = pr[gi * kFsRows + rloc];
+          bad = bad || (start && nr == 0.0f);
+          c.scale = start ? ns : c.scale;
+          c.zp = start ? nz : c.zp;
+          c.div.s = start ? ns : c.div.s;
+          c.div.r = start ? nr : c.div.r;
+          if constexpr (Codec<MODE>::kMx) {
+            Codec<MODE> n;
+            n.from_given(ns, nz);
+            c.e8m0 = start ? n.e8m0 : c.e8m0;
+          }
           next_start += start ? gs_step : 0;
           gl_next += start ? 1 : 0;
         }
@@ -532,6 +543,7 @@ __global__ void __launch_bounds__(kFsMaxWarps * 32) gptq_sweep_fast_kernel(const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   float* ps = reinterpret_cast<float*>(diag + B) + warp * FastSweepSmem::per_warp_floats;  // [16][rows of the warp]
   float* pz = ps + kSweepMaxGroups * kFsRows;
+  float* pr = pz + kSweepMaxGroups * kFsRows;
   float* hp = reinterpret_cast<float*>(diag + B) + nwarps * FastSweepSmem::per_warp_floats;  // [128][128], with err_prev
   const int i1 = a.i1;
 
@@ -575,10 +587,10 @@ __global__ void __launch_bounds__(kFsMaxWarps * 32) gptq_sweep_fast_kernel(const
     const bool valid = row < a.rows;
     bool redo = !all_fast;
     if (all_fast) {
-      const bool bad = sweep_row_group<MODE, QUAD_GROUPS, false>(a, hs, hp, diag, ps, pz, row, valid, lane, first_start, gs_step);
+      const bool bad = sweep_row_group<MODE, QUAD_GROUPS, false>(a, hs, hp, diag, ps, pz, pr, row, valid, lane, first_start, gs_step);
       redo = __any_sync(0xffffffffu, bad && valid);
     }
-    if (redo) sweep_row_group<MODE, QUAD_GROUPS, true>(a, hs, hp, diag, ps, pz, row, valid, lane, first_start, gs_step);
+    if (redo) sweep_row_group<MODE, QUAD_GROUPS, true>(a, hs, hp, diag, ps, pz, pr, row, valid, lane, first_start, gs_step);
   }
 }
 
