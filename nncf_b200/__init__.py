@@ -9,7 +9,7 @@ the package without the built library raises ``LibraryNotBuiltError``.
 from .errors import (InternalError, InvalidGroupSizeError, LibraryNotBuiltError, ParameterNotSupportedError,
                      UnsupportedModelError, ValidationError)
 from .parameters import (AdvancedAWQParameters, AdvancedCompressionParameters, AdvancedGPTQParameters,
-                         AdvancedScaleEstimationParameters, BackupMode, CompressionFormat, CompressWeightsMode,
+                         AdvancedLoraCorrectionParameters, AdvancedScaleEstimationParameters, BackupMode, CompressionFormat, CompressWeightsMode,
                          GroupSizeFallbackMode, SensitivityMetric)
 from .config import CompressedWeight, WCTensorStatistic, WeightCompressionConfig, WeightCompressionParameters
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is missing)

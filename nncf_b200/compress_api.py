@@ -36,6 +36,7 @@ from .parameters import (AdvancedCompressionParameters, BackupMode, CompressionF
                          GroupSizeFallbackMode, SensitivityMetric)
 from .pipeline import CompressionPlan
 from .scale_estimation import ScaleEstimation
+from .lora_correction import LoraAdapters, LoraCorrectionAlgorithm, attach_adapters
 from .weight_lowering import get_integer_quantization_error
 
 _M = CompressWeightsMode
@@ -128,8 +129,16 @@ def check_user_compression_configuration(mode, subset_size, dataset, ratio, grou
         msg = f"Torch backend does not support {mode.value} mode for weight compression."
         raise ParameterNotSupportedError(msg)
     if lora_correction:
-        msg = "Torch backend does not support the lora_correction option."
-        raise ParameterNotSupportedError(msg)
+        # the rules of the one reference backend that has the option (quantize_model.py:594-615)
+        if dataset is None:
+            msg = "Scale estimation, GPTQ or Lora Correction algorithm is defined, but dataset is None."
+            raise ParameterNotSupportedError(msg)
+        if gptq:
+            msg = "Simultaneous use of Lora correction and GPTQ algorithms is not supported. Select one of them."
+            raise ParameterNotSupportedError(msg)
+        if mode not in (_M.INT4_SYM, _M.INT4_ASYM, _M.NF4):
+            msg = f"Lora Correction algorithm is defined, but mode {mode.value} is not one of int4_sym, int4_asym, nf4."
+            raise ParameterNotSupportedError(msg)
     if compression_format != CompressionFormat.DQ:
         msg = f"{compression_format.value} compression format is not supported: only the default DQ format is."
         raise ParameterNotSupportedError(msg)
@@ -154,7 +163,11 @@ def check_user_compression_configuration(mode, subset_size, dataset, ratio, grou
     sizes = [subset_size]
     if advanced_parameters:
         sizes += [advanced_parameters.awq_params.subset_size, advanced_parameters.scale_estimation_params.subset_size,
-                  advanced_parameters.gptq_params.subset_size]
+                  advanced_parameters.gptq_params.subset_size, advanced_parameters.lora_correction_params.subset_size]
+        if advanced_parameters.lora_correction_params.adapter_rank <= 0:
+            rank = advanced_parameters.lora_correction_params.adapter_rank
+            msg = f"The lora adapter rank should be positive, but rank={rank} is given."
+            raise ValidationError(msg)
     for size in sizes:
         if size <= 0:
             msg = f"The subset_size value should be positive, but subset_size={size} is given."
@@ -575,7 +588,7 @@ def compress_weights(
         ratio_defining = [p for p in ratio_defining if p.compression_config is not None]
 
     # statistics (one calibration pass, hooks on every Linear input)
-    need_stats = bool(items) and (cfg["awq"] or cfg["scale_estimation"] or
+    need_stats = bool(items) and (cfg["awq"] or cfg["scale_estimation"] or bool(lora_correction) or
                                   (cfg["ratio"] < 1 and cfg["sensitivity_metric"] != SensitivityMetric.WEIGHT_QUANTIZATION_ERROR))
     stats: dict = {}
     act = None
@@ -762,7 +775,11 @@ def compress_weights(
         TIMERS["find_layers_and_order"] = t_before
         TIMERS["transform_model"] = time.perf_counter() - t0
         return model
-    _transform_model(active, precomputed)
+    lora = None
+    if lora_correction and not cfg["gptq"]:
+        # WC/algorithm.py:1187-1195: the statistics as they stand after AWQ
+        lora = LoraCorrectionAlgorithm(stats, adv.lora_correction_params)
+    _transform_model(active, precomputed, lora)
     return model
 
 
@@ -1213,9 +1230,10 @@ def _make_decompressor(p: WeightCompressionParameters, item) -> nn.Module:
     return FloatCodebookWeightsDecompressor(cfg.mode, scale, grouped, tuple(w.shape), w.dtype)
 
 
-def _transform_model(active: list, precomputed: dict) -> None:
+def _transform_model(active: list, precomputed: dict, lora: Optional[LoraCorrectionAlgorithm] = None) -> None:
     """torch_backend.py:424-485: compress every weight and install its decompressor.  Weights without
-    precomputed parameters go through one batched launch; the others through compress_weight."""
+    precomputed parameters go through one batched launch; the others through compress_weight.  With ``lora`` every
+    4-bit Linear with statistics also gets its pair of correcting adapters (openvino_backend.py:362-369)."""
     from .weight_lowering import compress_weight
 
     plain = [p for p in active if p.weight_name not in precomputed]
@@ -1238,9 +1256,17 @@ def _transform_model(active: list, precomputed: dict) -> None:
         packed = it.packed.reshape(-1, 1) if four else it.packed.reshape(p.weight.shape)
         mod = p.module
         dense_shape, dense_dtype = tuple(p.weight.shape), p.weight.dtype
+        original = p.weight.data
         mod.weight.requires_grad_(False)
         mod.weight.data = packed
         # tied weights: every holder of the Parameter gets the same decompressor over the one packed tensor
         for holder in [mod, *p.shared_modules]:
             parametrize.register_parametrization(holder, "weight", dec, unsafe=True)
             serialization.record(holder, p.compression_config, dense_shape, dense_dtype)
+        if lora is not None and lora.is_applicable(p) and not p.is_embedding and p.weight_name in lora._statistics:
+            with torch.no_grad():
+                fq = mod.weight.detach()           # what the layer now computes with
+                lora_a, lora_b = lora.calculate_adapters(original, fq, p)
+                adapters = LoraAdapters(lora_a, lora_b, dense_dtype, lora.use_int8_adapters)
+            attach_adapters(mod, adapters)
+            serialization.record_adapters(mod, adapters)

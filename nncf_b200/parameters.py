@@ -90,6 +90,16 @@ class AdvancedGPTQParameters:
 
 
 @dataclass
+class AdvancedLoraCorrectionParameters:
+    """src/nncf/quantization/advanced_parameters.py:360-382."""
+    adapter_rank: int = 8
+    num_iterations: int = 3
+    apply_regularization: bool = True
+    subset_size: int = 128
+    use_int8_adapters: bool = True
+
+
+@dataclass
 class AdvancedCompressionParameters:
     statistics_path: str | None = None
     group_size_fallback_mode: GroupSizeFallbackMode | None = None
@@ -98,3 +108,4 @@ class AdvancedCompressionParameters:
     scale_estimation_params: AdvancedScaleEstimationParameters = field(
         default_factory=AdvancedScaleEstimationParameters)
     gptq_params: AdvancedGPTQParameters = field(default_factory=AdvancedGPTQParameters)
+    lora_correction_params: AdvancedLoraCorrectionParameters = field(default_factory=AdvancedLoraCorrectionParameters)

@@ -35,6 +35,11 @@ def record(module: nn.Module, config: WeightCompressionConfig, weight_shape: tup
                             "weight_shape": [int(d) for d in weight_shape], "dtype": str(dtype).replace("torch.", "")})
 
 
+def record_adapters(module: nn.Module, adapters) -> None:
+    """Called when LoRA-correction adapters are attached to a compressed module."""
+    getattr(module, _ATTR)["lora_correction"] = {"rank": int(adapters.rank), "int8": bool(adapters.int8)}
+
+
 def get_config(model: nn.Module) -> dict:
     """JSON-able description of every compressed weight: module name -> mode, group size, dense shape, dtype.
     Together with ``model.state_dict()`` it restores the compressed model in another process."""
@@ -80,6 +85,13 @@ def load_from_config(model: nn.Module, config: dict, state_dict: Optional[dict] 
         mod.weight.data = packed
         parametrize.register_parametrization(mod, "weight", dec, unsafe=True)
         record(mod, cfg, shape, dtype)
+        if "lora_correction" in entry:
+            from .lora_correction import attach_adapters, empty_adapters
+
+            lc = entry["lora_correction"]
+            adapters = empty_adapters(out_ch, in_ch, int(lc["rank"]), dtype, bool(lc["int8"]), dev)
+            attach_adapters(mod, adapters)
+            record_adapters(mod, adapters)
     if state_dict is not None:
         model.load_state_dict(state_dict)
     return model
@@ -95,6 +107,14 @@ def strip(model: nn.Module) -> nn.Module:
         # torch cannot leave a float value in place of the packed uint8 original itself: drop the
         # parametrization with the original restored, then swap the parameter
         parametrize.remove_parametrizations(mod, "weight", leave_parametrized=False)
+        if hasattr(mod, "lora_correction"):
+            # y = x W^T + (x A^T) B^T = x (W + B A)^T: the adapters fold into the dense weight
+            from .lora_correction import detach_adapters
+
+            with torch.no_grad():
+                lc = mod.lora_correction
+                dense = (dense.float() + lc.b().float() @ lc.a().float()).to(dense.dtype)
+            detach_adapters(mod)
         mod.weight = nn.Parameter(dense, requires_grad=False)
         if hasattr(mod, _ATTR):
             delattr(mod, _ATTR)

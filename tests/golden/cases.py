@@ -89,3 +89,14 @@ def gptq_large_inputs():
         x = rs.randn(1, c["tokens"], c["cols"]).astype(np.float32) @ mix
         xs.append(torch.from_numpy(x).to(torch.bfloat16).float().numpy())
     return w, xs
+
+
+LORA_CASES = [
+    # name, out, in, gs, n samples, mode, rank, iterations, regularization
+    ("int4_sym_g32_r8", 96, 128, 32, 24, "int4_sym", 8, 3, True),
+    ("int4_asym_g32_r4", 64, 128, 32, 16, "int4_asym", 4, 3, True),
+    ("nf4_g64_r8", 80, 192, 64, 32, "nf4", 8, 2, True),
+    ("int4_sym_g32_noreg", 96, 128, 32, 24, "int4_sym", 8, 3, False),
+    ("int4_asym_row_r8", 48, 64, -1, 12, "int4_asym", 8, 3, True),
+    ("int4_sym_g32_many_samples", 40, 64, 32, 150, "int4_sym", 8, 2, True),   # more samples than subset_size = 128
+]

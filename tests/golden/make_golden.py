@@ -21,7 +21,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
-from cases import (AWQ_CASES, DTYPES, GPTQ_CASES, GPTQ_LARGE, GPTQ_SE_CASES, MODES, QUANT_CASES, SE_CASES,  # noqa: E402
+from cases import (AWQ_CASES, DTYPES, GPTQ_CASES, LORA_CASES, GPTQ_LARGE, GPTQ_SE_CASES, MODES, QUANT_CASES, SE_CASES,  # noqa: E402
                    gptq_large_inputs)
 
 
@@ -523,6 +523,52 @@ def gen_layerwise(out: dict):
     out["layerwise/index"] = np.array(names)
 
 
+def gen_lora(out: dict):
+    """LoRA correction (WC/lora_correction.py:139-271) on seeded weights and activation statistics: the reference's
+    compress_weight, its dequantisation and its adapters.  Stored: inputs, the dequantised weight the adapters
+    correct, both adapters, and the activation-weighted noise before and after."""
+    import torch
+
+    from nncf.parameters import CompressWeightsMode
+    from nncf.quantization.advanced_parameters import AdvancedLoraCorrectionParameters
+    from nncf.quantization.algorithms.weight_compression.activation_stats import process_stats
+    from nncf.quantization.algorithms.weight_compression.config import WeightCompressionConfig
+    from nncf.quantization.algorithms.weight_compression.lora_correction import LoraCorrectionAlgorithm
+    from nncf.quantization.algorithms.weight_compression.weight_lowering import (compress_weight,
+                                                                                   do_float_dequantization,
+                                                                                   do_integer_dequantization)
+    from nncf.tensor import Tensor
+
+    rng = np.random.default_rng(777)
+    names = []
+    for name, o, h, gs, n, mode, rank, iters, reg in LORA_CASES:
+        w = rng.normal(0, 0.05, size=(o, h)).astype(np.float32)
+        outl = rng.random(h) < 0.06
+        means = [(rng.normal(0, 1.0, size=(h,)) * (1 + 9 * outl)).astype(np.float32) for _ in range(n)]
+        shapes = [(1, int(rng.integers(4, 40)), h) for _ in range(n)]
+        cfg = WeightCompressionConfig(CompressWeightsMode(mode), gs)
+        cw = compress_weight(Tensor(torch.from_numpy(w.copy())), (1,), cfg)
+        axis = 1 if gs != -1 else -1
+        fq = do_float_dequantization(cw, axis) if mode == "nf4" else do_integer_dequantization(cw, axis)
+        params = AdvancedLoraCorrectionParameters(adapter_rank=rank, num_iterations=iters, apply_regularization=reg)
+        a, b, _ = LoraCorrectionAlgorithm.calculate_low_rank_matrices(Tensor(torch.from_numpy(w.copy())), cw, cfg, (1,),
+                                                                      params, _stats(means, shapes))
+        key = f"lora/{name}"
+        names.append(key)
+        out[key + "/w"] = w
+        out[key + "/fq"] = _np(fq).reshape(o, h)
+        out[key + "/means"] = np.stack(means)
+        out[key + "/tokens"] = np.array([s[1] for s in shapes], dtype=np.int64)
+        out[key + "/lora_A"] = _np(a)
+        out[key + "/lora_B"] = _np(b)
+        _, X = process_stats(_stats(means, shapes), params.subset_size)
+        X = _np(X).T.astype(np.float64)                       # [SS, H]
+        res = (w - out[key + "/fq"]).T.astype(np.float64)    # [H, O]
+        out[key + "/noise_before"] = np.float64(np.abs(X @ res).mean())
+        out[key + "/noise_after"] = np.float64(np.abs(X @ res - X @ _np(a).T.astype(np.float64) @ _np(b).T.astype(np.float64)).mean())
+    out["lora/index"] = np.array(names)
+
+
 def gen_config1(out: dict):
     """SHA-256 digests of every tensor of the state dict the reference's ``nncf.compress_weights`` produces for
     8 stacked Linear(4096 -> 4096) fp32 layers (INT4_SYM, group 128, ratio 1.0, CPU): a few hundred bytes that
@@ -564,6 +610,7 @@ def main():
         "gptq_large": gen_gptq_large,
         "config1": gen_config1,
         "layerwise": gen_layerwise,
+        "lora": gen_lora,
         "api": gen_api,
     }
     only = [a for a in sys.argv[1:] if a in groups]

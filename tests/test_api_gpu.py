@@ -529,3 +529,73 @@ def test_model_level_gptq_follows_the_reference_schedule_and_reference_gptq(mode
         logits = cm(ids[0]).float().cpu()
     want = torch.from_numpy(g[key + "/logits"])
     assert float((logits - want).norm() / want.norm()) < 2e-3
+
+
+def _lora_model(int8=True, mode="int4_sym", **extra):
+    import nncf_b200 as nb
+
+    ids = [i.cuda() for i in calibration_ids(n=8, seq=32)]
+    model = TinyGatedLM().cuda()
+    adv = nb.AdvancedCompressionParameters(lora_correction_params=nb.AdvancedLoraCorrectionParameters(
+        adapter_rank=4, use_int8_adapters=int8))
+    cm = nb.compress_weights(model, mode=nb.CompressWeightsMode(mode), group_size=16, dataset=nb.Dataset(ids),
+                             lora_correction=True, advanced_parameters=adv, **extra)
+    return cm, ids
+
+
+@pytest.mark.parametrize("int8", [True, False])
+def test_lora_correction_model_level_reduces_output_error(int8):
+    """``lora_correction=True`` (the reference has it for OpenVINO graphs only, openvino_backend.py:178-218,362-369):
+    every 4-bit Linear gets two adapters whose output is added to the layer's; the error of the model's output on
+    the calibration data falls below plain rounding's, the adapters are in the state dict (INT8_ASYM with their
+    own scale and zero point, or dense), embedding and INT8 backup layers get none."""
+    import nncf_b200 as nb
+
+    with torch.no_grad():
+        ids = [i.cuda() for i in calibration_ids(n=8, seq=32)]
+        base = torch.cat([TinyGatedLM().cuda()(i) for i in ids])
+        plain = nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode.INT4_SYM, group_size=16)
+        err_plain = float((torch.cat([plain(i) for i in ids]) - base).norm() / base.norm())
+        cm, _ = _lora_model(int8)
+        err_lora = float((torch.cat([cm(i) for i in ids]) - base).norm() / base.norm())
+    assert err_lora < 0.9 * err_plain, (err_lora, err_plain)
+    sd = cm.state_dict()
+    with_adapters = sorted({k.split(".lora_correction.")[0] for k in sd if ".lora_correction." in k})
+    assert with_adapters == sorted(n for n in LAYERS if n not in ("embed", "head"))
+    a = sd["blocks.0.q.lora_correction.a.weight"]
+    assert tuple(a.shape) == (4, 32) and a.dtype == (torch.uint8 if int8 else torch.float32)
+    assert ("blocks.0.q.lora_correction.a.decompressor._scale" in sd) == int8
+
+
+def test_lora_correction_survives_config_round_trip_and_strip():
+    import nncf_b200 as nb
+
+    cm, ids = _lora_model(True, "int4_asym")
+    with torch.no_grad():
+        want = cm(ids[0])
+    cfg = nb.get_config(cm)
+    assert cfg["weights"]["blocks.1.down"]["lora_correction"] == {"rank": 4, "int8": True}
+    fresh = nb.load_from_config(TinyGatedLM(seed=5).cuda(), cfg, cm.state_dict())
+    with torch.no_grad():
+        assert torch.equal(fresh(ids[0]), want)
+        stripped = nb.strip(fresh)
+        assert not any("lora_correction" in k or "parametrizations" in k for k in stripped.state_dict())
+        got = stripped(ids[0])
+    assert float((got - want).norm() / want.norm()) < 1e-5     # adapters folded into the dense weights
+
+
+def test_lora_correction_option_checks():
+    import nncf_b200 as nb
+
+    ids = [i.cuda() for i in calibration_ids()]
+    with pytest.raises(nb.ParameterNotSupportedError):
+        nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode.INT4_SYM, group_size=16,
+                            dataset=nb.Dataset(ids), gptq=True, lora_correction=True)
+    with pytest.raises(nb.ParameterNotSupportedError):
+        nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode.MXFP4, dataset=nb.Dataset(ids),
+                            lora_correction=True)
+    with pytest.raises(nb.ValidationError):
+        nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode.INT4_SYM, group_size=16,
+                            dataset=nb.Dataset(ids), lora_correction=True,
+                            advanced_parameters=nb.AdvancedCompressionParameters(
+                                lora_correction_params=nb.AdvancedLoraCorrectionParameters(adapter_rank=0)))
