@@ -68,6 +68,12 @@ API_CASES = [
     ("int4_sym_g16_ratio", dict(mode="int4_sym", group_size=16, ratio=0.6), False),
     ("int4_asym_g16_ratio_maxvar", dict(mode="int4_asym", group_size=16, ratio=0.6,
                                         sensitivity_metric="max_activation_variance"), True),
+    ("int4_sym_g16_ratio_hessian", dict(mode="int4_sym", group_size=16, ratio=0.5,
+                                        sensitivity_metric="hessian_input_activation"), True),
+    ("int4_sym_g16_ratio_meanvar", dict(mode="int4_sym", group_size=16, ratio=0.7,
+                                        sensitivity_metric="mean_activation_variance"), True),
+    ("int4_asym_g16_ratio_meanmag", dict(mode="int4_asym", group_size=16, ratio=0.4,
+                                         sensitivity_metric="mean_activation_magnitude"), True),
     ("int4_asym_g16_se", dict(mode="int4_asym", group_size=16, scale_estimation=True), True),
     ("int4_sym_g16_awq", dict(mode="int4_sym", group_size=16, awq=True), True),
     ("int4_asym_g16_awq_se", dict(mode="int4_asym", group_size=16, awq=True, scale_estimation=True), True),

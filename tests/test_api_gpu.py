@@ -567,7 +567,7 @@ def test_lora_correction_model_level_reduces_output_error(int8):
     assert ("blocks.0.q.lora_correction.a.decompressor._scale" in sd) == int8
 
 
-def test_lora_correction_survives_config_round_trip_and_strip():
+def test_lora_correction_survives_config_round_trip_and_strip(tmp_path):
     import nncf_b200 as nb
 
     cm, ids = _lora_model(True, "int4_asym")
@@ -576,8 +576,11 @@ def test_lora_correction_survives_config_round_trip_and_strip():
     cfg = nb.get_config(cm)
     assert cfg["weights"]["blocks.1.down"]["lora_correction"] == {"rank": 4, "int8": True}
     fresh = nb.load_from_config(TinyGatedLM(seed=5).cuda(), cfg, cm.state_dict())
+    nb.save_safetensors(cm, str(tmp_path / "lora.safetensors"))
+    from_file = nb.load_safetensors(TinyGatedLM(seed=6).cuda(), str(tmp_path / "lora.safetensors"))
     with torch.no_grad():
         assert torch.equal(fresh(ids[0]), want)
+        assert torch.equal(from_file(ids[0]), want)
         stripped = nb.strip(fresh)
         assert not any("lora_correction" in k or "parametrizations" in k for k in stripped.state_dict())
         got = stripped(ids[0])
@@ -599,3 +602,23 @@ def test_lora_correction_option_checks():
                             dataset=nb.Dataset(ids), lora_correction=True,
                             advanced_parameters=nb.AdvancedCompressionParameters(
                                 lora_correction_params=nb.AdvancedLoraCorrectionParameters(adapter_rank=0)))
+
+
+def test_lora_correction_after_awq_and_scale_estimation():
+    """The adapters are computed from the statistics as they stand after AWQ rescaled the activations and from
+    the weight ScaleEstimation's parameters produced (WC/algorithm.py:1150-1195): the combination runs and the
+    adapters still lower the output error of the same compression without them."""
+    import nncf_b200 as nb
+
+    ids = [i.cuda() for i in calibration_ids(n=8, seq=32)]
+    adv = nb.AdvancedCompressionParameters(awq_params=nb.AdvancedAWQParameters(percent_to_apply=0.05),
+                                           lora_correction_params=nb.AdvancedLoraCorrectionParameters(adapter_rank=4))
+    errs = {}
+    with torch.no_grad():
+        base = torch.cat([TinyGatedLM().cuda()(i) for i in ids])
+        for lora in (False, True):
+            cm = nb.compress_weights(TinyGatedLM().cuda(), mode=nb.CompressWeightsMode.INT4_ASYM, group_size=16,
+                                     dataset=nb.Dataset(ids), awq=True, scale_estimation=True,
+                                     lora_correction=lora or None, advanced_parameters=adv)
+            errs[lora] = float((torch.cat([cm(i) for i in ids]) - base).norm() / base.norm())
+    assert errs[True] < errs[False], errs
