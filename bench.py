@@ -314,6 +314,113 @@ def run_api_workload(args, device):
                       "seconds": seconds, "value": seconds["int4_sym_data_free"]}), flush=True)
 
 
+def run_decompress_workload(args, device):
+    """Decompression of stored weights (what every forward pass of a compressed model runs per layer): the seven
+    matrices of `--layers` Llama-3-8B decoder layers, INT4_SYM / INT4_ASYM g128 or INT8_ASYM per channel with fp16
+    scales as stored, decompressed to bf16 by one `nncfb_decompress` call per matrix.  GB/s of produced weights and
+    the fraction of the measured HBM peak in algorithmic bytes (codes + parameters read, bf16 weights written)."""
+    from nncf_b200 import CompressWeightsMode, WeightCompressionConfig, _lib
+    from nncf_b200.pipeline import CompressionPlan
+
+    mode = CompressWeightsMode(args.decompress_mode)
+    gs = -1 if mode == CompressWeightsMode.INT8_ASYM else 128
+    cfg = WeightCompressionConfig(mode, gs)
+    shapes = [("q_proj", (4096, 4096)), ("k_proj", (1024, 4096)), ("v_proj", (1024, 4096)), ("o_proj", (4096, 4096)),
+              ("gate_proj", (14336, 4096)), ("up_proj", (14336, 4096)), ("down_proj", (4096, 14336))]
+    gen = torch.Generator(device=device).manual_seed(1)
+    items = []
+    for layer in range(args.layers):
+        for name, shp in shapes:
+            w = torch.empty(shp, dtype=torch.bfloat16, device=device)
+            w.normal_(0.0, 0.02, generator=gen)
+            items.append((f"layers.{layer}.{name}", w, cfg))
+    plan = CompressionPlan(items, device, fp16_scales=True, packed_zero_points=True)
+    plan.run(use_graph=False)
+    torch.cuda.synchronize()
+    stored = []
+    out_bytes = alg_bytes = 0
+    for (name, w, _), it in zip(items, plan.items):
+        n = w.numel()
+        group = gs if gs != -1 else w.shape[1]
+        it.weight = None
+        zp = getattr(it, "zero_point_packed", None)
+        if zp is None and it.zero_point is not None:
+            zp = it.zero_point.to(torch.uint8)
+        out = torch.empty(n, dtype=torch.bfloat16, device=device)
+        scale = it.scale_f16 if it.scale_f16 is not None else it.scale.to(torch.float16)
+        stored.append((it.packed, n, group, scale, zp, out))
+        out_bytes += n * 2
+        alg_bytes += n * 2 + it.packed.numel() * it.packed.element_size() + scale.numel() * scale.element_size() + \
+            (zp.numel() * zp.element_size() if zp is not None else 0)
+    del items, plan
+    stream = _lib.stream_handle(device)
+    mode_id, bf16 = _lib.MODE_IDS[mode.value], _lib.DTYPE_IDS[torch.bfloat16]
+
+    def step():
+        nonlocal stream, stored
+        for packed, n, group, scale, zp, out in stored:
+            _lib.check(_lib.lib.nncfb_decompress(_lib.ptr(packed), mode_id, n, group, _lib.ptr(scale),
+                                                 _lib.ptr(zp) if zp is not None else None, _lib.ptr(out), bf16, stream))
+
+    # one pass = one CUDA graph of the per-matrix launches (28 ctypes calls take longer on the host than the
+    # kernels on the GPU); replayed like the compression pass of the headline workload
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        stream = _lib.stream_handle(device)
+        step()
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        stream = _lib.stream_handle(device)
+        step()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    peak, peak_src = _peaks()
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    # the same per shape: the launches of one kind of matrix (one per layer, different buffers) as a graph of their own
+    per_shape = {}
+    all_stored = stored
+    for k, (name, shp) in enumerate(shapes):
+        stored = all_stored[k::len(shapes)]
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2):
+            stream = _lib.stream_handle(device)
+            step()
+        for _ in range(3):
+            g2.replay()
+        e0.record()
+        for _ in range(args.steps):
+            g2.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps / len(stored)
+        n = shp[0] * shp[1]
+        bytes_one = alg_bytes * n / sum(a * b for _, (a, b) in shapes) / args.layers
+        per_shape[name] = {"us_per_launch": round(us, 2), "frac_of_hbm_peak": round(bytes_one / (us * 1e-6) / 1e9 / peak, 3)}
+    stored = all_stored
+    print(json.dumps({
+        "metric": f"decompressed_weight_GBps_{mode.value}", "value": round(out_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "data": "synthetic", "dtype": "f16",
+        "config": {"workload": f"decompression of {args.layers} Llama-3-8B decoder layers ({len(stored)} matrices, "
+                               f"{out_bytes / 1e9:.2f} GB of bf16 weights), {mode.value} group {gs}, fp16 scales; "
+                               "working set larger than L2"},
+        "gpu_launches": len(stored) * args.steps, "per_shape": per_shape,
+        "roofline": {"bound": "hbm", "kernel": "decompress_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes": "codes + scales (+ zero points) read, bf16 weights written"}}), flush=True)
+
+
 def run_moe_workload(args, device, rank, world, dist):
     """Benchmark configuration 5: NF4 (g128) or MXFP4 (E2M1 values, E8M0 scale per 32) data-free compression of a
     Mixtral-8x7B-shaped expert stack (per layer 8 experts x (w1, w3: 14336 x 4096; w2: 4096 x 14336), bf16
@@ -891,10 +998,12 @@ def main():
                          "against its NVLink ingest)")
     ap.add_argument("--registered-buffers", action="store_true",
                     help="N > 1: arenas from NCCL's allocator, registered with the communicator (zero-copy transfers)")
-    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "gptq_model", "data_aware", "data_aware_model", "moe", "api"],
+    ap.add_argument("--workload", default="compress", choices=["compress", "gptq", "gptq_model", "data_aware", "data_aware_model", "moe", "api", "decompress"],
                     help="compress: the headline line (default); gptq: per-kernel GPTQ timings; gptq_model: only the "
                          "GPTQ model run of the headline line")
     ap.add_argument("--mode", default="nf4", choices=["nf4", "mxfp4", "fp4"], help="mode of the moe workload")
+    ap.add_argument("--decompress-mode", default="int4_sym", choices=["int4_sym", "int4_asym", "int8_asym"],
+                    help="mode of the decompress workload")
     ap.add_argument("--layers", type=int, default=4, help="layers of the moe workload (32 = the full 90 GB stack)")
     ap.add_argument("--no-affinity", action="store_true", help="do not bind the process to the CPUs closest to its GPU")
     ap.add_argument("--profile-case", action="store_true",
@@ -939,10 +1048,10 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    if args.workload in ("gptq", "data_aware", "api", "data_aware_model"):
+    if args.workload in ("gptq", "data_aware", "api", "data_aware_model", "decompress"):
         if rank == 0:
             {"gptq": run_gptq_workload, "data_aware": run_data_aware_workload, "api": run_api_workload,
-             "data_aware_model": run_data_aware_model}[args.workload](args, device)
+             "data_aware_model": run_data_aware_model, "decompress": run_decompress_workload}[args.workload](args, device)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
