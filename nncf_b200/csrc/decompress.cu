@@ -125,28 +125,28 @@ __global__ void __launch_bounds__(256) decompress_kernel(const DecompressArgs a)
       if constexpr (mode_is_integer(MODE)) {
         const __half s = reinterpret_cast<const __half*>(a.scale)[g];
         const __half2 s2 = __half2half2(s);
+        // what is subtracted from 1024 + code: 1024 (+ 8 or + 128 for the symmetric modes' offset binary codes),
+        // plus the zero point for the asymmetric modes - every term an integer, so one subtraction is exact
+        uint32_t off_bits = MODE == NNCFB_INT4_SYM ? 0x64086408u : MODE == NNCFB_INT8_SYM ? 0x64806480u : 0x64006400u;
+        if constexpr (mode_is_asym(MODE)) {
+          uint32_t zb;
+          if constexpr (MODE == NNCFB_INT8_ASYM) zb = a.zp[g];
+          else zb = (a.zp[g >> 1] >> (4 * (g & 1))) & 15u;
+          off_bits |= zb | (zb << 16);
+        }
+        const __half2 off = as_half2(off_bits);
         __half2 x[4];
         if constexpr (kFour) {
           // nibbles i and i + 4 of the word as one pair
-          const __half2 off = __half2half2(__ushort_as_half(MODE == NNCFB_INT4_SYM ? 0x6408 : 0x6400));  // 1032 / 1024
 #pragma unroll
           for (int i = 0; i < 4; ++i) x[i] = __hsub2(as_half2(((raw[u].x >> (4 * i)) & 0x000f000fu) | 0x64006400u), off);
         } else {
           const uint32_t flip = MODE == NNCFB_INT8_SYM ? 0x80808080u : 0u;    // two's complement byte + 128
-          const __half2 off = __half2half2(__ushort_as_half(MODE == NNCFB_INT8_SYM ? 0x6480 : 0x6400));  // 1152 / 1024
           const uint32_t lo = raw[u].x ^ flip, hi = raw[u].y ^ flip;
           x[0] = __hsub2(as_half2(__byte_perm(lo, 0x64646464u, 0x4140)), off);
           x[1] = __hsub2(as_half2(__byte_perm(lo, 0x64646464u, 0x4342)), off);
           x[2] = __hsub2(as_half2(__byte_perm(hi, 0x64646464u, 0x4140)), off);
           x[3] = __hsub2(as_half2(__byte_perm(hi, 0x64646464u, 0x4342)), off);
-        }
-        if constexpr (mode_is_asym(MODE)) {
-          uint32_t zb;
-          if constexpr (MODE == NNCFB_INT8_ASYM) zb = a.zp[g];
-          else zb = (a.zp[g >> 1] >> (4 * (g & 1))) & 15u;
-          const __half2 z2 = __hsub2(as_half2((zb | (zb << 16)) | 0x64006400u), __half2half2(__ushort_as_half(0x6400)));
-#pragma unroll
-          for (int i = 0; i < 4; ++i) x[i] = __hsub2(x[i], z2);
         }
         __half2 r[4];
 #pragma unroll
