@@ -71,10 +71,18 @@ class ShardedCompression:
 
     def __init__(self, specs: Sequence[tuple], device, rank: Optional[int] = None, world_size: Optional[int] = None,
                  dst: int = 0, n_chunks: int = 4, dst_share: Optional[float] = None,
-                 group: Optional[dist.ProcessGroup] = None, registered_buffers: bool = False):
+                 group: Optional[dist.ProcessGroup] = None, registered_buffers: bool = False,
+                 peer_stores: bool = False):
         """``registered_buffers``: allocate the arenas from NCCL's own allocator and register them with the
         communicator (NCCL user-buffer registration), which lets NCCL move point-to-point data without its
-        staging copies where the transport supports it.  CUDA + NCCL only."""
+        staging copies where the transport supports it.  CUDA + NCCL only.
+
+        ``peer_stores``: no transfer step at all - the collecting rank's arena is mapped into every other rank's
+        process (CUDA IPC, one node) and their compression kernels write codes, scales and zero points straight
+        into their byte ranges of it over NVLink (plain stores to peer memory).  Nothing runs on the collecting
+        rank's SMs for the transfer and there is no staging copy; ``wait`` is a one-element all-reduce that orders
+        every rank's kernels before the collecting rank's next read.  Falls back to the NCCL transfers when the
+        mapping cannot be set up on every rank."""
         self.specs = list(specs)
         self.device = torch.device(device)
         self.group = group
@@ -128,6 +136,9 @@ class ShardedCompression:
         self.plan: Optional[CompressionPlan] = None
         self.arena: Optional[torch.Tensor] = None
         self.registered_buffers = bool(registered_buffers) and self.world > 1 and self.device.type == "cuda"
+        self.peer_stores = bool(peer_stores) and self.world > 1 and self.device.type == "cuda"
+        self._remote_arena: Optional[torch.Tensor] = None
+        self._flag: Optional[torch.Tensor] = None
         self._pool = None
         self._chunk_items: list[list[int]] = []
         self._pending: list = []
@@ -158,8 +169,15 @@ class ShardedCompression:
             start = self._region[(self.rank, 0)][0] if self.chunks[self.rank] else 0
             own = sum(self.out_sizes[i] for i in self.local_indices)
             self.plan = self._make_plan(items, self.arena[start:start + own]) if items else None
-        else:
-            self.plan = self._make_plan(items, arena[:own_bytes] if arena is not None else None) if items else None
+        if self.peer_stores:
+            self.peer_stores = self._map_collecting_arena()
+        if self.rank != self.dst:
+            if self.peer_stores:
+                start = self._region[(self.rank, 0)][0] if self.chunks[self.rank] else 0
+                target = self._remote_arena[start:start + own_bytes]
+            else:
+                target = arena[:own_bytes] if arena is not None else None
+            self.plan = self._make_plan(items, target) if items else None
             self.arena = self.plan.arena if self.plan is not None else None
         self._chunk_items, k = [], 0
         for chunk in self.chunks[self.rank]:
@@ -168,6 +186,53 @@ class ShardedCompression:
         if self.device.type == "cuda":
             with torch.cuda.device(self.device):
                 self._comm_stream = torch.cuda.Stream()
+
+    def _map_collecting_arena(self) -> bool:
+        """Maps the collecting rank's arena into this process (CUDA IPC) and lets this rank's GPU store into it.
+        Collective over the group; True when every rank succeeded."""
+        ok = 1
+        payload = [None]
+        try:
+            if self.rank == self.dst:
+                payload = [(torch.cuda.device_count(), self.arena.untyped_storage()._share_cuda_())]
+        except Exception:  # noqa: BLE001  (an allocator that cannot export its blocks: every rank falls back together)
+            ok = 0
+        dist.broadcast_object_list(payload, src=dist.get_global_rank(self.group, self.dst) if self.group is not None else self.dst,
+                                   group=self.group, device=self.device)
+        try:
+            if payload[0] is None:
+                ok = 0
+            elif self.rank != self.dst:
+                n_devices, handle = payload[0]
+                if n_devices != torch.cuda.device_count():
+                    msg = "the ranks do not see the same set of GPUs"
+                    raise RuntimeError(msg)
+                # The handle is opened with THIS rank's device current, so the collecting GPU's memory is mapped
+                # into this GPU's address space with peer access enabled for the mapping (what
+                # cudaIpcOpenMemHandle does for a handle from another device); torch then labels the tensor with
+                # this device although its bytes live on the collecting GPU.  Opened under the owner's device
+                # index instead, the mapping belongs to that device's context in this process and this GPU's
+                # kernels may not touch it.
+                if not torch.cuda.can_device_access_peer(self.device.index, int(handle[0])):
+                    msg = "the collecting rank's GPU is not a peer of this GPU"
+                    raise RuntimeError(msg)
+                with torch.cuda.device(self.device):
+                    storage = torch.UntypedStorage._new_shared_cuda(self.device.index, *handle[1:])
+                remote = torch.empty(0, dtype=torch.uint8, device=self.device).set_(storage)
+                if remote.numel() < self._arena_bytes:
+                    msg = "the collecting rank's arena is smaller than the model's results"
+                    raise RuntimeError(msg)
+                self._remote_arena = remote[: self._arena_bytes]
+        except Exception:  # noqa: BLE001
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        good = bool(int(flag.item()))
+        if not good:
+            self._remote_arena = None
+        else:
+            self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return good
 
     def _make_plan(self, items: list, arena: Optional[torch.Tensor]):
         """The batched launch plan of this rank's weights with its outputs in one arena (a seam for the CPU
@@ -187,6 +252,11 @@ class ShardedCompression:
         buffers then hold the previous pass's results)."""
         cuda = self.device.type == "cuda"
         self._pending = []
+        if self.peer_stores:
+            transfer = False  # the kernels' stores are the transfer
+            if compute and self.world > 1:
+                # nobody overwrites a byte range that the collecting rank may still be reading
+                dist.all_reduce(self._flag, group=self.group)
         if transfer and self.world > 1 and self.rank == self.dst:
             # receives first: they only need the arena, and the senders' first chunks arrive while this rank works
             ops = []
@@ -232,6 +302,10 @@ class ShardedCompression:
         complete.  No host synchronisation on CUDA."""
         for req in self._pending:
             req.wait()
+        if self.peer_stores and self.world > 1:
+            # stream-ordered on every rank behind its kernels: when this completes on the collecting rank, every
+            # other rank's stores into the arena have been performed
+            dist.all_reduce(self._flag, group=self.group)
         if self.device.type == "cuda" and self._comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
         self._pending = []
@@ -241,6 +315,14 @@ class ShardedCompression:
         the pool is deregistered from the communicator first, then its memory is returned."""
         self._pending = []
         self.plan = None
+        if self.peer_stores and self.world > 1:
+            # the mappings go before the memory: every rank drops its view, then the owner may free the arena
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            if self.rank != self.dst:
+                self.arena = None
+            self._remote_arena = None
+            dist.barrier(group=self.group)
         self.arena = None
         if self._pool is not None:
             pg = self.group if self.group is not None else dist.distributed_c10d._get_default_group()

@@ -1,5 +1,7 @@
 """The streamed multi-GPU compression on real GPUs: one model's tensors split over two ranks (NCCL), results
-collected in rank 0's arena while the other rank is still compressing, every byte checked against the oracle.
+collected in rank 0's arena while the other rank is still compressing, every byte checked against the oracle;
+by NCCL send / receive (plain or registered arenas) or by the other rank's kernels storing straight into rank 0's
+arena over NVLink (CUDA IPC mapping).
 Needs two GPUs (skipped otherwise); the protocol itself is covered on CPU by tests/test_sharding_cpu.py."""
 
 import os
@@ -23,7 +25,7 @@ def _weight(k, shape, device):
     return w
 
 
-def _worker(rank, world, port, registered, q):
+def _worker(rank, world, port, variant, q):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -37,8 +39,10 @@ def _worker(rank, world, port, registered, q):
         specs = [(f"w{k}", shp, torch.bfloat16, WeightCompressionConfig(CompressWeightsMode(m), g))
                  for k, (shp, m, g) in enumerate(SHAPES)]
         sc = ShardedCompression(specs, device, rank, world, dst=0, n_chunks=3, dst_share=0.5,
-                                registered_buffers=registered)
+                                registered_buffers=variant == "registered", peer_stores=variant == "peer_stores")
         sc.bind({i: _weight(i, specs[i][1], device) for i in sc.local_indices})
+        if variant == "peer_stores":
+            assert sc.peer_stores, "the collecting rank's arena could not be mapped"
         for _ in range(2):
             sc.run()
             sc.wait()
@@ -54,8 +58,8 @@ def _worker(rank, world, port, registered, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("registered", [False, True])
-def test_two_ranks_compress_one_model_and_rank_0_holds_every_result(registered):
+@pytest.mark.parametrize("variant", ["nccl", "registered", "peer_stores"])
+def test_two_ranks_compress_one_model_and_rank_0_holds_every_result(variant):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -67,7 +71,7 @@ def test_two_ranks_compress_one_model_and_rank_0_holds_every_result(registered):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, registered, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, variant, q)) for r in range(2)]
     for p in procs:
         p.start()
     got = {r: (out, idx) for r, out, idx in (q.get(timeout=300) for _ in procs)}
