@@ -480,10 +480,10 @@ class _GptqRanks:
     def same_factor(self, hinv: torch.Tensor) -> torch.Tensor:
         """Every rank computed the factor from the same Hessian; rank 0's copy is the one all of them use."""
         if self.world > 1:
-            dead = getattr(hinv, "_dead_columns", None)
+            dead, info = getattr(hinv, "_dead_columns", None), getattr(hinv, "_cholesky_info", None)
             self.dist.broadcast(hinv, self.dist.get_global_rank(self.group, 0) if self.group is not None else 0,
                                 group=self.group)
-            hinv._dead_columns = dead
+            hinv._dead_columns, hinv._cholesky_info = dead, info
         return hinv
 
     def from_owner(self, owner: int, p: WeightCompressionParameters, q, scale, zero_point):
@@ -711,6 +711,7 @@ def compress_weights(
                     p._gptq_weight = q[r0:r1]
                     r0 = r1
             timer.stop(h_sweeps)
+            g.check_factor(hinv)
             g.check_tensor_core_status(dev)
             for p in group:
                 p.module.weight.data = p._gptq_weight.to(p.weight.dtype)

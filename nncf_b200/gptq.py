@@ -200,25 +200,31 @@ class GPTQ:
         factorisations and a full inverse: under a third of the time at C = 14336 and a smaller rounding error (8.7e-7 against 1.4e-6 relative to an fp64
         evaluation); the two routes differ by 1.7e-6 relative, the size of the reference route's own
         rounding.  ``inverse_factor="reference"`` runs the reference's three calls instead."""
+        # Nothing here makes the host wait for the GPU (no boolean-mask indexing, no error check that reads a flag
+        # back): the host goes on enqueueing the inverse and the sweeps while the factorisation runs.  The
+        # factorisation's status travels with the factor and is read by ``check_factor`` / the caller's one check.
         diag = torch.diagonal(hessian)
         dead = diag == 0
-        diag[dead] = 1
-        weight_tensor[:, dead] = 0
+        diag.masked_fill_(dead, 1.0)
+        weight_tensor.masked_fill_(dead, 0.0)
         damp = self._damp_percent * torch.mean(torch.diagonal(hessian))
         torch.diagonal(hessian).add_(damp)
         if self._inverse_factor == "reference":
-            L = torch.linalg.cholesky(hessian)
+            L, info = torch.linalg.cholesky_ex(hessian)
             Hinv = torch.cholesky_inverse(L)
-            U = torch.linalg.cholesky(Hinv, upper=True).contiguous()
+            U, info2 = torch.linalg.cholesky_ex(Hinv, upper=True)
+            U = U.contiguous()
+            info = torch.maximum(info, info2)
         else:
             # The factorisation itself stays with the library: a blocked Cholesky whose panel solves and trailing
             # updates run as tensor-core products was measured at 19.7 ms against cuSOLVER's 24.8 ms (C = 14336)
             # but five times less accurate (1.4e-6 against 2.6e-7 relative to an fp64 factor), which is not a trade
             # worth making for GPTQ.
-            L = torch.linalg.cholesky(torch.flip(hessian, (0, 1)))
+            L, info = torch.linalg.cholesky_ex(torch.flip(hessian, (0, 1)))
             U = torch.flip(lower_triangular_inverse(L), (0, 1)).contiguous()
             del L
-        U._dead_columns = dead if bool(dead.any()) else None  # reused when several weights share this factor
+        U._dead_columns = dead            # reused when several weights share this factor
+        U._cholesky_info = info           # 0, or the order of the leading minor that is not positive definite
         return U
 
     @staticmethod
@@ -251,7 +257,7 @@ class GPTQ:
         if hinv is None:
             hinv = self.prepare_hessian_inverse(hessian, weight_tensor)
         elif getattr(hinv, "_dead_columns", None) is not None:
-            weight_tensor[:, hinv._dead_columns] = 0
+            weight_tensor.masked_fill_(hinv._dead_columns, 0.0)
         rows, cols = weight_tensor.shape
         gs = config.group_size if config.group_size != -1 else cols
         dev = weight_tensor.device
@@ -286,8 +292,10 @@ class GPTQ:
                     _lib.ptr(weight_tensor), rows, cols, _lib.ptr(hinv), _lib.MODE_IDS[config.mode.value], gs,
                     self._block_size, _lib.ptr(q), _lib.ptr(scale), _lib.ptr(zp), _lib.ptr(workspace), ws_bytes,
                     _lib.stream_handle(dev)))
-            if self._tensor_cores and check_status:
-                _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(dev)))  # bounded waits of the TC kernels
+            if check_status:
+                self.check_factor(hinv)
+                if self._tensor_cores:
+                    _lib.check(_lib.lib.nncfb_hessian_status(_lib.stream_handle(dev)))  # bounded waits of the TC kernels
         scales = scale.reshape(rows, G, 1)
         zero_points = zp.reshape(rows, G, 1) if zp is not None else None
         if config.group_size == -1:
@@ -296,6 +304,16 @@ class GPTQ:
         if config.mode not in (CompressWeightsMode.INT8_ASYM, CompressWeightsMode.INT4_ASYM):
             zero_points = None
         return q, scales, zero_points
+
+    @staticmethod
+    def check_factor(hinv: torch.Tensor) -> None:
+        """Raises like ``torch.linalg.cholesky`` when the factorisation behind ``hinv`` met a Hessian that is not
+        positive definite (reads one integer back: synchronises)."""
+        info = getattr(hinv, "_cholesky_info", None)
+        if info is not None and int(info.max()) != 0:
+            msg = (f"linalg.cholesky: The factorization could not be completed because the input is not "
+                   f"positive-definite (the leading minor of order {int(info.max())} is not positive-definite).")
+            raise torch.linalg.LinAlgError(msg)
 
     @staticmethod
     def check_tensor_core_status(device: torch.device) -> None:

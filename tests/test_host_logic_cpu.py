@@ -311,3 +311,19 @@ def test_same_input_groups_equal_the_reference_schedule():
     groups = _same_input_groups(model, layerwise_ids()[0], targets)
     got = [",".join(p.weight_name for p in grp) for grp in groups]
     assert got == [str(s) for s in golden("layerwise")["layerwise/int4_sym/steps"]]
+
+
+def test_factor_of_an_indefinite_hessian_is_reported_by_the_deferred_check():
+    """The factorisation's error check does not read a flag back when it runs (the host keeps enqueueing); the
+    status travels with the factor and ``check_factor`` raises what ``torch.linalg.cholesky`` would have."""
+    from nncf_b200 import gptq as g
+
+    good = torch.eye(64) * 2.0
+    w = torch.randn(8, 64)
+    hinv = g.GPTQ(0.01).prepare_hessian_inverse(good.clone(), w.clone())
+    g.GPTQ.check_factor(hinv)
+    bad = good.clone()
+    bad[5, 5] = -3.0
+    hinv = g.GPTQ(0.01).prepare_hessian_inverse(bad, w.clone())
+    with pytest.raises(torch.linalg.LinAlgError):
+        g.GPTQ.check_factor(hinv)
