@@ -352,6 +352,20 @@ def test_inner_dimension_that_is_not_a_multiple_of_8_compresses_and_runs(mode, k
         np.testing.assert_array_equal(m.weight.detach().cpu().numpy(), dq.reshape(w.shape))
 
 
+def _distributed_gptq_model():
+    """A two-block Llama and 16 x 64 calibration tokens over a vocabulary of 512: more tokens than hidden channels and
+    more distinct embeddings than that, so every Hessian has full rank and the comparison between two summation
+    orders is not dominated by the damping of a singular matrix."""
+    import transformers
+
+    cfg = transformers.LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+    gen = torch.Generator().manual_seed(0)
+    ids = [torch.randint(0, 512, (1, 64), generator=gen).cuda() for _ in range(16)]
+    torch.manual_seed(0)
+    return transformers.LlamaForCausalLM(cfg).cuda().eval(), ids
+
+
 def _distributed_gptq_worker(rank, world, port, q):
     import os
 
@@ -361,20 +375,13 @@ def _distributed_gptq_worker(rank, world, port, q):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        import transformers
-
         import nncf_b200 as nb
 
-        cfg = transformers.LlamaConfig(vocab_size=96, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-                                       num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
-        gen = torch.Generator().manual_seed(0)
-        ids = [torch.randint(0, 96, (1, 32), generator=gen).cuda() for _ in range(8)]
-        torch.manual_seed(0)
-        model = transformers.LlamaForCausalLM(cfg).cuda().eval()
+        model, ids = _distributed_gptq_model()
         model = nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_ASYM, group_size=64, dataset=nb.Dataset(ids),
                                     gptq=True, process_group=dist.group.WORLD,
                                     advanced_parameters=nb.AdvancedCompressionParameters(
-                                        gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.1, subset_size=8)))
+                                        gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.1, subset_size=16)))
         sd = {k: v.cpu() for k, v in model.state_dict().items()}
         with torch.no_grad():
             sd["__logits"] = model(ids[0]).logits.float().cpu()
@@ -396,7 +403,6 @@ def test_gptq_shared_among_two_ranks_matches_one_rank():
     import socket
 
     import torch.multiprocessing as mp
-    import transformers
 
     import nncf_b200 as nb
 
@@ -414,15 +420,10 @@ def test_gptq_shared_among_two_ranks_matches_one_rank():
     assert all(isinstance(v, dict) for v in results.values()), results
     a, b = results[0], results[1]
     assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
-    cfg = transformers.LlamaConfig(vocab_size=96, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
-    gen = torch.Generator().manual_seed(0)
-    ids = [torch.randint(0, 96, (1, 32), generator=gen).cuda() for _ in range(8)]
-    torch.manual_seed(0)
-    model = transformers.LlamaForCausalLM(cfg).cuda().eval()
+    model, ids = _distributed_gptq_model()
     model = nb.compress_weights(model, mode=nb.CompressWeightsMode.INT4_ASYM, group_size=64, dataset=nb.Dataset(ids),
                                 gptq=True, advanced_parameters=nb.AdvancedCompressionParameters(
-                                    gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.1, subset_size=8)))
+                                    gptq_params=nb.AdvancedGPTQParameters(damp_percent=0.1, subset_size=16)))
     one = {k: v.cpu() for k, v in model.state_dict().items()}
     with torch.no_grad():
         one["__logits"] = model(ids[0]).logits.float().cpu()
