@@ -717,7 +717,8 @@ def run_compress(args, device, rank, world, local_rank, dist):
         specs = specs[1:8]  # one decoder layer: 436 MB of weights, larger than L2
         args.steps, args.no_e2e, args.no_cpu_baseline, args.no_gptq, args.no_parity = 1, True, True, True, True
     sc = ShardedCompression(specs, device, rank, world, dst=0, n_chunks=args.chunks, dst_share=args.dst_share,
-                            registered_buffers=args.registered_buffers, peer_stores=args.transport == "peer")
+                            registered_buffers=args.registered_buffers, peer_stores=args.transport == "peer",
+                            peer_copies=args.transport == "peer_copy")
     index_of = {s[0]: i for i, s in enumerate(specs)}
     weights = {i: make_weight(specs[i][1], i if not args.profile_case else i + 1, device) for i in sc.local_indices}
     sc.bind(weights)
@@ -820,7 +821,7 @@ def run_compress(args, device, rank, world, local_rank, dist):
             "compress_only": {"ms_per_step_max_over_ranks": round(compress_ms, 4),
                               "value": round(src_total / (compress_ms * 1e-3) / 1e9, 1),
                               "ms_per_rank": [round(float(g[0]), 4) for g in gathered]},
-            "transport": "peer stores" if sc.peer_stores else "NCCL send/recv",
+            "transport": ("peer copies" if sc.peer_copies else "peer stores") if sc.peer_stores else "NCCL send/recv",
             "gather_only": None if sc.peer_stores else {
                 "ms_per_step": round(gather_ms, 4), "bytes_into_rank0": sc.output_bytes_total -
                 sum(sc.out_sizes[i] for i in sc.assignment[0]),
@@ -829,9 +830,12 @@ def run_compress(args, device, rank, world, local_rank, dist):
             "bytes_into_rank0": sc.output_bytes_total - sum(sc.out_sizes[i] for i in sc.assignment[0]),
             "gather_exposed_ms": None if sc.peer_stores else round(ms_per_step - compress_ms, 4),
             "bound_ms": round(compress_ms if sc.peer_stores else max(compress_ms, gather_ms), 4),
-            "how": ("rank 0's arena is mapped into every rank's process (CUDA IPC); the other ranks' compression kernels "
-                    "store codes, scales and zero points straight into their byte ranges of it over NVLink; one "
-                    "4-byte all-reduce before and after a pass orders them against rank 0's reads; requested: " +
+            "how": ("rank 0's arena is mapped into every rank's process (CUDA IPC); " +
+                    ("every finished chunk of another rank is copied into its byte range of it by one cudaMemcpyAsync "
+                     "(copy engines over NVLink, nothing on any SM); " if sc.peer_copies else
+                     "the other ranks' compression kernels store codes, scales and zero points straight into their "
+                     "byte ranges of it over NVLink; ") +
+                    "one 4-byte all-reduce before and after a pass orders them against rank 0's reads; requested: " +
                     args.transport) if sc.peer_stores else
                    ("per chunk one nncfb_quantize_batch launch, an event, one NCCL isend of the chunk's contiguous output "
                     "range on a side stream; rank 0 posts irecvs straight into the final arena (no repacking, no "
@@ -1010,7 +1014,7 @@ def main():
                     help="compress: the headline line (default); gptq: per-kernel GPTQ timings; gptq_model: only the "
                          "GPTQ model run of the headline line")
     ap.add_argument("--mode", default="nf4", choices=["nf4", "mxfp4", "fp4"], help="mode of the moe workload")
-    ap.add_argument("--transport", default="peer", choices=["nccl", "peer"],
+    ap.add_argument("--transport", default="peer_copy", choices=["nccl", "peer", "peer_copy"],
                     help="N > 1: how results reach rank 0 (NCCL send/recv, or the kernels' own stores into rank 0's "
                          "memory over NVLink)")
     ap.add_argument("--decompress-mode", default="int4_sym", choices=["int4_sym", "int4_asym", "int8_asym"],

@@ -72,7 +72,7 @@ class ShardedCompression:
     def __init__(self, specs: Sequence[tuple], device, rank: Optional[int] = None, world_size: Optional[int] = None,
                  dst: int = 0, n_chunks: int = 4, dst_share: Optional[float] = None,
                  group: Optional[dist.ProcessGroup] = None, registered_buffers: bool = False,
-                 peer_stores: bool = False):
+                 peer_stores: bool = False, peer_copies: bool = False):
         """``registered_buffers``: allocate the arenas from NCCL's own allocator and register them with the
         communicator (NCCL user-buffer registration), which lets NCCL move point-to-point data without its
         staging copies where the transport supports it.  CUDA + NCCL only.
@@ -82,7 +82,11 @@ class ShardedCompression:
         into their byte ranges of it over NVLink (plain stores to peer memory).  Nothing runs on the collecting
         rank's SMs for the transfer and there is no staging copy; ``wait`` is a one-element all-reduce that orders
         every rank's kernels before the collecting rank's next read.  Falls back to the NCCL transfers when the
-        mapping cannot be set up on every rank."""
+        mapping cannot be set up on every rank.
+
+        ``peer_copies``: the same mapping, but the kernels keep writing into the rank's own arena and every finished
+        chunk is copied into the collecting rank's arena by one ``cudaMemcpyAsync`` on a side stream (the copy
+        engines move it in large NVLink writes; nothing runs on any SM for the transfer)."""
         self.specs = list(specs)
         self.device = torch.device(device)
         self.group = group
@@ -93,7 +97,12 @@ class ShardedCompression:
         self.layouts = [stored_outputs(s[0], s[1], -1, s[3]) for s in self.specs]
         self.out_sizes = [stored_bytes(lay) for lay in self.layouts]
         if dst_share is None:
-            dst_share = default_dst_share(self.world, float(sum(sizes)), float(sum(self.out_sizes)))
+            # measured ingest of the collecting GPU: ~650 GB/s through NCCL send/recv or from one peer's copy engine,
+            # ~820 GB/s when several peers' copy engines write at once (the share that made all ranks finish
+            # together at N = 4 was 0.62)
+            several_copiers = bool(peer_copies) and self.world > 2
+            dst_share = default_dst_share(self.world, float(sum(sizes)), float(sum(self.out_sizes)),
+                                          ingest_gbps=820.0 if several_copiers else 650.0)
         self.dst_share = 1.0 if self.world == 1 else float(dst_share)
         capacity = None
         if self.world > 1:
@@ -136,7 +145,8 @@ class ShardedCompression:
         self.plan: Optional[CompressionPlan] = None
         self.arena: Optional[torch.Tensor] = None
         self.registered_buffers = bool(registered_buffers) and self.world > 1 and self.device.type == "cuda"
-        self.peer_stores = bool(peer_stores) and self.world > 1 and self.device.type == "cuda"
+        self.peer_copies = bool(peer_copies) and self.world > 1 and self.device.type == "cuda"
+        self.peer_stores = (bool(peer_stores) or self.peer_copies) and self.world > 1 and self.device.type == "cuda"
         self._remote_arena: Optional[torch.Tensor] = None
         self._flag: Optional[torch.Tensor] = None
         self._pool = None
@@ -171,8 +181,9 @@ class ShardedCompression:
             self.plan = self._make_plan(items, self.arena[start:start + own]) if items else None
         if self.peer_stores:
             self.peer_stores = self._map_collecting_arena()
+        self.peer_copies = self.peer_copies and self.peer_stores
         if self.rank != self.dst:
-            if self.peer_stores:
+            if self.peer_stores and not self.peer_copies:
                 start = self._region[(self.rank, 0)][0] if self.chunks[self.rank] else 0
                 target = self._remote_arena[start:start + own_bytes]
             else:
@@ -284,6 +295,15 @@ class ShardedCompression:
                         self.plan.launch(idx)
                 else:
                     self.plan.launch(idx)
+            if self.peer_copies and compute and self.rank != self.dst:
+                view = self._chunk_view(c)
+                if view.numel():
+                    off = self._region[(self.rank, c)][0]
+                    done = torch.cuda.Event()
+                    done.record(torch.cuda.current_stream(self.device))
+                    self._comm_stream.wait_event(done)
+                    with torch.cuda.stream(self._comm_stream):
+                        self._remote_arena[off:off + view.numel()].copy_(view, non_blocking=True)
             if transfer and self.world > 1 and self.rank != self.dst:
                 view = self._chunk_view(c)
                 if view.numel() == 0:
@@ -303,8 +323,10 @@ class ShardedCompression:
         for req in self._pending:
             req.wait()
         if self.peer_stores and self.world > 1:
-            # stream-ordered on every rank behind its kernels: when this completes on the collecting rank, every
-            # other rank's stores into the arena have been performed
+            if self.peer_copies and self._comm_stream is not None:
+                torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+            # stream-ordered on every rank behind its kernels (and copies): when this completes on the collecting
+            # rank, every other rank's stores into the arena have been performed
             dist.all_reduce(self._flag, group=self.group)
         if self.device.type == "cuda" and self._comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)

@@ -1,7 +1,7 @@
 """The streamed multi-GPU compression on real GPUs: one model's tensors split over two ranks (NCCL), results
 collected in rank 0's arena while the other rank is still compressing, every byte checked against the oracle;
-by NCCL send / receive (plain or registered arenas) or by the other rank's kernels storing straight into rank 0's
-arena over NVLink (CUDA IPC mapping).
+by NCCL send / receive (plain or registered arenas), by the other rank's kernels storing straight into rank 0's
+arena over NVLink (CUDA IPC mapping), or by copies of finished chunks into that mapping.
 Needs two GPUs (skipped otherwise); the protocol itself is covered on CPU by tests/test_sharding_cpu.py."""
 
 import os
@@ -39,9 +39,10 @@ def _worker(rank, world, port, variant, q):
         specs = [(f"w{k}", shp, torch.bfloat16, WeightCompressionConfig(CompressWeightsMode(m), g))
                  for k, (shp, m, g) in enumerate(SHAPES)]
         sc = ShardedCompression(specs, device, rank, world, dst=0, n_chunks=3, dst_share=0.5,
-                                registered_buffers=variant == "registered", peer_stores=variant == "peer_stores")
+                                registered_buffers=variant == "registered", peer_stores=variant == "peer_stores",
+                                peer_copies=variant == "peer_copies")
         sc.bind({i: _weight(i, specs[i][1], device) for i in sc.local_indices})
-        if variant == "peer_stores":
+        if variant in ("peer_stores", "peer_copies"):
             assert sc.peer_stores, "the collecting rank's arena could not be mapped"
         for _ in range(2):
             sc.run()
@@ -58,7 +59,7 @@ def _worker(rank, world, port, variant, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("variant", ["nccl", "registered", "peer_stores"])
+@pytest.mark.parametrize("variant", ["nccl", "registered", "peer_stores", "peer_copies"])
 def test_two_ranks_compress_one_model_and_rank_0_holds_every_result(variant):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
