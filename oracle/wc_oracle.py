@@ -782,3 +782,45 @@ def gptq_quantize(weight: np.ndarray, hinv: np.ndarray, mode: str, group_size: i
         S = np.squeeze(S, axis=-1)
         Z = np.squeeze(Z, axis=-1) if Z is not None else None
     return Q, S, Z
+
+
+# ---------------------------------------------------------------------------------------
+# LoRA correction (WC/lora_correction.py:139-271)
+# ---------------------------------------------------------------------------------------
+def lora_correction_adapters(weight: np.ndarray, fq_weight: np.ndarray, mean_values: Sequence[np.ndarray],
+                             shape_values: Sequence[tuple], group_size: int, rank: int = 8, num_iterations: int = 3,
+                             apply_regularization: bool = True, subset_size: int = 128):
+    """The two low-rank adapters of one layer, with the reference's own dense routines: full SVD of the weighted
+    residual for the start (:212-216), then alternating least squares with QR-type solvers (:222-269).
+    ``weight`` / ``fq_weight`` [O, H] (reduction axis 1); returns (lora_A [R, H], lora_B [O, R]) in fp32."""
+    residual = (weight.astype(np.float32) - fq_weight.astype(np.float32)).T.copy()      # [H, O]
+    s, X = process_stats(mean_values, shape_values, subset_size)                         # [H], [H, SS]
+    s = s.astype(np.float32).copy()
+    X = X.astype(np.float32).T                                                           # [SS, H]
+    svd_residual = residual
+    if group_size > 0:
+        # :197-209: activation magnitudes normalised per quantisation group (sum to one, then largest = one)
+        for i in range(s.shape[0] // group_size):
+            sl = slice(i * group_size, (i + 1) * group_size)
+            s[sl] = s[sl] / np.sum(s[sl])
+            s[sl] = s[sl] / np.max(s[sl])
+        svd_residual = residual * s[:, None]
+    U_full, S_full, V_full = np.linalg.svd(svd_residual, full_matrices=False)
+    U = U_full[:, :rank]
+    V = np.diag(S_full[:rank]) @ V_full[:rank, :]
+    noise = X @ residual
+    for _ in range(num_iterations):
+        XU = X @ U
+        if not apply_regularization:
+            V = np.linalg.lstsq(XU, noise, rcond=None)[0]
+        else:
+            V = np.linalg.lstsq(np.concatenate([U, XU], axis=0), np.concatenate([residual, noise], axis=0), rcond=None)[0]
+        VI = np.linalg.pinv(V)
+        noiseVI = noise @ VI
+        if not apply_regularization:
+            U = np.linalg.lstsq(X, noiseVI, rcond=None)[0]
+        else:
+            E = np.eye(U.shape[0], dtype=U.dtype)
+            U = np.linalg.lstsq(np.concatenate([E, X], axis=0), np.concatenate([residual @ VI, noiseVI], axis=0),
+                                rcond=None)[0]
+    return U.T.astype(np.float32), V.T.astype(np.float32)

@@ -69,3 +69,43 @@ def test_adapters_on_the_gpu_from_the_library_dequantisation(case):
     a, b = LoraCorrectionAlgorithm.calculate_low_rank_matrices(w.cuda(), mine, cfg, (1,), prm, stats)
     want = torch.from_numpy(g[key + "/lora_B"]) @ torch.from_numpy(g[key + "/lora_A"])
     assert float(((b @ a).cpu() - want).norm() / want.norm()) < 1e-4
+
+
+@pytest.mark.parametrize("case", LORA_CASES, ids=[c[0] for c in LORA_CASES])
+def test_oracle_adapters_match_reference_golden(case):
+    """The numpy restatement with the reference's dense routines (full SVD, least squares on the stacked systems)
+    against the same goldens, and the package's small-system formulation against the restatement on a wider
+    layer than the fixtures hold."""
+    from oracle import wc_oracle as O
+
+    name, o, h, gs, n, mode, rank, iters, reg = case
+    g = golden("lora")
+    key = f"lora/{name}"
+    shapes = [(1, int(t), h) for t in g[key + "/tokens"]]
+    a, b = O.lora_correction_adapters(g[key + "/w"], g[key + "/fq"], list(g[key + "/means"]), shapes, gs, rank, iters, reg)
+    want = g[key + "/lora_B"].astype(np.float64) @ g[key + "/lora_A"].astype(np.float64)
+    have = b.astype(np.float64) @ a.astype(np.float64)
+    assert np.linalg.norm(have - want) / np.linalg.norm(want) < 1e-4
+
+
+def test_small_system_formulation_equals_the_dense_one_on_a_wider_layer():
+    import nncf_b200 as nb
+    from nncf_b200.config import WCTensorStatistic
+    from nncf_b200.lora_correction import LoraCorrectionAlgorithm
+    from oracle import wc_oracle as O
+
+    rng = np.random.default_rng(5)
+    o, h, gs, n = 192, 512, 64, 48
+    w = rng.normal(0, 0.05, size=(o, h)).astype(np.float32)
+    dq, _ = O.integer_quantize_dequantize(w, "int4_asym", gs, 1)
+    fq = np.asarray(dq, dtype=np.float32).reshape(o, h)
+    means = [(rng.normal(0, 1.0, size=(h,)) * (1 + 9 * (rng.random(h) < 0.05))).astype(np.float32) for _ in range(n)]
+    shapes = [(1, int(rng.integers(4, 40)), h) for _ in range(n)]
+    a0, b0 = O.lora_correction_adapters(w, fq, means, shapes, gs)
+    stats = WCTensorStatistic([torch.from_numpy(m) for m in means], shapes)
+    a1, b1 = LoraCorrectionAlgorithm.calculate_low_rank_matrices(
+        torch.from_numpy(w), torch.from_numpy(fq), nb.WeightCompressionConfig(nb.CompressWeightsMode.INT4_ASYM, gs), (1,),
+        nb.AdvancedLoraCorrectionParameters(), stats)
+    want = b0.astype(np.float64) @ a0.astype(np.float64)
+    have = (b1.double() @ a1.double()).numpy()
+    assert np.linalg.norm(have - want) / np.linalg.norm(want) < 1e-4
