@@ -100,7 +100,7 @@ __device__ __forceinline__ void store_pairs<float>(float* dst, const __half2 (&r
 }
 
 template <typename OutT, int MODE>
-__global__ void __launch_bounds__(256) decompress_kernel(const DecompressArgs a) {
+__global__ void __launch_bounds__(256, 8) decompress_kernel(const DecompressArgs a) {
   constexpr bool kFour = mode_bits(MODE) == 4;
   constexpr int U = kDecompressUnroll;
   const int64_t nvec = a.n >> 3;
