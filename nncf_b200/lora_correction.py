@@ -116,7 +116,6 @@ class LoraCorrectionAlgorithm:
 
         x64, res64 = x.double(), residual.double()
         noise = x64 @ res64                                           # [SS, O]
-        eye_r = torch.eye(rank, dtype=torch.float64, device=residual.device)
         # (I + X^T X)^-1 B = B - X^T (I + X X^T)^-1 (X B): one SS x SS factorisation serves every iteration
         gram_x = x64 @ x64.T
         if p.apply_regularization:
@@ -133,7 +132,7 @@ class LoraCorrectionAlgorithm:
             else:
                 lhs = xu.T @ xu
                 rhs = xu.T @ noise
-            v64 = _solve_small(lhs, rhs, eye_r)
+            v64 = _solve_small(lhs, rhs)
             # part 2: V fixed, find U
             vi = torch.linalg.pinv(v64)                               # [O, R]
             noise_vi = noise @ vi                                     # [SS, R]
@@ -146,7 +145,7 @@ class LoraCorrectionAlgorithm:
         return u64.T.float().contiguous(), v64.T.float().contiguous()
 
 
-def _solve_small(lhs: torch.Tensor, rhs: torch.Tensor, eye: torch.Tensor) -> torch.Tensor:
+def _solve_small(lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
     """Least-squares solution of an R x R normal system; a singular system (rank-deficient start) falls back to
     the pseudo-inverse, which is what a rank-revealing least-squares driver returns."""
     try:

@@ -200,3 +200,16 @@ def test_streamed_sharded_compression_collects_every_result_on_rank_0(world, dst
         assert p.exitcode == 0
     assert all(r[1] == "ok" for r in results), results
     assert [r for r in results if r[0] == 0][0][2] > 0   # something did cross between the ranks
+
+
+def test_default_share_of_the_collecting_rank():
+    """The collecting rank keeps the share at which its own work and its ingest end together: more of the model when
+    results arrive slowly, never less than an even split, everything on one GPU."""
+    from nncf_b200.sharding import default_dst_share
+
+    src, out = 16.06e9, 4.76e9
+    assert default_dst_share(1, src, out) == 1.0
+    slow = default_dst_share(8, src, out, ingest_gbps=650.0)
+    fast = default_dst_share(8, src, out, ingest_gbps=820.0)
+    assert 0.6 < fast < slow < 0.7
+    assert default_dst_share(2, src, out, ingest_gbps=1e6) == 0.5
