@@ -213,3 +213,77 @@ def test_default_share_of_the_collecting_rank():
     fast = default_dst_share(8, src, out, ingest_gbps=820.0)
     assert 0.6 < fast < slow < 0.7
     assert default_dst_share(2, src, out, ingest_gbps=1e6) == 0.5
+
+
+def _gptq_ranks_worker(rank, world, port, q):
+    import os
+    from types import SimpleNamespace
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import nncf_b200 as nb
+        from nncf_b200.compress_api import _GptqRanks
+        from nncf_b200.config import WCTensorStatistic
+
+        ranks = _GptqRanks(dist.group.WORLD)
+        items = list(range(7))
+        mine = ranks.share(items)
+        # every rank accumulates the running average (2 / n_r) * sum x^T x over ITS items; the combination must be
+        # the average over all of them
+        gen = torch.Generator().manual_seed(0)
+        xs = [torch.randn(5, 6, generator=gen, dtype=torch.float64) for _ in items]
+        H = torch.zeros(6, 6, dtype=torch.float64)
+        for i in mine:
+            H += (2.0 / len(mine)) * xs[i].T @ xs[i]
+        stat = WCTensorStatistic([xs[i].mean(0) for i in mine], [(1, 5, 6)] * len(mine))
+        Hc, merged = ranks.combine(H, len(mine), stat)
+        want = sum((2.0 / len(items)) * x.T @ x for x in xs)
+        factor = torch.full((3, 3), float(rank + 1))
+        factor._dead_columns, factor._cholesky_info = "dead", "info"
+        factor = ranks.same_factor(factor)
+        p = SimpleNamespace(compression_config=nb.WeightCompressionConfig(nb.CompressWeightsMode.INT4_ASYM, 2),
+                            weight=torch.zeros(3, 4))
+        owner = 1
+        given = (torch.full((3, 4), 7.0), torch.full((3, 2, 1), 0.5), torch.full((3, 2, 1), 3, dtype=torch.int32)) \
+            if rank == owner else (None, None, None)
+        got = ranks.from_owner(owner, p, *given)
+        q.put((rank, dict(
+            mine=mine, h_err=float((Hc - want).abs().max()),
+            means_in_item_order=all(torch.equal(m, xs[i].mean(0)) for i, m in enumerate(merged.mean_values)),
+            n_means=len(merged.mean_values), factor=float(factor[0, 0]), kept=(factor._dead_columns, factor._cholesky_info),
+            owner_values=(float(got[0][0, 0]), float(got[1][0, 0, 0]), int(got[2][0, 0, 0])))))
+    except Exception as exc:  # noqa: BLE001
+        q.put((rank, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gptq_exchange_steps_over_two_gloo_ranks():
+    """The three exchange steps of distributed GPTQ on CPU tensors: calibration items dealt round-robin, per-rank
+    running averages of the Hessian combined into the average over all items (weights n_r / n), per-item statistics
+    back in item order, rank 0's factor on every rank, one layer's results from the rank that swept it."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_gptq_ranks_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert all(isinstance(v, dict) for v in out.values()), out
+    assert out[0]["mine"] == [0, 2, 4, 6] and out[1]["mine"] == [1, 3, 5]
+    for r in (0, 1):
+        assert out[r]["h_err"] < 1e-12
+        assert out[r]["means_in_item_order"] and out[r]["n_means"] == 7
+        assert out[r]["factor"] == 1.0 and out[r]["kept"] == ("dead", "info")
+        assert out[r]["owner_values"] == (7.0, 0.5, 3)
